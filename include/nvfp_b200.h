@@ -1,0 +1,137 @@
+/*
+ * nvfp_b200.h -- C ABI of libnvfp_b200.so: NVFP4 / MXFP4 quantize and block-scaled
+ * FP4 GEMM for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its work on the
+ * given CUDA stream (a cudaStream_t passed as void*; NULL = the legacy default
+ * stream) of the CURRENT device and returns without synchronising.  The return value
+ * is an nvfp_status_t; on failure nvfp_last_error() holds a message for the calling
+ * thread.  Nothing here allocates device memory unless the comment on the function
+ * says so.  The caller owns every buffer.
+ *
+ * Each declaration cites the interface of the reference implementation
+ * (huweim/nvfp_kernel, paths relative to that project) that it replaces.
+ */
+#ifndef NVFP_B200_H_
+#define NVFP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  NVFP_OK = 0,
+  NVFP_ERR_INVALID_ARGUMENT = 1, /* shape / dtype / alignment rejected on the host      */
+  NVFP_ERR_CUDA = 2,             /* a CUDA runtime or driver call failed                 */
+  NVFP_ERR_DEVICE_TIMEOUT = 3,   /* a bounded wait inside a kernel expired (see below)   */
+  NVFP_ERR_UNSUPPORTED = 4       /* the current device is not sm_100                     */
+} nvfp_status_t;
+
+/* element types of 16-bit inputs / outputs */
+#define NVFP_DTYPE_F16 0
+#define NVFP_DTYPE_BF16 1
+#define NVFP_DTYPE_F32 2 /* GEMM output only: unrounded partial sums for K-split layers */
+
+/* MXFP4 scale rounding: exponent of amax/6 rounded up (no element saturates), or
+ * truncated (the reference's disabled e8m0 branch, kernel/nvfp4_utils.cuh:196-202). */
+#define NVFP_MX_ROUND_CEIL 0
+#define NVFP_MX_ROUND_FLOOR 1
+
+/* Message describing the last failure on the calling thread ("" if none). */
+const char* nvfp_last_error(void);
+
+/* Library / ABI version (major*1000 + minor). */
+int nvfp_version(void);
+
+/* Number of padded scale rows / columns for a [rows, k] operand:
+ *   rows_padded = round_up(rows, 128), cols_padded = round_up(k / block, 4)
+ * (nvfp/_ops_real.py:48-54 and kernel/nvfp4_scaled_mm_sm120_kernels.cu:254-259). */
+int64_t nvfp_sf_rows_padded(int64_t rows);
+int64_t nvfp_sf_cols_padded(int64_t k, int block);
+
+/*
+ * NVFP4 quantizer.  Replaces scaled_fp4_quant_sm1xxa (kernel/nvfp4_quant.h:4-7,
+ * kernel/nvfp4_quant_kernels.cu:69-99) and its kernel cvt_fp16_to_fp4
+ * (kernel/nvfp4_utils.cuh:245-280); results are bit-identical to it.
+ *
+ *   in            [m, n] fp16 / bf16, row stride in_row_stride elements (>= n, multiple of 8),
+ *                 base 16-byte aligned, n % 16 == 0
+ *   global_scale  device pointer to one fp32 (NULL = 1.0f, kernel/nvfp4_utils.cuh:258)
+ *   out_fp4       [m, n/2] bytes, element 2j in the low nibble of byte j
+ *   out_sf        round_up(m,128) x round_up(n/16,4) ue4m3 bytes in the swizzled
+ *                 [mTile][kTile][32][4][4] layout (kernel/nvfp4_utils.cuh:126-153).
+ *                 Unlike the reference, padding bytes are written (as 0).
+ */
+int nvfp_scaled_fp4_quant(void* out_fp4, void* out_sf, const void* in, const float* global_scale,
+                          int64_t m, int64_t n, int64_t in_row_stride, int in_dtype, void* stream);
+
+/*
+ * MXFP4 quantizer: 32-element blocks, ue8m0 scales in the same swizzled layout
+ * (round_up(m,128) x round_up(n/32,4) bytes), no global scale.  n % 32 == 0.
+ * The reference has no reachable counterpart; the closest code is the UE8M0_SF
+ * template branch at kernel/nvfp4_utils.cuh:196-202 (16-element blocks, disabled at
+ * kernel/nvfp4_quant_kernels.cu:90-91).
+ */
+int nvfp_mxfp4_quant(void* out_fp4, void* out_sf, const void* in, int64_t m, int64_t n,
+                     int64_t in_row_stride, int in_dtype, int rounding, void* stream);
+
+/*
+ * Block-scaled FP4 GEMM  D[m,n] = alpha * sum_k (A*sfa)[m,k] * (B*sfb)[n,k], fp32
+ * accumulation, fp16 / bf16 output.  Replaces cutlass_scaled_fp4_mm
+ * (kernel/nvfp4_scaled_mm_entry.h:4-7, kernel/nvfp4_scaled_mm_entry.cu:23-36) and the
+ * CUTLASS instantiation behind it (kernel/nvfp4_scaled_mm_sm120_kernels.cu:72-294),
+ * with the same argument checks: k % 32 == 0, n % 32 == 0, contiguous operands.
+ *
+ *   a    [m, k/2] packed e2m1, b [n, k/2] packed e2m1 (weights are [N, K], K-major)
+ *   sfa  round_up(m,128) x round_up(k/16,4) ue4m3, swizzled; sfb likewise for n.
+ *        Scale bytes of K-blocks beyond k must be finite (the quantizers here write 0).
+ *   alpha device pointer to one fp32, read by the kernel's epilogue
+ *   d    [m, n] out_dtype (fp16 / bf16 as in the reference, or fp32), row-major,
+ *        16-byte aligned
+ */
+int nvfp_scaled_fp4_mm(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+                       const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype,
+                       void* stream);
+
+/* Same for MXFP4 operands: 32-element blocks, ue8m0 scales
+ * (round_up(rows,128) x round_up(k/32,4)), k % 64 == 0.  alpha may be NULL (= 1).
+ * No counterpart in the reference (see nvfp_mxfp4_quant). */
+int nvfp_mxfp4_mm(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+                  const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, void* stream);
+
+/*
+ * y[i] = rcp.approx.ftz.f32(x[i]).  Replaces reciprocal_approximate_ftz_tensor
+ * (kernel/reciprocal_kernels.h:4-5, kernel/reciprocal_kernels.cu:91-121); fp32 only,
+ * the one dtype reachable through the reference's Python wrapper (nvfp/ops.py:87-92).
+ */
+int nvfp_reciprocal_approximate_ftz(float* out, const float* in, int64_t count, void* stream);
+
+/*
+ * Per-tensor global scale  gs = (448 * 6) / max|x|  as one fp32 on the device.
+ * Replaces the torch sequence abs().max() -> 2688/amax of speed_test.py:40-41,46-47
+ * and nvfp/pseudo_quant.py:94-96 with two kernels and no temporary.
+ *   amax_bits  device scratch, one uint32; the call resets it on the stream first.
+ *   gs_out     device, one fp32; amax == 0 gives gs = 2688 (amax treated as 1,
+ *              as in test_refactor.py:21-25).
+ */
+int nvfp_global_scale(float* gs_out, uint32_t* amax_bits, const void* in, int64_t m, int64_t n,
+                      int64_t in_row_stride, int in_dtype, void* stream);
+
+/* alpha_out[0] = 1 / (gs_a[0] * gs_b[0]) in fp32 on the device (speed_test.py:49). */
+int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const float* gs_b, void* stream);
+
+/*
+ * Kernels here never spin without a limit: a wait on an mbarrier that does not
+ * complete within about two seconds makes the kernel record a code in a per-device
+ * status word and return.  This call synchronises the current device, reads and
+ * clears that word: *status_out == 0 means no kernel gave up since the last call.
+ * Returns NVFP_ERR_DEVICE_TIMEOUT when the word was non-zero.
+ */
+int nvfp_device_status(uint32_t* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP_B200_H_ */

@@ -1,0 +1,27 @@
+"""B200-native NVFP4 / MXFP4 quantize-and-GEMM: drop-in for the `nvfp` package of
+huweim/nvfp_kernel on its real-kernel path (nvfp/__init__.py:1-27 there)."""
+from .ops import (
+    alpha_from_scales,
+    cutlass_scaled_fp4_mm,
+    device_status,
+    get_active_backend,
+    global_scale,
+    mxfp4_scaled_mm,
+    reciprocal_approximate_ftz_tensor,
+    scaled_fp4_quant,
+    scaled_mxfp4_quant,
+)
+from .linear import QuantLinear
+
+__all__ = [
+    "scaled_fp4_quant",
+    "cutlass_scaled_fp4_mm",
+    "get_active_backend",
+    "reciprocal_approximate_ftz_tensor",
+    "scaled_mxfp4_quant",
+    "mxfp4_scaled_mm",
+    "global_scale",
+    "alpha_from_scales",
+    "device_status",
+    "QuantLinear",
+]

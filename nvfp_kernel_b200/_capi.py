@@ -1,0 +1,82 @@
+"""ctypes view of libnvfp_b200.so (declarations: include/nvfp_b200.h).
+
+Used by code that wants the C ABI without torch types in the way (tests, the smoke
+test, the benchmark).  There is no fallback: a missing library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libnvfp_b200.so")
+
+NVFP_OK = 0
+NVFP_ERR_INVALID_ARGUMENT = 1
+NVFP_ERR_CUDA = 2
+NVFP_ERR_DEVICE_TIMEOUT = 3
+NVFP_ERR_UNSUPPORTED = 4
+NVFP_DTYPE_F16 = 0
+NVFP_DTYPE_BF16 = 1
+NVFP_DTYPE_F32 = 2
+NVFP_MX_ROUND_CEIL = 0
+NVFP_MX_ROUND_FLOOR = 1
+
+_vp, _i64, _int = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+
+# name -> (restype, argtypes); every symbol declared in include/nvfp_b200.h
+PROTOTYPES = {
+    "nvfp_last_error": (ctypes.c_char_p, []),
+    "nvfp_version": (_int, []),
+    "nvfp_sf_rows_padded": (_i64, [_i64]),
+    "nvfp_sf_cols_padded": (_i64, [_i64, _int]),
+    "nvfp_scaled_fp4_quant": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "nvfp_mxfp4_quant": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "nvfp_scaled_fp4_mm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "nvfp_mxfp4_mm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "nvfp_reciprocal_approximate_ftz": (_int, [_vp, _vp, _i64, _vp]),
+    "nvfp_global_scale": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "nvfp_alpha_from_scales": (_int, [_vp, _vp, _vp, _vp]),
+    "nvfp_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32)]),
+}
+
+_lib = None
+
+
+class NvfpError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libnvfp_b200 status {code}: {message}")
+        self.code = code
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library and attaches prototypes; raises if it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build it with `python -m nvfp_kernel_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        lib = ctypes.CDLL(_LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != NVFP_OK:
+        raise NvfpError(rc, load().nvfp_last_error().decode())
+
+
+def device_status() -> int:
+    """Synchronises the current device and returns (and clears) its status word."""
+    word = ctypes.c_uint32(0)
+    rc = load().nvfp_device_status(ctypes.byref(word))
+    if rc not in (NVFP_OK, NVFP_ERR_DEVICE_TIMEOUT):
+        check(rc)
+    return word.value

@@ -1,0 +1,146 @@
+"""Wrappers over the `scaled_fp4_ops` extension: input checks and output allocation.
+
+Mirror of the reference's nvfp/_ops_real.py:25-98 (same asserts, shapes and dtypes of
+the results) plus the MXFP4 and helper entry points.  The extension is looked up by
+module name like the reference does (nvfp/_ops_real.py:8), then in this package's own
+directory where the in-tree build puts it.
+"""
+from __future__ import annotations
+
+import importlib
+import importlib.util
+import os
+import sys
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+
+
+def _load_scaled_fp4_ops(required_symbols: tuple[str, ...]):
+    module = sys.modules.get("scaled_fp4_ops")
+    if module is None:
+        try:
+            module = importlib.import_module("scaled_fp4_ops")
+        except ImportError:
+            module = None
+            for name in sorted(os.listdir(_PKG_DIR)):
+                if name.startswith("scaled_fp4_ops") and name.endswith(".so"):
+                    spec = importlib.util.spec_from_file_location("scaled_fp4_ops", os.path.join(_PKG_DIR, name))
+                    module = importlib.util.module_from_spec(spec)
+                    spec.loader.exec_module(module)
+                    sys.modules["scaled_fp4_ops"] = module
+                    break
+            if module is None:
+                raise RuntimeError(
+                    "scaled_fp4_ops extension is not available. "
+                    "Build it with `python -m nvfp_kernel_b200.build` (sm_100a; no fallback exists)."
+                ) from None
+    missing = [name for name in required_symbols if not hasattr(module, name)]
+    if missing:
+        raise RuntimeError(
+            "scaled_fp4_ops is missing required real-kernel symbols: "
+            f"{', '.join(missing)}. Rebuild with `python -m nvfp_kernel_b200.build --force`.")
+    return module
+
+
+def _round_up(x: int, y: int) -> int:
+    return (x + y - 1) // y * y
+
+
+def _quant_common(input: torch.Tensor, block_size: int):
+    assert input.is_cuda, "input must be a CUDA tensor"
+    assert input.ndim >= 1, f"input.ndim needs to be >= 1, but got {input.ndim}."
+    other_dims = 1 if input.ndim == 1 else -1
+    input = input.reshape(other_dims, input.shape[-1])
+    m, n = input.shape
+    assert n % block_size == 0, f"last dim has to be multiple of {block_size}, but got {n}."
+    assert input.dtype in (torch.float16, torch.bfloat16), \
+        f"input.dtype needs to be fp16 or bf16 but got {input.dtype}."
+    if input.stride(-1) != 1 or (m > 1 and input.stride(0) % 8 != 0) or input.data_ptr() % 16 != 0:
+        input = input.contiguous()
+    output = torch.empty((m, n // 2), device=input.device, dtype=torch.uint8)
+    rounded_m = _round_up(m, 128)
+    rounded_n = _round_up(n // block_size, 4)
+    output_scale = torch.empty((rounded_m, rounded_n // 4), device=input.device, dtype=torch.int32)
+    return input, output, output_scale
+
+
+def scaled_fp4_quant(input: torch.Tensor, input_global_scale: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16/fp16 [..., n] -> (uint8 [m, n/2], float8_e4m3fn [round_up(m,128), round_up(n/16,4)])."""
+    assert input_global_scale.is_cuda, "input_global_scale must be a CUDA tensor"
+    assert input_global_scale.dtype == torch.float, \
+        f"input_global_scale.dtype needs to be fp32 but got {input_global_scale.dtype}."
+    input, output, output_scale = _quant_common(input, 16)
+    ext = _load_scaled_fp4_ops(("scaled_fp4_quant_sm1xxa",))
+    ext.scaled_fp4_quant_sm1xxa(output, input, output_scale, input_global_scale)
+    return output, output_scale.view(torch.float8_e4m3fn)
+
+
+def scaled_mxfp4_quant(input: torch.Tensor, rounding: str = "rceil") -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16/fp16 [..., n] -> (uint8 [m, n/2], float8_e8m0fnu [round_up(m,128), round_up(n/32,4)])."""
+    assert rounding in ("rceil", "floor"), f"rounding must be 'rceil' or 'floor', got {rounding!r}"
+    input, output, output_scale = _quant_common(input, 32)
+    ext = _load_scaled_fp4_ops(("scaled_mxfp4_quant",))
+    ext.scaled_mxfp4_quant(output, input, output_scale, 0 if rounding == "rceil" else 1)
+    return output, output_scale.view(torch.float8_e8m0fnu)
+
+
+def _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, sf_dtype):
+    assert a.is_cuda, "a must be a CUDA tensor"
+    assert b.is_cuda, "b must be a CUDA tensor"
+    assert block_scale_a.is_cuda, "block_scale_a must be a CUDA tensor"
+    assert block_scale_b.is_cuda, "block_scale_b must be a CUDA tensor"
+    assert a.ndim == 2 and b.ndim == 2
+    assert a.dtype in (torch.uint8,), f"a.dtype needs to be uint8 but got {a.dtype}"
+    assert b.dtype in (torch.uint8,), f"b.dtype needs to be uint8 but got {b.dtype}"
+    assert block_scale_a.dtype in (sf_dtype,), f"block_scale_a.dtype needs to be {sf_dtype} but got {block_scale_a.dtype}"
+    assert block_scale_b.dtype in (sf_dtype,), f"block_scale_b.dtype needs to be {sf_dtype} but got {block_scale_b.dtype}"
+    if alpha is not None:
+        assert alpha.is_cuda, "alpha must be a CUDA tensor"
+        assert alpha.dtype == torch.float, f"alpha.dtype needs to be fp32 but got {alpha.dtype}"
+    assert out_dtype in (torch.float16, torch.bfloat16), f"out_dtype needs to be fp16 or bf16 but got {out_dtype}"
+
+
+def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype) -> torch.Tensor:
+    """out[m,n] = alpha * (a*sfa) @ (b*sfb)^T.  The name is the reference's; the kernel is
+    the hand-written tcgen05 one (no CUTLASS)."""
+    assert alpha is not None, "alpha must be a CUDA tensor"
+    _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, torch.float8_e4m3fn)
+    m, n = a.shape[0], b.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    ext = _load_scaled_fp4_ops(("cutlass_scaled_fp4_mm",))
+    ext.cutlass_scaled_fp4_mm(out, a, b, block_scale_a, block_scale_b, alpha)
+    return out
+
+
+def mxfp4_scaled_mm(a, b, block_scale_a, block_scale_b, out_dtype, alpha=None) -> torch.Tensor:
+    _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, torch.float8_e8m0fnu)
+    m, n = a.shape[0], b.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    ext = _load_scaled_fp4_ops(("mxfp4_scaled_mm",))
+    ext.mxfp4_scaled_mm(out, a, b, block_scale_a, block_scale_b, alpha)
+    return out
+
+
+def global_scale(input: torch.Tensor, scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 [1] on the device: (448*6)/max|input|, without materialising |input|."""
+    assert input.is_cuda, "input must be a CUDA tensor"
+    assert input.dtype in (torch.float16, torch.bfloat16), f"input.dtype needs to be fp16 or bf16 but got {input.dtype}."
+    x = input.reshape(1 if input.ndim == 1 else -1, input.shape[-1])
+    assert x.shape[-1] % 8 == 0, f"last dim has to be multiple of 8, but got {x.shape[-1]}."
+    if x.stride(-1) != 1 or (x.shape[0] > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    out = torch.empty(1, dtype=torch.float32, device=input.device)
+    if scratch is None:
+        scratch = torch.empty(1, dtype=torch.int32, device=input.device)
+    ext = _load_scaled_fp4_ops(("global_scale",))
+    ext.global_scale(out, scratch, x)
+    return out
+
+
+def alpha_from_scales(gs_a: torch.Tensor, gs_b: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(1, dtype=torch.float32, device=gs_a.device)
+    ext = _load_scaled_fp4_ops(("alpha_from_scales",))
+    ext.alpha_from_scales(out, gs_a, gs_b)
+    return out

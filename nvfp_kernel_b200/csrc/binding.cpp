@@ -1,0 +1,189 @@
+// Torch extension module `scaled_fp4_ops`: the three entry points the reference's
+// binding.cpp:10-17 exports (same names, argument order and checks), plus the MXFP4 and
+// helper entry points, each a thin wrapper over the C ABI of libnvfp_b200.so.  No device
+// code lives here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "../../include/nvfp_b200.h"
+
+namespace {
+
+void* current_stream(const torch::Tensor& t) {
+  return static_cast<void*>(at::cuda::getCurrentCUDAStream(t.get_device()).stream());
+}
+
+void check_status(int rc) {
+  if (rc == NVFP_OK) return;
+  if (rc == NVFP_ERR_UNSUPPORTED) TORCH_CHECK_NOT_IMPLEMENTED(false, nvfp_last_error());
+  TORCH_CHECK(false, nvfp_last_error());
+}
+
+int dtype_code(const torch::Tensor& t, const char* what) {
+  if (t.scalar_type() == at::ScalarType::Half) return NVFP_DTYPE_F16;
+  if (t.scalar_type() == at::ScalarType::BFloat16) return NVFP_DTYPE_BF16;
+  TORCH_CHECK(false, what);
+  return -1;
+}
+
+#define CHECK_OPERAND(x, st, name)                                      \
+  TORCH_CHECK((x).is_cuda(), name, " must be a CUDA tensor");           \
+  TORCH_CHECK((x).is_contiguous(), name, " must be contiguous");        \
+  TORCH_CHECK((x).scalar_type() == (st), "Inconsistency of Tensor type: ", name)
+
+int64_t round_up(int64_t x, int64_t y) { return (x + y - 1) / y * y; }
+
+// kernel/nvfp4_quant_kernels.cu:69-99 of the reference.
+void scaled_fp4_quant_sm1xxa(torch::Tensor const& output, torch::Tensor const& input,
+                             torch::Tensor const& output_sf, torch::Tensor const& input_sf) {
+  TORCH_CHECK(input.dim() == 2, "input must be a matrix");
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(n % 16 == 0, "The N dimension must be multiple of 16.");
+  const int dt = dtype_code(input, "Unsupported input data type for quantize_to_fp4.");
+  TORCH_CHECK(input.is_cuda() && output.is_cuda() && output_sf.is_cuda() && input_sf.is_cuda(),
+              "all tensors must be CUDA tensors");
+  TORCH_CHECK(input.stride(1) == 1, "input rows must be dense");
+  TORCH_CHECK(output.is_contiguous() && output_sf.is_contiguous(), "outputs must be contiguous");
+  TORCH_CHECK(output.numel() * output.element_size() >= m * n / 2, "output too small");
+  TORCH_CHECK(output_sf.numel() * output_sf.element_size() >= round_up(m, 128) * round_up(n / 16, 4),
+              "output_sf too small");
+  TORCH_CHECK(input_sf.scalar_type() == at::ScalarType::Float, "input_sf must be fp32");
+  const at::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_status(nvfp_scaled_fp4_quant(output.data_ptr(), output_sf.data_ptr(), input.data_ptr(),
+                                     static_cast<const float*>(input_sf.data_ptr()), m, n,
+                                     m > 1 ? input.stride(0) : n, dt, current_stream(input)));
+}
+
+void scaled_mxfp4_quant(torch::Tensor const& output, torch::Tensor const& input,
+                        torch::Tensor const& output_sf, int64_t rounding) {
+  TORCH_CHECK(input.dim() == 2, "input must be a matrix");
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(n % 32 == 0, "The N dimension must be multiple of 32.");
+  const int dt = dtype_code(input, "Unsupported input data type for quantize_to_fp4.");
+  TORCH_CHECK(input.is_cuda() && output.is_cuda() && output_sf.is_cuda(), "all tensors must be CUDA tensors");
+  TORCH_CHECK(input.stride(1) == 1, "input rows must be dense");
+  TORCH_CHECK(output.is_contiguous() && output_sf.is_contiguous(), "outputs must be contiguous");
+  TORCH_CHECK(output.numel() * output.element_size() >= m * n / 2, "output too small");
+  TORCH_CHECK(output_sf.numel() * output_sf.element_size() >= round_up(m, 128) * round_up(n / 32, 4),
+              "output_sf too small");
+  const at::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_status(nvfp_mxfp4_quant(output.data_ptr(), output_sf.data_ptr(), input.data_ptr(), m, n,
+                                m > 1 ? input.stride(0) : n, dt, (int)rounding, current_stream(input)));
+}
+
+// Argument checks of kernel/nvfp4_scaled_mm_sm120_kernels.cu:222-273 of the reference.
+void scaled_mm_impl(torch::Tensor& D, torch::Tensor const& A, torch::Tensor const& B,
+                    torch::Tensor const& A_sf, torch::Tensor const& B_sf,
+                    c10::optional<torch::Tensor> const& alpha, bool mx) {
+  const auto sf_dtype = mx ? at::ScalarType::Float8_e8m0fnu : at::ScalarType::Float8_e4m3fn;
+  CHECK_OPERAND(A, at::ScalarType::Byte, "a");
+  CHECK_OPERAND(B, at::ScalarType::Byte, "b");
+  CHECK_OPERAND(A_sf, sf_dtype, "scale_a");
+  CHECK_OPERAND(B_sf, sf_dtype, "scale_b");
+  if (alpha.has_value()) { CHECK_OPERAND(*alpha, at::ScalarType::Float, "alpha"); }
+  TORCH_CHECK(mx || alpha.has_value(), "alpha is required");
+  TORCH_CHECK(D.is_cuda() && D.is_contiguous(), "out must be a contiguous CUDA tensor");
+  TORCH_CHECK(A.dim() == 2, "a must be a matrix");
+  TORCH_CHECK(B.dim() == 2, "b must be a matrix");
+  TORCH_CHECK(A.sizes()[1] == B.sizes()[1], "a and b shapes cannot be multiplied (", A.sizes()[0], "x",
+              A.sizes()[1], " and ", B.sizes()[0], "x", B.sizes()[1], ")");
+  const int64_t m = A.sizes()[0], n = B.sizes()[0], k = A.sizes()[1] * 2;
+  const int64_t alignment = mx ? 64 : 32, block = mx ? 32 : 16;
+  TORCH_CHECK(k % alignment == 0, "Expected k to be divisible by ", alignment, ", but got a shape: (",
+              A.sizes()[0], "x", A.sizes()[1], "), k: ", k, ".");
+  TORCH_CHECK(n % 32 == 0, "Expected n to be divisible by 32, but got b shape: (", B.sizes()[0], "x",
+              B.sizes()[1], ").");
+  const int64_t rounded_m = round_up(m, 128), rounded_n = round_up(n, 128), rounded_k = round_up(k / block, 4);
+  TORCH_CHECK(A_sf.dim() == 2, "scale_a must be a matrix");
+  TORCH_CHECK(B_sf.dim() == 2, "scale_b must be a matrix");
+  TORCH_CHECK(A_sf.sizes()[1] == B_sf.sizes()[1], "scale_a and scale_b shapes cannot be multiplied (",
+              A_sf.sizes()[0], "x", A_sf.sizes()[1], " and ", B_sf.sizes()[0], "x", B_sf.sizes()[1], ")");
+  TORCH_CHECK(A_sf.sizes()[0] == rounded_m && A_sf.sizes()[1] == rounded_k,
+              "scale_a must be padded and swizzled to a shape (", rounded_m, "x", rounded_k,
+              "), but got a shape (", A_sf.sizes()[0], "x", A_sf.sizes()[1], ")");
+  TORCH_CHECK(B_sf.sizes()[0] == rounded_n && B_sf.sizes()[1] == rounded_k,
+              "scale_b must be padded and swizzled to a shape (", rounded_n, "x", rounded_k,
+              "), but got a shape (", B_sf.sizes()[0], "x", B_sf.sizes()[1], ")");
+  TORCH_CHECK(D.dim() == 2 && D.sizes()[0] == m && D.sizes()[1] == n, "out must have shape (", m, "x", n, ")");
+  int dt;
+  if (D.scalar_type() == at::ScalarType::BFloat16) dt = NVFP_DTYPE_BF16;
+  else if (D.scalar_type() == at::ScalarType::Half) dt = NVFP_DTYPE_F16;
+  else if (D.scalar_type() == at::ScalarType::Float) dt = NVFP_DTYPE_F32;
+  else TORCH_CHECK(false, "Unsupported output data type of nvfp4 mm (", D.scalar_type(), ")");
+  const at::cuda::OptionalCUDAGuard guard(device_of(A));
+  const float* alpha_ptr = alpha.has_value() ? static_cast<const float*>(alpha->data_ptr()) : nullptr;
+  auto fn = mx ? nvfp_mxfp4_mm : nvfp_scaled_fp4_mm;
+  check_status(fn(D.data_ptr(), A.data_ptr(), B.data_ptr(), A_sf.data_ptr(), B_sf.data_ptr(), alpha_ptr,
+                  m, n, k, dt, current_stream(A)));
+}
+
+void cutlass_scaled_fp4_mm(torch::Tensor& D, torch::Tensor const& A, torch::Tensor const& B,
+                           torch::Tensor const& A_sf, torch::Tensor const& B_sf,
+                           torch::Tensor const& alpha) {
+  scaled_mm_impl(D, A, B, A_sf, B_sf, alpha, false);
+}
+
+void mxfp4_scaled_mm(torch::Tensor& D, torch::Tensor const& A, torch::Tensor const& B,
+                     torch::Tensor const& A_sf, torch::Tensor const& B_sf,
+                     c10::optional<torch::Tensor> const& alpha) {
+  scaled_mm_impl(D, A, B, A_sf, B_sf, alpha, true);
+}
+
+// kernel/reciprocal_kernels.cu:91-121 of the reference (fp32, the only reachable dtype).
+void reciprocal_approximate_ftz_tensor(torch::Tensor const& input, torch::Tensor& output) {
+  TORCH_CHECK(input.scalar_type() == at::ScalarType::Float, "Input tensor must be float");
+  TORCH_CHECK(output.scalar_type() == input.scalar_type(),
+              "Output tensor must have the same dtype as input tensor");
+  TORCH_CHECK(input.sizes() == output.sizes(), "Input and output tensors must have the same shape");
+  TORCH_CHECK(input.is_cuda() && output.is_cuda(), "Input and output tensors must be on CUDA device");
+  TORCH_CHECK(input.is_contiguous() && output.is_contiguous(), "tensors must be contiguous");
+  const at::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_status(nvfp_reciprocal_approximate_ftz(static_cast<float*>(output.data_ptr()),
+                                               static_cast<const float*>(input.data_ptr()),
+                                               input.numel(), current_stream(input)));
+}
+
+void global_scale(torch::Tensor& gs_out, torch::Tensor& scratch, torch::Tensor const& input) {
+  TORCH_CHECK(input.dim() == 2 && input.stride(1) == 1, "input must be a matrix with dense rows");
+  TORCH_CHECK(gs_out.is_cuda() && scratch.is_cuda() && input.is_cuda(), "all tensors must be CUDA tensors");
+  TORCH_CHECK(gs_out.scalar_type() == at::ScalarType::Float && gs_out.numel() >= 1, "gs_out must be fp32");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 4, "scratch must hold 4 bytes");
+  const int dt = dtype_code(input, "Unsupported input data type for global_scale.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_status(nvfp_global_scale(static_cast<float*>(gs_out.data_ptr()),
+                                 static_cast<uint32_t*>(scratch.data_ptr()), input.data_ptr(),
+                                 input.size(0), input.size(1),
+                                 input.size(0) > 1 ? input.stride(0) : input.size(1), dt,
+                                 current_stream(input)));
+}
+
+void alpha_from_scales(torch::Tensor& alpha_out, torch::Tensor const& gs_a, torch::Tensor const& gs_b) {
+  TORCH_CHECK(alpha_out.is_cuda() && gs_a.is_cuda() && gs_b.is_cuda(), "all tensors must be CUDA tensors");
+  TORCH_CHECK(alpha_out.scalar_type() == at::ScalarType::Float && gs_a.scalar_type() == at::ScalarType::Float &&
+                  gs_b.scalar_type() == at::ScalarType::Float, "all tensors must be fp32");
+  const at::cuda::OptionalCUDAGuard guard(device_of(alpha_out));
+  check_status(nvfp_alpha_from_scales(static_cast<float*>(alpha_out.data_ptr()),
+                                      static_cast<const float*>(gs_a.data_ptr()),
+                                      static_cast<const float*>(gs_b.data_ptr()), current_stream(alpha_out)));
+}
+
+int64_t device_status() {
+  uint32_t word = 0;
+  int rc = nvfp_device_status(&word);
+  if (rc != NVFP_OK && rc != NVFP_ERR_DEVICE_TIMEOUT) check_status(rc);
+  return word;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("scaled_fp4_quant_sm1xxa", &scaled_fp4_quant_sm1xxa);
+  m.def("cutlass_scaled_fp4_mm", &cutlass_scaled_fp4_mm);
+  m.def("reciprocal_approximate_ftz_tensor", &reciprocal_approximate_ftz_tensor);
+  m.def("scaled_mxfp4_quant", &scaled_mxfp4_quant);
+  m.def("mxfp4_scaled_mm", &mxfp4_scaled_mm);
+  m.def("global_scale", &global_scale);
+  m.def("alpha_from_scales", &alpha_from_scales);
+  m.def("device_status", &device_status);
+}

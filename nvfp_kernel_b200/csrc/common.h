@@ -1,0 +1,46 @@
+// Host-side helpers shared by the translation units of libnvfp_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/nvfp_b200.h"
+
+namespace nvfp {
+
+// Stores a printf-style message for nvfp_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+
+// Properties of the current device, queried once per device (not once per process:
+// the reference caches the first device's attribute for all devices,
+// kernel/cuda_utils_kernels.cu:18-31).
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  int cc_minor = 0;
+};
+int current_device_info(DeviceInfo* out);
+
+inline int64_t round_up(int64_t x, int64_t y) { return (x + y - 1) / y * y; }
+inline int64_t ceil_div(int64_t x, int64_t y) { return (x + y - 1) / y; }
+
+// Device status word written by kernels whose bounded waits expire.
+uint32_t* device_status_word();
+
+}  // namespace nvfp
+
+#define NVFP_REQUIRE(cond, ...)                                             \
+  do {                                                                      \
+    if (!(cond)) return ::nvfp::fail(NVFP_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+#define NVFP_CUDA(call)                                                                   \
+  do {                                                                                    \
+    cudaError_t e_ = (call);                                                              \
+    if (e_ != cudaSuccess)                                                                \
+      return ::nvfp::fail(NVFP_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)

@@ -1,0 +1,440 @@
+// Block-scaled FP4 GEMM for sm_100a:  D[m,n] = alpha * sum_k (A*sfa)[m,k] * (B*sfb)[n,k].
+//
+// Replaces the reference's CUTLASS Sm120 instantiation
+// (kernel/nvfp4_scaled_mm_sm120_kernels.cu:72-188 of huweim/nvfp_kernel, warp-level
+// mma.sync for consumer Blackwell) with a hand-written tcgen05 kernel:
+//
+//   warp 0   producer: TMA loads of 128 x 256-element A and BN x 256-element B tiles
+//            (packed e2m1, 128-byte swizzle) plus bulk copies of the 512-byte scale
+//            chunks, into a ring of shared-memory stages guarded by mbarriers
+//   warp 1   issuer: copies the scale chunks shared -> tensor memory (tcgen05.cp) and
+//            issues one tcgen05.mma (M=128, N=BN, K=64) per 64 elements of K; fp32
+//            accumulators live in tensor memory; tcgen05.commit frees stages
+//   warps 2-5 epilogue: tcgen05.ld of the accumulator, * alpha, convert, store
+//
+// The kernel is persistent (one CTA per SM walks the output tiles).  Every wait is
+// bounded; on expiry the CTA records a code in the device status word and leaves
+// through the common exit, which also frees its tensor memory.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+
+namespace nvfp {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;            // rows of A per tile = M of one MMA
+constexpr int kStageK = 256;        // elements of K per pipeline stage (= one 128-byte swizzle row)
+constexpr int kStageKBytes = 128;
+constexpr int kMmaK = 64;           // K of one tcgen05.mma for 4-bit operands
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kSmemLimit = 232448;  // 227 KB
+
+// Status codes (one bit per waiting role) recorded when a bounded wait expires.
+constexpr uint32_t kErrProducer = 1u, kErrIssuer = 2u, kErrEpilogue = 4u;
+
+template <int BN, bool MX>
+struct Cfg {
+  static constexpr int kHalves = BN / 128;                       // 128-row scale tiles of B per tile
+  static constexpr int kChunksPerStage = MX ? 2 : 4;              // 512-byte scale chunks per operand tile per stage
+  static constexpr int kMmasPerChunk = MX ? 2 : 1;
+  static constexpr uint32_t kABytes = kBM * kStageKBytes;         // 16 KB
+  static constexpr uint32_t kBBytes = BN * kStageKBytes;
+  static constexpr uint32_t kSfaBytes = kChunksPerStage * 512;
+  static constexpr uint32_t kSfbBytes = kHalves * kChunksPerStage * 512;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kAccStages = BN == 128 ? 2 : 1;
+  static constexpr int kStages = (kSmemLimit - 2048) / kStageBytes > 8 ? 8 : (kSmemLimit - 2048) / kStageBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 2048;  // + alignment slack and barriers
+  // tensor-memory columns: accumulators first, then two slots of scale columns
+  static constexpr uint32_t kAccCols = BN;
+  static constexpr uint32_t kSfColBase = kAccStages * BN;
+  static constexpr uint32_t kSfaCols = 4 * kChunksPerStage;
+  static constexpr uint32_t kSfbCols = 4 * kChunksPerStage * kHalves;
+  static constexpr uint32_t kSfSlotCols = kSfaCols + kSfbCols;
+  static_assert(kSfColBase + 2 * kSfSlotCols <= kTmemCols, "tensor memory budget");
+  static_assert(kStages >= 2, "pipeline depth");
+};
+
+struct GemmParams {
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  const float* alpha;
+  void* d;
+  int m, n, k;
+  int tiles_m, tiles_n;
+  int sf_k_chunks;      // 512-byte chunks per 128-row scale tile along K
+  int sfb_row_tiles;    // 128-row scale tiles of B
+  uint32_t* status;
+};
+
+template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// 32 consecutive fp32 accumulators of one row * alpha -> 32 outputs, 16-byte stores.
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t (&r)[32], float alpha) {
+  uint4* dst = reinterpret_cast<uint4*>(dst_elems);
+  if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      uint4 o;
+      o.x = __float_as_uint(__uint_as_float(r[4 * v + 0]) * alpha);
+      o.y = __float_as_uint(__uint_as_float(r[4 * v + 1]) * alpha);
+      o.z = __float_as_uint(__uint_as_float(r[4 * v + 2]) * alpha);
+      o.w = __float_as_uint(__uint_as_float(r[4 * v + 3]) * alpha);
+      dst[v] = o;
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint4 o;
+      o.x = pack2<OutT>(__uint_as_float(r[8 * v + 0]) * alpha, __uint_as_float(r[8 * v + 1]) * alpha);
+      o.y = pack2<OutT>(__uint_as_float(r[8 * v + 2]) * alpha, __uint_as_float(r[8 * v + 3]) * alpha);
+      o.z = pack2<OutT>(__uint_as_float(r[8 * v + 4]) * alpha, __uint_as_float(r[8 * v + 5]) * alpha);
+      o.w = pack2<OutT>(__uint_as_float(r[8 * v + 6]) * alpha, __uint_as_float(r[8 * v + 7]) * alpha);
+      dst[v] = o;
+    }
+  }
+}
+
+template <int BN, bool MX, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmParams p) {
+  using C = Cfg<BN, MX>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle pattern of the operand tiles
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ctrl = smem + C::kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
+  // barrier indices
+  constexpr int kFull = 0, kEmpty = C::kStages, kAccFull = 2 * C::kStages,
+                kAccEmpty = kAccFull + C::kAccStages, kDrain = kAccEmpty + C::kAccStages,
+                kNumBars = kDrain + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* never_set = tmem_slot + 2;   // stays 0: lets the exit-path waits run to their limit
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(bar(kFull + i), 1);
+      mbar_init(bar(kEmpty + i), 1);
+    }
+    for (int i = 0; i < C::kAccStages; ++i) {
+      mbar_init(bar(kAccFull + i), 1);
+      mbar_init(bar(kAccEmpty + i), 4);   // one arrival per epilogue warp
+    }
+    mbar_init(bar(kDrain), 1);
+    *abort_flag = 0;
+    *never_set = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_stages = (p.k + kStageK - 1) / kStageK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer ---
+    if (elect_one()) {
+      uint32_t kc = 0;   // stage fills issued so far
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        const int halves = min(C::kHalves, p.sfb_row_tiles - tn * C::kHalves);
+        for (int ks = 0; ks < k_stages; ++ks, ++kc) {
+          const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
+          if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicOr(p.status, kErrProducer);
+            ok = false;
+            break;
+          }
+          const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
+          const uint32_t sf_bytes = (uint32_t)chunks * 512u;
+          const uint32_t st = smem_base + s * C::kStageBytes;
+          mbar_arrive_expect_tx(bar(kFull + s), C::kABytes + C::kBBytes + sf_bytes * (1 + halves));
+          tma_load_2d(st, &tmap_a, bar(kFull + s), ks * kStageKBytes, tm * kBM);
+          tma_load_2d(st + C::kABytes, &tmap_b, bar(kFull + s), ks * kStageKBytes, tn * BN);
+          const int64_t chunk0 = (int64_t)ks * C::kChunksPerStage;
+          bulk_load(st + C::kABytes + C::kBBytes,
+                    p.sfa + ((int64_t)tm * p.sf_k_chunks + chunk0) * 512, sf_bytes, bar(kFull + s));
+          for (int h = 0; h < halves; ++h)
+            bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + h * C::kChunksPerStage * 512,
+                      p.sfb + ((int64_t)(tn * C::kHalves + h) * p.sf_k_chunks + chunk0) * 512,
+                      sf_bytes, bar(kFull + s));
+        }
+      }
+      if (*abort_flag) {
+        // give the copies already issued a bounded chance to land before the CTA exits
+        for (uint32_t s = 0; s < (uint32_t)C::kStages; ++s) {
+          const uint32_t fills = (kc + C::kStages - 1 - s) / C::kStages;
+          if (fills) mbar_wait_bounded(bar(kFull + s), (fills - 1) & 1u, never_set, 200000000ull);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- issuer ---
+    if (elect_one()) {
+      uint32_t kc = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int tn = tile / p.tiles_m;
+        const int halves = min(C::kHalves, p.sfb_row_tiles - tn * C::kHalves);
+        const int as = it % C::kAccStages;
+        const uint32_t acc_ph = (uint32_t)(it / C::kAccStages) & 1u;
+        if (!mbar_wait_bounded(bar(kAccEmpty + as), acc_ph ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(p.status, kErrIssuer);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * C::kAccCols;
+        for (int ks = 0; ks < k_stages; ++ks, ++kc) {
+          const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
+          if (!mbar_wait_bounded(bar(kFull + s), ph, abort_flag)) {
+            *abort_flag = 1;
+            atomicOr(p.status, kErrIssuer);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
+          const int mmas = min(kStageK / kMmaK, (p.k - ks * kStageK + kMmaK - 1) / kMmaK);
+          const uint32_t st = smem_base + s * C::kStageBytes;
+          const uint32_t sf_slot = tmem_base + C::kSfColBase + (kc & 1u) * C::kSfSlotCols;
+          const uint32_t sfa_tmem = sf_slot, sfb_tmem = sf_slot + C::kSfaCols;
+          // scales: shared -> tensor memory, one 512-byte chunk (128 rows x 4 scales) per copy
+          for (int c = 0; c < chunks; ++c) {
+            tc_copy_sf_32x128b_warpx4(
+                sfa_tmem + 4 * c,
+                make_smem_desc(st + C::kABytes + C::kBBytes + c * 512, 0, 128, 0));
+            for (int h = 0; h < halves; ++h)
+              tc_copy_sf_32x128b_warpx4(
+                  sfb_tmem + 4 * (c * C::kHalves + h),
+                  make_smem_desc(st + C::kABytes + C::kBBytes + C::kSfaBytes +
+                                     (h * C::kChunksPerStage + c) * 512, 0, 128, 0));
+          }
+          const uint64_t a_desc = make_smem_desc(st, 16, 1024, 2);
+          const uint64_t b_desc = make_smem_desc(st + C::kABytes, 16, 1024, 2);
+          for (int j = 0; j < mmas; ++j) {
+            const uint32_t accumulate = (ks | j) != 0 ? 1u : 0u;
+            const uint64_t koff = (uint64_t)((j * (kMmaK / 2)) >> 4);   // 32 bytes of K per MMA
+            const int c = j / C::kMmasPerChunk;
+            if (MX) {
+              const uint32_t sf_id = (uint32_t)(j % C::kMmasPerChunk) * 2u;
+              tc_mma_mxf4(d_tmem, a_desc + koff, b_desc + koff,
+                          make_idesc_fp4_block_scaled(kBM, BN, true, sf_id, sf_id),
+                          sfa_tmem + 4 * c, sfb_tmem + 4 * c * C::kHalves, accumulate);
+            } else {
+              tc_mma_nvf4(d_tmem, a_desc + koff, b_desc + koff,
+                          make_idesc_fp4_block_scaled(kBM, BN, false),
+                          sfa_tmem + 4 * c, sfb_tmem + 4 * c * C::kHalves, accumulate);
+            }
+          }
+          tc_commit(bar(kEmpty + s));   // stage reusable once these MMAs have read it
+        }
+        if (ok) tc_commit(bar(kAccFull + as));
+      }
+      if (*abort_flag) {
+        tc_commit(bar(kDrain));
+        mbar_wait_bounded(bar(kDrain), 0, never_set, 200000000ull);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue ---
+    const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+    OutT* d = static_cast<OutT*>(p.d);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      const int as = it % C::kAccStages;
+      const uint32_t acc_ph = (uint32_t)(it / C::kAccStages) & 1u;
+      // warp-uniform decision: the tensor-memory loads below are .sync.aligned
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull + as), acc_ph, abort_flag))) {
+        *abort_flag = 1;
+        if (lane == 0) atomicOr(p.status, kErrEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tm * kBM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + as * C::kAccCols + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col = tn * BN + c * 32;
+        if (row < p.m && col < p.n) store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kAccEmpty + as));
+    }
+  }
+
+  // -------------------------------------------------------------- common exit ---
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------ host side ---
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// Row-major [rows, k/2] bytes of packed e2m1; box = 128 bytes of K x box_rows rows,
+// 128-byte swizzle; out-of-range rows / bytes read as zero.
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)(k / 2), (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)(k / 2)};
+  const cuuint32_t box[2] = {(cuuint32_t)kStageKBytes, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return NVFP_OK;
+}
+
+template <int BN, bool MX, typename OutT>
+int launch_config(const GemmParams& base, const void* a, const void* b, int sm_count,
+                  cudaStream_t stream) {
+  using C = Cfg<BN, MX>;
+  GemmParams p = base;
+  p.tiles_m = (int)ceil_div(p.m, kBM);
+  p.tiles_n = (int)ceil_div(p.n, BN);
+  CUtensorMap map_a, map_b;
+  if (int rc = make_operand_map(&map_a, a, p.m, p.k, kBM)) return rc;
+  if (int rc = make_operand_map(&map_b, b, p.n, p.k, BN)) return rc;
+  auto kernel = fp4_gemm_kernel<BN, MX, OutT>;
+  NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count);
+  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}
+
+template <bool MX>
+int scaled_mm(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+              const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream) {
+  constexpr int kBlock = MX ? 32 : 16;
+  constexpr int kAlign = MX ? 64 : 32;
+  NVFP_REQUIRE(m >= 0 && n >= 0 && k >= 0, "negative shape");
+  NVFP_REQUIRE(k % kAlign == 0, "Expected k to be divisible by %d, but got k: %lld.", kAlign, (long long)k);
+  NVFP_REQUIRE(n % 32 == 0, "Expected n to be divisible by 32, but got n: %lld.", (long long)n);
+  NVFP_REQUIRE(out_dtype == NVFP_DTYPE_F16 || out_dtype == NVFP_DTYPE_BF16 || out_dtype == NVFP_DTYPE_F32,
+               "Unsupported output data type of nvfp4 mm (dtype code %d)", out_dtype);
+  NVFP_REQUIRE(MX || alpha != nullptr, "alpha pointer is null");
+  NVFP_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "shape too large");
+  if (m == 0 || n == 0) return NVFP_OK;
+  NVFP_REQUIRE(k > 0, "k must be positive");
+  NVFP_REQUIRE(d && a && b && sfa && sfb, "null pointer");
+  NVFP_REQUIRE(((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                 reinterpret_cast<uintptr_t>(sfa) | reinterpret_cast<uintptr_t>(sfb) |
+                 reinterpret_cast<uintptr_t>(d)) & 15) == 0,
+               "operands, scales and output must be 16-byte aligned");
+  DeviceInfo info;
+  if (int rc = current_device_info(&info)) return rc;
+  if (info.cc_major != 10)
+    return fail(NVFP_ERR_UNSUPPORTED, "No compiled nvfp4 mm kernel for compute capability %d.%d (needs sm_100)",
+                info.cc_major, info.cc_minor);
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.alpha = alpha;
+  p.d = d;
+  p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.sf_k_chunks = (int)ceil_div(k / kBlock, 4);
+  p.sfb_row_tiles = (int)ceil_div(n, 128);
+  p.status = device_status_word();
+  NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
+  // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a
+  // single accumulator buffer; use them when there are enough tiles to fill the GPU.
+  const int64_t tiles256 = ceil_div(m, kBM) * ceil_div(n, 256);
+  const bool wide = n >= 256 && tiles256 >= info.sm_count;
+  if (wide) {
+    switch (out_dtype) {
+      case NVFP_DTYPE_BF16: return launch_config<256, MX, __nv_bfloat16>(p, a, b, info.sm_count, stream);
+      case NVFP_DTYPE_F16: return launch_config<256, MX, __half>(p, a, b, info.sm_count, stream);
+      default: return launch_config<256, MX, float>(p, a, b, info.sm_count, stream);
+    }
+  }
+  switch (out_dtype) {
+    case NVFP_DTYPE_BF16: return launch_config<128, MX, __nv_bfloat16>(p, a, b, info.sm_count, stream);
+    case NVFP_DTYPE_F16: return launch_config<128, MX, __half>(p, a, b, info.sm_count, stream);
+    default: return launch_config<128, MX, float>(p, a, b, info.sm_count, stream);
+  }
+}
+
+}  // namespace
+}  // namespace nvfp
+
+using namespace nvfp;
+
+extern "C" int nvfp_scaled_fp4_mm(void* d, const void* a, const void* b, const void* sfa,
+                                  const void* sfb, const float* alpha, int64_t m, int64_t n,
+                                  int64_t k, int out_dtype, void* stream) {
+  clear_error();
+  return scaled_mm<false>(d, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvfp_mxfp4_mm(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+                             const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype,
+                             void* stream) {
+  clear_error();
+  return scaled_mm<true>(d, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,344 @@
+// NVFP4 / MXFP4 quantizers, the approximate-reciprocal op and the global-scale
+// reduction for sm_100a.
+//
+// The arithmetic of the NVFP4 quantizer follows, step by step, the reference's
+// cvt_warp_fp16_to_fp4 (kernel/nvfp4_utils.cuh:166-242 of huweim/nvfp_kernel) so
+// that packed nibbles and scale bytes are bit-identical: block amax in the input
+// type, s = gs*(amax*rcp(6)), ue4m3 round-to-nearest-saturate, output scale
+// rcp(s'*rcp(gs)), flush-to-zero fp32 multiplies (the reference is built with
+// --use_fast_math, setup.py:45) and cvt.rn.satfinite.e2m1x2.f32.
+//
+// What is new is the data movement: one CTA owns a 128-row x (4 scale columns) tile,
+// which is exactly one 512-byte chunk of the swizzled [mTile][kTile][32][4][4] scale
+// layout (kernel/nvfp4_utils.cuh:126-153).  Scale bytes are staged in shared memory
+// and leave as 32 coalesced 16-byte stores instead of the reference's scattered
+// 1-byte stores; every thread keeps four 16-byte loads in flight; padding bytes of
+// the scale tensor are written as zero.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <algorithm>
+
+#include "common.h"
+
+namespace nvfp {
+namespace {
+
+__device__ __forceinline__ float rcp_approx_ftz(float a) {
+  float b;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(a));
+  return b;
+}
+
+__device__ __forceinline__ float mul_ftz(float a, float b) {
+  float c;
+  asm("mul.ftz.f32 %0, %1, %2;" : "=f"(c) : "f"(a), "f"(b));
+  return c;
+}
+
+// Eight fp32 -> eight e2m1 nibbles in one word; value i lands in bits [4i, 4i+4).
+// cvt.rn.satfinite.e2m1x2.f32 d, a, b puts a in the high and b in the low nibble.
+__device__ __forceinline__ uint32_t cvt_e2m1x8(float f0, float f1, float f2, float f3, float f4,
+                                               float f5, float f6, float f7) {
+  uint32_t r;
+  asm("{\n"
+      ".reg .b8 q0, q1, q2, q3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 q0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 q1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 q2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 q3, %8, %7;\n"
+      "mov.b32 %0, {q0, q1, q2, q3};\n"
+      "}"
+      : "=r"(r)
+      : "f"(f0), "f"(f1), "f"(f2), "f"(f3), "f"(f4), "f"(f5), "f"(f6), "f"(f7));
+  return r;
+}
+
+template <typename T> struct Vec2;
+template <> struct Vec2<__half> { using type = __half2; };
+template <> struct Vec2<__nv_bfloat16> { using type = __nv_bfloat162; };
+
+template <typename T> __device__ __forceinline__ float2 to_float2(typename Vec2<T>::type v);
+template <> __device__ __forceinline__ float2 to_float2<__half>(__half2 v) { return __half22float2(v); }
+template <> __device__ __forceinline__ float2 to_float2<__nv_bfloat16>(__nv_bfloat162 v) {
+  return __bfloat1622float2(v);
+}
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T> __device__ __forceinline__ typename Vec2<T>::type zero2();
+template <> __device__ __forceinline__ __half2 zero2<__half>() { return __float2half2_rn(0.0f); }
+template <> __device__ __forceinline__ __nv_bfloat162 zero2<__nv_bfloat16>() {
+  return __float2bfloat162_rn(0.0f);
+}
+
+template <typename T>
+union Pack8 {
+  uint4 raw;
+  typename Vec2<T>::type h2[4];
+};
+
+// |max| of the 8 values held by this thread, in the input type.
+template <typename T>
+__device__ __forceinline__ typename Vec2<T>::type local_absmax2(const Pack8<T>& v) {
+  auto mx = __habs2(v.h2[0]);
+#pragma unroll
+  for (int i = 1; i < 4; ++i) mx = __hmax2(mx, __habs2(v.h2[i]));
+  return mx;
+}
+
+// 8 values * scale -> 8 packed nibbles.
+template <typename T>
+__device__ __forceinline__ uint32_t scale_and_pack(const Pack8<T>& v, float scale) {
+  float2 f[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[i] = to_float2<T>(v.h2[i]);
+    f[i].x = mul_ftz(f[i].x, scale);
+    f[i].y = mul_ftz(f[i].y, scale);
+  }
+  return cvt_e2m1x8(f[0].x, f[0].y, f[1].x, f[1].y, f[2].x, f[2].y, f[3].x, f[3].y);
+}
+
+constexpr int kThreads = 256;
+constexpr int kTileRows = 128;
+
+// BLOCK = elements per scale (16: NVFP4 / ue4m3, 32: MXFP4 / ue8m0).
+template <typename T, int BLOCK>
+__global__ void __launch_bounds__(kThreads)
+quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __restrict__ gs_ptr,
+                 uint8_t* __restrict__ out, uint8_t* __restrict__ sf_out, int m, int n,
+                 int num_k_tiles, int mx_rounding) {
+  constexpr int kTileCols = 4 * BLOCK;              // one scale chunk = 4 scale columns
+  constexpr int kThreadsPerRow = kTileCols / 8;     // 8 elements (16 bytes) per thread
+  constexpr int kRowsPerPass = kThreads / kThreadsPerRow;
+  constexpr int kPasses = kTileRows / kRowsPerPass;
+  constexpr int kBatch = 4;                         // loads in flight per thread
+  constexpr int kThreadsPerBlock = BLOCK / 8;       // threads sharing one scale
+  static_assert(kPasses % kBatch == 0, "pass count");
+
+  __shared__ __align__(16) uint8_t sf_stage[512];
+
+  const int kt = blockIdx.x % num_k_tiles;
+  const int mt = blockIdx.x / num_k_tiles;
+  const int tid = threadIdx.x;
+  const int row_in_pass = tid / kThreadsPerRow;
+  const int col = kt * kTileCols + (tid % kThreadsPerRow) * 8;
+  const int sf_col_in_chunk = (tid % kThreadsPerRow) / kThreadsPerBlock;   // 0..3
+  const bool col_ok = col < n;
+
+  float gs = 1.0f, rcp_gs = 1.0f;
+  if (BLOCK == 16) {
+    gs = gs_ptr ? __ldg(gs_ptr) : 1.0f;
+    rcp_gs = rcp_approx_ftz(gs);
+  }
+  // NVFP4 uses the hardware reciprocal like the reference; MXFP4 (no reference to
+  // match) uses the correctly rounded constant so that a CPU restatement is exact.
+  const float rcp6 = BLOCK == 16 ? rcp_approx_ftz(6.0f) : __uint_as_float(0x3E2AAAABu);
+
+#pragma unroll
+  for (int b = 0; b < kPasses / kBatch; ++b) {
+    Pack8<T> v[kBatch];
+#pragma unroll
+    for (int p = 0; p < kBatch; ++p) {
+      const int row = mt * kTileRows + (b * kBatch + p) * kRowsPerPass + row_in_pass;
+      v[p].raw = make_uint4(0u, 0u, 0u, 0u);
+      if (col_ok && row < m)
+        v[p].raw = __ldg(reinterpret_cast<const uint4*>(in + (int64_t)row * in_stride + col));
+    }
+#pragma unroll
+    for (int p = 0; p < kBatch; ++p) {
+      const int row_in_tile = (b * kBatch + p) * kRowsPerPass + row_in_pass;
+      const int row = mt * kTileRows + row_in_tile;
+      auto mx2 = local_absmax2<T>(v[p]);
+#pragma unroll
+      for (int s = 1; s < kThreadsPerBlock; s <<= 1)
+        mx2 = __hmax2(__shfl_xor_sync(0xffffffffu, mx2, s), mx2);
+      const float amax = to_float<T>(__hmax(mx2.x, mx2.y));
+
+      uint8_t sf_byte;
+      float out_scale;
+      if (BLOCK == 16) {
+        const float sf_value = mul_ftz(gs, mul_ftz(amax, rcp6));
+        sf_byte = (uint8_t)__nv_cvt_float_to_fp8(sf_value, __NV_SATFINITE, __NV_E4M3);
+        const float sf_q = __half2float(__half(__nv_cvt_fp8_to_halfraw(sf_byte, __NV_E4M3)));
+        out_scale = sf_q != 0.0f ? rcp_approx_ftz(mul_ftz(sf_q, rcp_gs)) : 0.0f;
+      } else {
+        const float sf_value = mul_ftz(amax, rcp6);
+        const uint32_t bits = __float_as_uint(sf_value);
+        uint32_t e = (bits >> 23) & 0xffu;
+        if (mx_rounding == NVFP_MX_ROUND_CEIL && (bits & 0x7fffffu) != 0 && e < 254) e += 1;
+        e = min(e, 254u);
+        if (sf_value != sf_value) e = 255u;
+        sf_byte = (uint8_t)e;
+        out_scale = (e > 0 && e < 254) ? __uint_as_float((254u - e) << 23) : 0.0f;
+      }
+
+      const uint32_t packed = scale_and_pack<T>(v[p], out_scale);
+      if (col_ok && row < m)
+        *reinterpret_cast<uint32_t*>(out + (int64_t)row * (n / 2) + col / 2) = packed;
+      if (tid % kThreadsPerBlock == 0)
+        sf_stage[(row_in_tile % 32) * 16 + (row_in_tile / 32) * 4 + sf_col_in_chunk] = sf_byte;
+    }
+  }
+  __syncthreads();
+  if (tid < 32) {
+    uint4* dst = reinterpret_cast<uint4*>(sf_out + ((int64_t)mt * num_k_tiles + kt) * 512);
+    dst[tid] = reinterpret_cast<const uint4*>(sf_stage)[tid];
+  }
+}
+
+__global__ void rcp_kernel(float* __restrict__ out, const float* __restrict__ in, int64_t count) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = rcp_approx_ftz(in[i]);
+}
+
+// max |x| over the tensor -> atomicMax on the fp32 bit pattern (non-negative floats
+// order like unsigned integers).
+template <typename T>
+__global__ void __launch_bounds__(256)
+amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, uint32_t* amax_bits) {
+  const int64_t vec_per_row = n / 8;
+  const int64_t total = m * vec_per_row;
+  typename Vec2<T>::type mx2 = zero2<T>();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / vec_per_row, c = i % vec_per_row;
+    Pack8<T> v;
+    v.raw = __ldg(reinterpret_cast<const uint4*>(in + row * in_stride + c * 8));
+    mx2 = __hmax2(mx2, local_absmax2<T>(v));
+  }
+  float mx = to_float<T>(__hmax(mx2.x, mx2.y));
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+  __shared__ float warp_max[8];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float r = warp_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) r = fmaxf(r, warp_max[w]);
+    atomicMax(amax_bits, __float_as_uint(r));
+  }
+}
+
+__global__ void finish_global_scale_kernel(float* gs_out, const uint32_t* amax_bits) {
+  float amax = __uint_as_float(*amax_bits);
+  if (amax == 0.0f) amax = 1.0f;
+  *gs_out = __fdiv_rn(448.0f * 6.0f, amax);
+}
+
+__global__ void alpha_kernel(float* alpha_out, const float* gs_a, const float* gs_b) {
+  *alpha_out = __fdiv_rn(1.0f, __fmul_rn(*gs_a, *gs_b));
+}
+
+int check_16bit_input(const void* in, int64_t m, int64_t n, int64_t stride, int dtype, int block) {
+  NVFP_REQUIRE(in != nullptr, "input pointer is null");
+  NVFP_REQUIRE(m >= 0 && n >= 0, "negative shape (%lld x %lld)", (long long)m, (long long)n);
+  NVFP_REQUIRE(n % block == 0, "The N dimension must be multiple of %d (got %lld).", block, (long long)n);
+  NVFP_REQUIRE(dtype == NVFP_DTYPE_F16 || dtype == NVFP_DTYPE_BF16,
+               "Unsupported input data type for quantize_to_fp4 (dtype code %d).", dtype);
+  NVFP_REQUIRE(stride >= n && stride % 8 == 0,
+               "input row stride %lld must be >= n and a multiple of 8 elements", (long long)stride);
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(in) & 15) == 0, "input must be 16-byte aligned");
+  NVFP_REQUIRE(m < (1ll << 31) && n < (1ll << 31), "shape too large");
+  return NVFP_OK;
+}
+
+template <int BLOCK>
+int launch_quant(void* out_fp4, void* out_sf, const void* in, const float* gs, int64_t m, int64_t n,
+                 int64_t stride, int dtype, int rounding, cudaStream_t stream) {
+  if (int rc = check_16bit_input(in, m, n, stride, dtype, BLOCK)) return rc;
+  NVFP_REQUIRE(out_fp4 != nullptr && out_sf != nullptr, "output pointer is null");
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(out_fp4) & 3) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0,
+               "outputs must be aligned (fp4: 4 bytes, scales: 16 bytes)");
+  if (m == 0 || n == 0) return NVFP_OK;
+  const int64_t m_tiles = ceil_div(m, 128);
+  const int64_t k_tiles = ceil_div(n, 4 * BLOCK);
+  NVFP_REQUIRE(m_tiles * k_tiles < (1ll << 31), "too many tiles");
+  const dim3 grid((unsigned)(m_tiles * k_tiles));
+  if (dtype == NVFP_DTYPE_F16) {
+    quant_fp4_kernel<__half, BLOCK><<<grid, kThreads, 0, stream>>>(
+        static_cast<const __half*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
+        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)k_tiles, rounding);
+  } else {
+    quant_fp4_kernel<__nv_bfloat16, BLOCK><<<grid, kThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
+        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)k_tiles, rounding);
+  }
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}
+
+}  // namespace
+}  // namespace nvfp
+
+using namespace nvfp;
+
+extern "C" int nvfp_scaled_fp4_quant(void* out_fp4, void* out_sf, const void* in,
+                                     const float* global_scale, int64_t m, int64_t n,
+                                     int64_t in_row_stride, int in_dtype, void* stream) {
+  clear_error();
+  return launch_quant<16>(out_fp4, out_sf, in, global_scale, m, n, in_row_stride, in_dtype, 0,
+                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvfp_mxfp4_quant(void* out_fp4, void* out_sf, const void* in, int64_t m, int64_t n,
+                                int64_t in_row_stride, int in_dtype, int rounding, void* stream) {
+  clear_error();
+  NVFP_REQUIRE(rounding == NVFP_MX_ROUND_CEIL || rounding == NVFP_MX_ROUND_FLOOR,
+               "unknown MXFP4 scale rounding %d", rounding);
+  return launch_quant<32>(out_fp4, out_sf, in, nullptr, m, n, in_row_stride, in_dtype, rounding,
+                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvfp_reciprocal_approximate_ftz(float* out, const float* in, int64_t count,
+                                               void* stream) {
+  clear_error();
+  NVFP_REQUIRE(count >= 0, "negative element count");
+  if (count == 0) return NVFP_OK;
+  NVFP_REQUIRE(out != nullptr && in != nullptr, "null pointer");
+  const int64_t blocks = ceil_div(count, 256);
+  NVFP_REQUIRE(blocks < (1ll << 31), "tensor too large");
+  rcp_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(out, in, count);
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}
+
+extern "C" int nvfp_global_scale(float* gs_out, uint32_t* amax_bits, const void* in, int64_t m,
+                                 int64_t n, int64_t in_row_stride, int in_dtype, void* stream_) {
+  clear_error();
+  if (int rc = check_16bit_input(in, m, n, in_row_stride, in_dtype, 8)) return rc;
+  NVFP_REQUIRE(gs_out != nullptr && amax_bits != nullptr, "null pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  NVFP_CUDA(cudaMemsetAsync(amax_bits, 0, sizeof(uint32_t), stream));
+  if (m > 0 && n > 0) {
+    DeviceInfo info;
+    if (int rc = current_device_info(&info)) return rc;
+    const int64_t vecs = m * (n / 8);
+    const int64_t want = ceil_div(vecs, 256 * 4);
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 8));
+    if (in_dtype == NVFP_DTYPE_F16)
+      amax_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(in), in_row_stride, m, n, amax_bits);
+    else
+      amax_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), in_row_stride, m, n, amax_bits);
+    NVFP_CUDA(cudaGetLastError());
+  }
+  finish_global_scale_kernel<<<1, 1, 0, stream>>>(gs_out, amax_bits);
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}
+
+extern "C" int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const float* gs_b,
+                                      void* stream) {
+  clear_error();
+  NVFP_REQUIRE(alpha_out && gs_a && gs_b, "null pointer");
+  alpha_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(alpha_out, gs_a, gs_b);
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}

@@ -1,0 +1,161 @@
+"""QuantLinear(mode="real"): a linear layer whose forward runs activation quantize ->
+block-scaled FP4 GEMM on the sm_100a kernels.
+
+The reference names this class only in prose (README.md:18 there); the behaviour it
+exercises is FP4GemmWithOnlineActivation (speed_test.py:36-50): the weight is quantized
+once with gs_w = 2688/max|W|; each call computes gs_a = 2688/max|x|, quantizes x,
+forms alpha = 1/(gs_a*gs_w) on the device and calls the GEMM.  This class keeps those
+numerics and adds MXFP4 and the two tensor-parallel shardings (see sharding.py).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .sharding import gather_columns_layout, shard_columns, shard_range, shard_rows
+
+_FORMATS = {"nvfp4": 16, "mxfp4": 32}
+
+
+class QuantLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, mode: str = "real",
+                 format: str = "nvfp4", parallel: str | None = None, process_group=None,
+                 out_dtype: torch.dtype = torch.bfloat16, mx_rounding: str = "rceil",
+                 gather_output: bool = True, input_is_parallel: bool = False, device=None):
+        super().__init__()
+        if mode != "real":
+            raise ValueError(f"mode={mode!r}: only the real-kernel path exists (no emulation, no pseudo-quant fallback)")
+        if format not in _FORMATS:
+            raise ValueError(f"format={format!r}; expected one of {sorted(_FORMATS)}")
+        if parallel not in (None, "column", "row"):
+            raise ValueError(f"parallel={parallel!r}; expected None, 'column' or 'row'")
+        self.in_features, self.out_features = in_features, out_features
+        self.format, self.block = format, _FORMATS[format]
+        self.parallel, self.process_group = parallel, process_group
+        self.out_dtype, self.mx_rounding = out_dtype, mx_rounding
+        self.gather_output, self.input_is_parallel = gather_output, input_is_parallel
+        self.world, self.rank = 1, 0
+        if parallel is not None:
+            import torch.distributed as dist
+            self.world = dist.get_world_size(process_group)
+            self.rank = dist.get_rank(process_group)
+        n_local, k_local = out_features, in_features
+        if parallel == "column":
+            lo, hi = shard_range(out_features, self.rank, self.world, 128, "out_features")
+            n_local = hi - lo
+        elif parallel == "row":
+            lo, hi = shard_range(in_features, self.rank, self.world, 4 * self.block, "in_features")
+            k_local = hi - lo
+        self.n_local, self.k_local = n_local, k_local
+        rn = (n_local + 127) // 128 * 128
+        rk = (k_local // self.block + 3) // 4 * 4
+        self.register_buffer("weight_fp4", torch.zeros((n_local, k_local // 2), dtype=torch.uint8, device=device))
+        self.register_buffer("weight_sf", torch.zeros((rn, rk), dtype=torch.uint8, device=device))
+        self.register_buffer("weight_global_scale", torch.ones(1, dtype=torch.float32, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=out_dtype, device=device)) if bias else None
+
+    # ------------------------------------------------------------------ weights ---
+    @torch.no_grad()
+    def load_weight(self, weight: torch.Tensor) -> "QuantLinear":
+        """Quantizes the FULL [out_features, in_features] fp16/bf16 weight on its device
+        and keeps this rank's shard."""
+        assert weight.shape == (self.out_features, self.in_features), "weight shape mismatch"
+        if self.format == "nvfp4":
+            gs = ops.global_scale(weight)
+            w_fp4, w_sf = ops.scaled_fp4_quant(weight, gs)
+            self.weight_global_scale.copy_(gs)
+        else:
+            w_fp4, w_sf = ops.scaled_mxfp4_quant(weight, self.mx_rounding)
+        w_sf = w_sf.view(torch.uint8)
+        if self.parallel == "column":
+            w_fp4, w_sf = shard_columns(w_fp4, w_sf, self.rank, self.world)
+        elif self.parallel == "row":
+            w_fp4, w_sf = shard_rows(w_fp4, w_sf, self.rank, self.world, self.block)
+        self.weight_fp4 = w_fp4.to(self.weight_fp4.device)
+        self.weight_sf = w_sf.to(self.weight_sf.device)
+        return self
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, **kw) -> "QuantLinear":
+        w = linear.weight.detach()
+        if w.dtype not in (torch.float16, torch.bfloat16):
+            w = w.to(torch.bfloat16)
+        layer = cls(linear.in_features, linear.out_features, bias=linear.bias is not None,
+                    device=w.device, **kw)
+        layer.load_weight(w)
+        if linear.bias is not None:
+            layer.bias.data.copy_(linear.bias.detach().to(layer.bias.dtype))
+        return layer
+
+    def _sf_view(self, t: torch.Tensor) -> torch.Tensor:
+        return t.view(torch.float8_e4m3fn if self.format == "nvfp4" else torch.float8_e8m0fnu)
+
+    # ------------------------------------------------------------------ forward ---
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if self.parallel == "row" and not self.input_is_parallel:
+            lo, hi = shard_range(self.in_features, self.rank, self.world, 4 * self.block, "in_features")
+            x2 = x2[:, lo:hi]
+        acc_dtype = torch.float32 if self.parallel == "row" and self.world > 1 else self.out_dtype
+        if self.format == "nvfp4":
+            a_gs = self._activation_global_scale(x2)
+            a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
+            alpha = ops.alpha_from_scales(a_gs, self.weight_global_scale)
+            y = ops.cutlass_scaled_fp4_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha, acc_dtype) \
+                if acc_dtype != torch.float32 else self._mm_f32(a_fp4, a_sf, alpha)
+        else:
+            a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
+            y = ops.mxfp4_scaled_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), acc_dtype)
+        y = self._combine(y)
+        if self.bias is not None:
+            y = y + (self.bias if y.shape[-1] == self.out_features else self._bias_shard())
+        return y.reshape(*lead, y.shape[-1]) if y.shape[0] == x2.shape[0] else y
+
+    def _mm_f32(self, a_fp4, a_sf, alpha):
+        from ._ops_real import _load_scaled_fp4_ops
+        out = torch.empty((a_fp4.shape[0], self.weight_fp4.shape[0]), dtype=torch.float32, device=a_fp4.device)
+        _load_scaled_fp4_ops(("cutlass_scaled_fp4_mm",)).cutlass_scaled_fp4_mm(
+            out, a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha)
+        return out
+
+    def _activation_global_scale(self, x2: torch.Tensor) -> torch.Tensor:
+        if self.parallel == "row" and self.world > 1:
+            # every rank must quantize its K-slice with the scale of the WHOLE activation:
+            # max-reduce the per-rank amax bit patterns (non-negative floats order like ints)
+            import torch.distributed as dist
+            scratch = torch.empty(1, dtype=torch.int32, device=x2.device)
+            ops.global_scale(x2, scratch)
+            dist.all_reduce(scratch, op=dist.ReduceOp.MAX, group=self.process_group)
+            amax = scratch.view(torch.float32)
+            amax = torch.where(amax == 0, torch.ones_like(amax), amax)
+            return (448.0 * 6.0) / amax
+        return ops.global_scale(x2)
+
+    def _combine(self, y: torch.Tensor) -> torch.Tensor:
+        if self.world == 1 or self.parallel is None:
+            return y
+        import torch.distributed as dist
+        if self.parallel == "column":
+            if not self.gather_output:
+                return y
+            parts = torch.empty((self.world * y.shape[0], y.shape[1]), dtype=y.dtype, device=y.device)
+            dist.all_gather_into_tensor(parts, y.contiguous(), group=self.process_group)
+            return gather_columns_layout(parts.view(self.world, *y.shape))
+        # row-parallel: fp32 partial sums, reduce-scatter over rows, round once
+        m = y.shape[0]
+        if m % self.world != 0:
+            dist.all_reduce(y, group=self.process_group)
+            return y.to(self.out_dtype)
+        out = torch.empty((m // self.world, y.shape[1]), dtype=y.dtype, device=y.device)
+        dist.reduce_scatter_tensor(out, y.contiguous(), group=self.process_group)
+        return out.to(self.out_dtype)
+
+    def _bias_shard(self):
+        lo, hi = shard_range(self.out_features, self.rank, self.world, 128, "out_features")
+        return self.bias[lo:hi]
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, format={self.format}, "
+                f"parallel={self.parallel}, world={self.world}")

@@ -1,0 +1,84 @@
+"""Generates ref_kernel_sm100.npz by RUNNING the reference's own CUDA quantizer
+(kernel/nvfp4_quant_kernels.cu of the reference, built for sm_100a by
+oracle/build_oracle.py into oracle/_ref/) on a B200.
+
+    python tests/golden/make_ref_kernel_golden.py OUT_DIR
+
+For every case it stores the kernel's packed nibbles, its scale bytes (valid region only:
+the reference leaves padding uninitialised), the global scale, and the results of the
+reference's reciprocal_approximate_ftz_tensor for every value the quantizer can feed to
+rcp.approx.ftz with that global scale, so that the CPU oracle can replay the hardware
+reciprocal exactly.  Inputs are the seeded tensors of tests/golden/inputs.py (seed 11).
+"""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path[:0] = [HERE, ROOT]
+from inputs import DISTRIBUTIONS, make_input  # noqa: E402
+from oracle import nvfp_oracle as O  # noqa: E402
+
+CASE_DISTS = DISTRIBUTIONS + ("zeros_mixed",)
+CASE_SHAPES = ((128, 128), (129, 80))
+
+
+def load_ref():
+    d = os.path.join(ROOT, "oracle", "_ref")
+    name = [f for f in os.listdir(d) if f.startswith("ref_scaled_fp4_ops") and f.endswith(".so")][0]
+    spec = importlib.util.spec_from_file_location("ref_scaled_fp4_ops", os.path.join(d, name))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def ref_quant(ref, x, gs):
+    m, n = x.shape
+    out = torch.empty((m, n // 2), dtype=torch.uint8, device="cuda")
+    rm, rn = (m + 127) // 128 * 128, (n // 16 + 3) // 4 * 4
+    sf = torch.zeros((rm, rn // 4), dtype=torch.int32, device="cuda")
+    ref.scaled_fp4_quant_sm1xxa(out, x, sf, gs)
+    return out, sf.view(torch.uint8).reshape(rm, rn)
+
+
+def ref_rcp(ref, t):
+    y = torch.zeros_like(t)
+    ref.reciprocal_approximate_ftz_tensor(t, y)
+    return y
+
+
+def main():
+    out_dir = sys.argv[1] if len(sys.argv) > 1 else "."
+    ref = load_ref()
+    out = {}
+    for dist in CASE_DISTS:
+        for shape in CASE_SHAPES:
+            for dt_name, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+                x = make_input(dist, shape, dt, seed=11)
+                amax = x.float().abs().max()
+                gs = (torch.tensor(448.0 * 6.0) / (amax if amax > 0 else torch.tensor(1.0))).to(torch.float32)
+                xg, gsg = x.cuda(), gs.reshape(1).cuda()
+                fp4, sf = ref_quant(ref, xg, gsg)
+                first = torch.tensor([6.0, gs.item()], dtype=torch.float32, device="cuda")
+                r1 = ref_rcp(ref, first)
+                second = torch.from_numpy(O.rcp_second_pass_inputs(r1[1].item())).cuda()
+                r2 = ref_rcp(ref, second)
+                key = f"{dist}_{shape[0]}x{shape[1]}_{dt_name}"
+                out[key + "_gs"] = gs.numpy().reshape(1)
+                out[key + "_fp4"] = fp4.cpu().numpy()
+                out[key + "_sf"] = O.unswizzle_128x4(sf.cpu().numpy(), shape[0], shape[1] // 16)
+                out[key + "_rcp_in"] = torch.cat([first, second]).cpu().numpy()
+                out[key + "_rcp_out"] = torch.cat([r1, r2]).cpu().numpy()
+                if dist == "zeros_mixed":
+                    out[key + "_x"] = x.view(torch.int16).numpy()
+    path = os.path.join(out_dir, "ref_kernel_sm100.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

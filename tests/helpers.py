@@ -1,0 +1,115 @@
+"""Helpers for the GPU parity tests: calls through the C ABI (ctypes) with torch tensors
+as device buffers, and comparison utilities."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from nvfp_kernel_b200 import _capi
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.dtype) -> int:
+    return {torch.float16: _capi.NVFP_DTYPE_F16, torch.bfloat16: _capi.NVFP_DTYPE_BF16,
+            torch.float32: _capi.NVFP_DTYPE_F32}[t]
+
+
+def sf_shape(m: int, n: int, block: int):
+    return ((m + 127) // 128 * 128, (n // block + 3) // 4 * 4)
+
+
+def capi_quant(x: torch.Tensor, gs: torch.Tensor | None, fill: int = 0xAA):
+    """NVFP4 quantize through nvfp_scaled_fp4_quant.  Outputs are pre-filled with `fill`
+    so that bytes the kernel does not write are visible."""
+    lib = _capi.load()
+    m, n = x.shape
+    out = torch.full((m, n // 2), fill, dtype=torch.uint8, device=x.device)
+    sf = torch.full(sf_shape(m, n, 16), fill, dtype=torch.uint8, device=x.device)
+    _capi.check(lib.nvfp_scaled_fp4_quant(out.data_ptr(), sf.data_ptr(), x.data_ptr(),
+                                          gs.data_ptr() if gs is not None else None, m, n,
+                                          x.stride(0) if m > 1 else n, _dt(x.dtype), _stream()))
+    return out, sf
+
+
+def capi_mx_quant(x: torch.Tensor, rounding: str = "rceil", fill: int = 0xAA):
+    lib = _capi.load()
+    m, n = x.shape
+    out = torch.full((m, n // 2), fill, dtype=torch.uint8, device=x.device)
+    sf = torch.full(sf_shape(m, n, 32), fill, dtype=torch.uint8, device=x.device)
+    _capi.check(lib.nvfp_mxfp4_quant(out.data_ptr(), sf.data_ptr(), x.data_ptr(), m, n,
+                                     x.stride(0) if m > 1 else n, _dt(x.dtype),
+                                     0 if rounding == "rceil" else 1, _stream()))
+    return out, sf
+
+
+def capi_mm(a, b, sfa, sfb, alpha, out_dtype=torch.bfloat16, mx: bool = False):
+    lib = _capi.load()
+    m, n, k = a.shape[0], b.shape[0], a.shape[1] * 2
+    # canary-padded output: the kernel must not write outside [m, n]
+    buf = torch.full((m * n + 256,), float("nan"), dtype=out_dtype, device=a.device)
+    d = buf[128:128 + m * n].view(m, n)
+    fn = lib.nvfp_mxfp4_mm if mx else lib.nvfp_scaled_fp4_mm
+    _capi.check(fn(d.data_ptr(), a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                   alpha.data_ptr() if alpha is not None else None, m, n, k, _dt(out_dtype), _stream()))
+    assert _capi.device_status() == 0, "a kernel gave up on a bounded wait"
+    assert torch.isnan(buf[:128]).all() and torch.isnan(buf[128 + m * n:]).all(), "out-of-bounds write"
+    return d
+
+
+def capi_global_scale(x: torch.Tensor) -> torch.Tensor:
+    lib = _capi.load()
+    gs = torch.empty(1, dtype=torch.float32, device=x.device)
+    scratch = torch.empty(1, dtype=torch.int32, device=x.device)
+    m, n = x.shape
+    _capi.check(lib.nvfp_global_scale(gs.data_ptr(), scratch.data_ptr(), x.data_ptr(), m, n,
+                                      x.stride(0) if m > 1 else n, _dt(x.dtype), _stream()))
+    return gs
+
+
+def capi_rcp(x: torch.Tensor) -> torch.Tensor:
+    lib = _capi.load()
+    y = torch.empty_like(x)
+    _capi.check(lib.nvfp_reciprocal_approximate_ftz(y.data_ptr(), x.data_ptr(), x.numel(), _stream()))
+    return y
+
+
+def gpu_rcp_table(gs: float, device="cuda"):
+    """(inputs, outputs) of the hardware reciprocal for every value the NVFP4 quantizer
+    can feed it for global scale `gs`: lets the CPU oracle replay rcp.approx.ftz exactly."""
+    from oracle import nvfp_oracle as O
+    first = torch.tensor([6.0, gs], dtype=torch.float32, device=device)
+    r1 = capi_rcp(first)
+    second = torch.from_numpy(O.rcp_second_pass_inputs(r1[1].item())).to(device)
+    r2 = capi_rcp(second)
+    return (torch.cat([first, second]).cpu().numpy(), torch.cat([r1, r2]).cpu().numpy())
+
+
+def dequant_gpu(packed: torch.Tensor, sf_swz: torch.Tensor, block: int, ue8m0: bool, dtype=torch.float32):
+    """value * block scale on the GPU (exact in bf16 and fp32), [rows, k]."""
+    rows, kh = packed.shape
+    k = kh * 2
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6],
+                       dtype=torch.float32, device=packed.device)
+    nib = torch.stack((packed & 0xF, packed >> 4), dim=-1).reshape(rows, k).long()
+    vals = lut[nib]
+    rp, cp = sf_swz.shape
+    sf = sf_swz.reshape(rp // 128, cp // 4, 32, 4, 4).transpose(1, 3).reshape(rp, cp)[:rows, :k // block]
+    sf = sf.contiguous().view(torch.float8_e8m0fnu if ue8m0 else torch.float8_e4m3fn).float()
+    return (vals.reshape(rows, k // block, block) * sf.unsqueeze(-1)).reshape(rows, k).to(dtype)
+
+
+def check_gemm(out: torch.Tensor, ref: torch.Tensor, rel: float = 1e-2):
+    """Tolerance of the GEMM contract: max|out-ref| <= rel*max|ref| and per element
+    |out-ref| <= rel*|ref| + 2^-8 * rms(ref)."""
+    out, ref = out.double(), ref.double()
+    assert torch.isfinite(out).all(), "non-finite output"
+    err = (out - ref).abs()
+    rms = ref.pow(2).mean().sqrt()
+    mx = ref.abs().max()
+    assert err.max() <= rel * mx + 1e-30, f"max err {err.max().item():.4g} vs max|ref| {mx.item():.4g}"
+    bad = err > rel * ref.abs() + rms * 2.0 ** -8 + 1e-30
+    assert not bad.any(), f"{int(bad.sum())} elements outside tolerance; worst {err.max().item():.4g}"
+    return float(err.max()), float(mx)

@@ -1,0 +1,81 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares
+(and nothing is declared that is not exported), and its pure-host entry points work."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from nvfp_kernel_b200 import _capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "nvfp_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nvfp_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_library_agree():
+    lib = _capi.load()
+    declared = _declared_symbols()
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/nvfp_b200.h but not exported"
+    assert sorted(_capi.PROTOTYPES) == declared, "ctypes prototypes and header differ"
+
+
+def test_host_only_entry_points():
+    lib = _capi.load()
+    assert lib.nvfp_version() >= 1000
+    assert lib.nvfp_sf_rows_padded(1) == 128 and lib.nvfp_sf_rows_padded(129) == 256
+    assert lib.nvfp_sf_cols_padded(80, 16) == 8 and lib.nvfp_sf_cols_padded(8192, 16) == 512
+    assert lib.nvfp_sf_cols_padded(8192, 32) == 256
+    assert lib.nvfp_last_error() is not None
+
+
+def test_argument_validation_needs_no_gpu():
+    """Bad arguments are rejected on the host, before any CUDA call."""
+    lib = _capi.load()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf) // 16 * 16 + 16
+    rc = lib.nvfp_scaled_fp4_quant(p, p, p, None, 4, 24, 24, _capi.NVFP_DTYPE_BF16, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"multiple of 16" in lib.nvfp_last_error()
+    rc = lib.nvfp_scaled_fp4_quant(p, p, p, None, 4, 32, 32, 7, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"data type" in lib.nvfp_last_error()
+    rc = lib.nvfp_scaled_fp4_mm(p, p, p, p, p, p, 4, 32, 48, _capi.NVFP_DTYPE_BF16, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"divisible by 32" in lib.nvfp_last_error()
+    rc = lib.nvfp_scaled_fp4_mm(p, p, p, p, p, p, 4, 40, 64, _capi.NVFP_DTYPE_BF16, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"n to be divisible" in lib.nvfp_last_error()
+    rc = lib.nvfp_mxfp4_quant(p, p, p, 4, 64, 64, _capi.NVFP_DTYPE_BF16, 9, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT
+    with pytest.raises(_capi.NvfpError):
+        _capi.check(rc)
+
+
+def test_python_wrappers_assert_like_the_reference():
+    import nvfp_kernel_b200 as nv
+    import nvfp.ops as compat
+    assert compat.scaled_fp4_quant is not None and nv.get_active_backend() == "real"
+    x = torch.zeros(4, 32, dtype=torch.bfloat16)
+    gs = torch.ones(1)
+    with pytest.raises(AssertionError, match="CUDA tensor"):
+        nv.scaled_fp4_quant(x, gs)
+    u8 = torch.zeros(4, 16, dtype=torch.uint8)
+    with pytest.raises(AssertionError, match="CUDA tensor"):
+        nv.cutlass_scaled_fp4_mm(u8, u8, u8, u8, gs, torch.bfloat16)
+    with pytest.raises(ValueError, match="real"):
+        nv.QuantLinear(64, 128, mode="emulation")
+    with pytest.raises(ValueError):
+        nv.QuantLinear(64, 128, format="int4")
+
+
+def test_extension_exports_reference_symbols():
+    from nvfp_kernel_b200._ops_real import _load_scaled_fp4_ops
+    ext = _load_scaled_fp4_ops(("scaled_fp4_quant_sm1xxa", "cutlass_scaled_fp4_mm",
+                                "reciprocal_approximate_ftz_tensor"))
+    with pytest.raises(RuntimeError, match="missing required"):
+        _load_scaled_fp4_ops(("no_such_symbol",))
+    assert ext.__name__ == "scaled_fp4_ops"

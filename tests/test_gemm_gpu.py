@@ -1,0 +1,196 @@
+"""Block-scaled FP4 GEMM parity on the GPU, through the C ABI.
+
+Reference value: alpha * dequant(A) @ dequant(B)^T on the very bytes the kernel consumed,
+unrounded -- from the CPU oracle (fp64) at small sizes, and on the GPU as an fp32 matmul
+of the dequantized operands at large ones (e2m1 x ue4m3 products are exact in fp32), with
+fp64 spot checks.  Tolerance (max rel err <= 1e-2) is spelled out in helpers.check_gemm.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import capi_global_scale, capi_mm, capi_mx_quant, capi_quant, check_gemm, dequant_gpu
+from inputs import gemm_inputs, make_input
+from oracle import c_oracle, nvfp_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _quantize_pair(a, w):
+    a, w = a.cuda(), w.cuda()
+    ga, gw = capi_global_scale(a), capi_global_scale(w)
+    a_fp4, a_sf = capi_quant(a, ga)
+    w_fp4, w_sf = capi_quant(w, gw)
+    alpha = (1.0 / (ga * gw)).to(torch.float32)
+    return a_fp4, a_sf, w_fp4, w_sf, alpha
+
+
+def _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha, block=16, ue8m0=False):
+    da = dequant_gpu(a_fp4, a_sf, block, ue8m0)
+    dw = dequant_gpu(w_fp4, w_sf, block, ue8m0)
+    return (da @ dw.T).double() * (alpha.double() if alpha is not None else 1.0)
+
+
+def _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, count=4096, block=16, ue8m0=False, seed=0):
+    """`count` random output elements against an fp64 dot product on the CPU."""
+    m, n = out.shape
+    g = torch.Generator().manual_seed(seed)
+    rows = torch.randint(0, m, (64,), generator=g).unique()
+    cols = torch.randint(0, n, (64,), generator=g).unique()
+    da = dequant_gpu(a_fp4[rows.cuda()], _rows_of_sf(a_sf, rows, a_fp4.shape[1] * 2, block), block, ue8m0).double().cpu()
+    dw = dequant_gpu(w_fp4[cols.cuda()], _rows_of_sf(w_sf, cols, a_fp4.shape[1] * 2, block), block, ue8m0).double().cpu()
+    ref = (da @ dw.T) * (alpha.double().cpu() if alpha is not None else 1.0)
+    got = out[rows.cuda()][:, cols.cuda()].double().cpu()
+    check_gemm(got, ref)
+
+
+def _rows_of_sf(sf_swz, rows, k, block):
+    """Re-swizzled scale tensor holding only the selected rows (so dequant_gpu can be reused)."""
+    rp, cp = sf_swz.shape
+    lin = sf_swz.reshape(rp // 128, cp // 4, 32, 4, 4).transpose(1, 3).reshape(rp, cp)
+    sel = lin[rows.to(sf_swz.device)]
+    r = sel.shape[0]
+    pad = torch.zeros(((r + 127) // 128 * 128, cp), dtype=torch.uint8, device=sf_swz.device)
+    pad[:r] = sel
+    return pad.reshape(pad.shape[0] // 128, 4, 32, cp // 4, 4).transpose(1, 3).reshape(pad.shape[0], cp).contiguous()
+
+
+def test_scale_addressing_with_constant_operands():
+    """All data nibbles 1.0; scales are distinct powers of two per (row, K-block): any
+    mistake in how scale chunks reach tensor memory changes the result."""
+    m, n, k = 256, 384, 512
+    a_fp4 = torch.full((m, k // 2), 0x22, dtype=torch.uint8, device="cuda")
+    w_fp4 = torch.full((n, k // 2), 0x22, dtype=torch.uint8, device="cuda")
+    g = torch.Generator().manual_seed(5)
+    sfa_lin = (torch.randint(0, 6, (m, k // 16), generator=g) * 8 + 40).to(torch.uint8)   # exact powers of two
+    sfb_lin = (torch.randint(0, 6, (n, k // 16), generator=g) * 8 + 40).to(torch.uint8)
+    sfa = torch.from_numpy(O.swizzle_128x4(sfa_lin.numpy())).cuda()
+    sfb = torch.from_numpy(O.swizzle_128x4(sfb_lin.numpy())).cuda()
+    alpha = torch.ones(1, device="cuda")
+    out = capi_mm(a_fp4, w_fp4, sfa, sfb, alpha, torch.float32)
+    fa = torch.from_numpy(O.e4m3_decode(sfa_lin.numpy())).double()
+    fb = torch.from_numpy(O.e4m3_decode(sfb_lin.numpy())).double()
+    ref = 16.0 * (fa @ fb.T)
+    assert torch.equal(out.double().cpu(), ref)      # sums of powers of two: exact in fp32
+
+
+def test_one_hot_operands_locate_every_k_position():
+    """A has a single non-zero nibble per row at a row-dependent K position; B is dense.
+    Checks the K ordering inside swizzled operand tiles and across pipeline stages."""
+    m, n, k = 128, 128, 1024
+    a = torch.zeros((m, k), dtype=torch.bfloat16)
+    pos = (torch.arange(m) * 37) % k
+    a[torch.arange(m), pos] = 3.0
+    w = make_input("uniform", (n, k), torch.bfloat16, 8)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.float32)
+    ref = torch.from_numpy(O.scaled_mm_reference(a_fp4.cpu().numpy(), w_fp4.cpu().numpy(), a_sf.cpu().numpy(),
+                                                 w_sf.cpu().numpy(), alpha.item()))
+    check_gemm(out.cpu(), ref, rel=1e-5)
+
+
+@pytest.mark.parametrize("m", [1, 16, 17, 127, 128, 129, 300])
+@pytest.mark.parametrize("n,k", [(32, 32), (64, 64), (128, 96), (160, 256), (256, 320), (384, 1024), (512, 2048)])
+def test_edge_shapes_vs_cpu_oracle(m, n, k):
+    a, w = gemm_inputs(m, n, k, seed=m + n + k)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    ref = c_oracle.scaled_mm(a_fp4.cpu().numpy(), w_fp4.cpu().numpy(), a_sf.cpu().numpy(), w_sf.cpu().numpy(),
+                             alpha.item())
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
+        out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, dt)
+        check_gemm(out.cpu(), torch.from_numpy(ref))
+
+
+def test_config1_vs_reference_pseudo_quant_path():
+    """BASELINE config 1 (1024^3, seed 0): real path vs the port of the reference's torch
+    pseudo-quant path on CPU (oracle/pseudo_path.py, itself pinned to the reference's output)."""
+    from inputs import c1_inputs
+    from oracle import pseudo_path
+    a, w = c1_inputs()
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    pa, pw = pseudo_path.quantize(a), pseudo_path.quantize(w)
+    assert torch.equal(a_fp4.cpu(), pa[0]) and torch.equal(w_fp4.cpu(), pw[0])       # same bytes as the torch path
+    assert torch.equal(a_sf.cpu(), pa[1]) and torch.equal(w_sf.cpu(), pw[1])
+    ref = pseudo_path.dequantize(*pa) @ pseudo_path.dequantize(*pw).T
+    check_gemm(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("size", [64, 128, 256, 512, 1024, 2048, 4096, 8192])
+def test_square_sweep(size):
+    g = torch.Generator(device="cuda").manual_seed(size)
+    a = torch.randn((size, size), generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randn((size, size), generator=g, device="cuda").to(torch.bfloat16)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha))
+    _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, seed=size)
+    # linearity in alpha: doubling alpha doubles every output exactly (power-of-two scaling)
+    out2 = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha * 2, torch.bfloat16)
+    assert torch.equal(out2.float(), out.float() * 2)
+    # and the quantized product approximates the bf16 product
+    dense = a.float() @ w.float().T
+    assert (out.float() - dense).abs().max() < 0.25 * dense.abs().max()
+
+
+@pytest.mark.parametrize("m", [1, 16, 128])
+@pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)])
+def test_llama8b_decode_shapes(m, k, n):
+    a, w = gemm_inputs(m, n, k, seed=3, w_std=0.02)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha))
+
+
+def test_llama70b_prefill_shard_shapes_with_outlier_channels():
+    """Per-GPU slices of BASELINE config 4 at 8 GPUs: gate_up N/8 = 7168, down K/8 = 3584."""
+    for (m, n, k) in ((8192, 7168, 8192), (8192, 8192, 3584)):
+        a, w = gemm_inputs(m, n, k, seed=4, w_std=0.02, outlier_cols=True)
+        a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+        out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+        check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha))
+        _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, seed=k)
+
+
+@pytest.mark.parametrize("rounding", ["rceil", "floor"])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (17, 64, 192), (129, 256, 448), (256, 384, 1024), (4096, 8192, 8192)])
+def test_mxfp4_gemm(rounding, m, n, k):
+    """BASELINE config 5 (4096 x 8192 x 8192, Student-t activations) and edge shapes."""
+    a = make_input("student_t3", (m, k), torch.bfloat16, 5).cuda()
+    w = (make_input("normal", (n, k), torch.float32, 6) * 0.02).to(torch.bfloat16).cuda()
+    a_fp4, a_sf = capi_mx_quant(a, rounding)
+    w_fp4, w_sf = capi_mx_quant(w, rounding)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, None, torch.bfloat16, mx=True)
+    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, None, block=32, ue8m0=True))
+    if m * n * k <= 2 ** 24:
+        ref = c_oracle.scaled_mm(a_fp4.cpu().numpy(), w_fp4.cpu().numpy(), a_sf.cpu().numpy(),
+                                 w_sf.cpu().numpy(), 1.0, block=32, ue8m0=True)
+        check_gemm(out.cpu(), torch.from_numpy(ref))
+    else:
+        _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, None, block=32, ue8m0=True)
+
+
+def test_python_api_and_error_behaviour():
+    import nvfp_kernel_b200 as nv
+    a, w = gemm_inputs(64, 128, 256, seed=9)
+    a, w = a.cuda(), w.cuda()
+    ga, gw = nv.global_scale(a), nv.global_scale(w)
+    a_fp4, a_sf = nv.scaled_fp4_quant(a, ga)
+    w_fp4, w_sf = nv.scaled_fp4_quant(w, gw)
+    alpha = nv.alpha_from_scales(ga, gw)
+    assert alpha.item() == (1.0 / (ga * gw)).item()
+    out = nv.cutlass_scaled_fp4_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.float16)
+    assert out.shape == (64, 128) and out.dtype == torch.float16
+    c = capi_mm(a_fp4, w_fp4, a_sf.view(torch.uint8), w_sf.view(torch.uint8), alpha, torch.float16)
+    assert torch.equal(out, c)
+    with pytest.raises(RuntimeError, match="padded and swizzled"):
+        nv.cutlass_scaled_fp4_mm(a_fp4, w_fp4, a_sf[:64], w_sf, alpha, torch.bfloat16)
+    with pytest.raises(RuntimeError, match="cannot be multiplied"):
+        nv.cutlass_scaled_fp4_mm(a_fp4, w_fp4[:, :64].contiguous(), a_sf, w_sf, alpha, torch.bfloat16)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        nv.cutlass_scaled_fp4_mm(a_fp4[:, ::2], w_fp4[:, ::2], a_sf, w_sf, alpha, torch.bfloat16)
+    with pytest.raises(AssertionError, match="uint8"):
+        nv.cutlass_scaled_fp4_mm(a_fp4.float(), w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    with pytest.raises(AssertionError, match="fp16 or bf16"):
+        nv.cutlass_scaled_fp4_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.float32)
+    assert nv.device_status() == 0

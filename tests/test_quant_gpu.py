@@ -1,0 +1,231 @@
+"""NVFP4 / MXFP4 quantizer parity on the GPU, through the C ABI.
+
+Bit-exactness authorities, in order: (1) the reference's own CUDA quantizer built for
+sm_100a (oracle/_ref, run live here), (2) its committed outputs (tests/golden/
+ref_kernel_sm100.npz), (3) the CPU oracle replaying the hardware reciprocal.
+"""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import capi_global_scale, capi_mx_quant, capi_quant, capi_rcp, gpu_rcp_table
+from inputs import DISTRIBUTIONS, make_input
+from oracle import c_oracle, nvfp_oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TORCH_DT = {"bf16": torch.bfloat16, "fp16": torch.float16}
+ALL_DISTS = DISTRIBUTIONS + ("zeros_mixed",)
+
+
+def _load_ref():
+    d = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(d):
+        return None
+    names = [f for f in os.listdir(d) if f.startswith("ref_scaled_fp4_ops") and f.endswith(".so")]
+    if not names:
+        return None
+    spec = importlib.util.spec_from_file_location("ref_scaled_fp4_ops", os.path.join(d, names[0]))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+REF = _load_ref() if torch.cuda.is_available() else None
+needs_ref = pytest.mark.skipif(REF is None, reason="oracle/_ref (reference quantizer for sm_100a) not built")
+
+
+def _gs_for(x):
+    amax = x.float().abs().max()
+    return (torch.tensor(448.0 * 6.0) / (amax if amax > 0 else torch.tensor(1.0))).to(torch.float32).reshape(1)
+
+
+def _ref_quant(x, gs):
+    m, n = x.shape
+    out = torch.empty((m, n // 2), dtype=torch.uint8, device="cuda")
+    rm, rn = (m + 127) // 128 * 128, (n // 16 + 3) // 4 * 4
+    sf = torch.full((rm, rn // 4), 0x55555555, dtype=torch.int32, device="cuda")
+    REF.scaled_fp4_quant_sm1xxa(out, x, sf, gs)
+    return out, sf.view(torch.uint8).reshape(rm, rn)
+
+
+def _valid_sf(sf, m, n, block=16):
+    return O.unswizzle_128x4(sf.cpu().numpy(), m, n // block)
+
+
+def _padding_is_zero(sf, m, n, block=16):
+    sfn = sf.cpu().numpy().copy()
+    rp, cp = sfn.shape
+    lin = O.unswizzle_128x4(sfn, rp, cp).copy()
+    lin[:m, :n // block] = 0
+    return not lin.any()
+
+
+@needs_ref
+@pytest.mark.parametrize("shape", [(128, 128), (129, 80), (1, 4096), (17, 14336), (16, 16), (300, 2048), (1024, 1024)])
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_bit_exact_vs_reference_kernel(shape, dt):
+    for dist in ALL_DISTS:
+        x = make_input(dist, shape, TORCH_DT[dt], seed=11).cuda()
+        gs = _gs_for(x).cuda()
+        r_fp4, r_sf = _ref_quant(x, gs)
+        fp4, sf = capi_quant(x, gs)
+        assert torch.equal(fp4, r_fp4), f"{dist}: packed nibbles differ in {(fp4 != r_fp4).sum().item()} bytes"
+        assert np.array_equal(_valid_sf(sf, *shape), _valid_sf(r_sf, *shape)), f"{dist}: scale bytes differ"
+        assert _padding_is_zero(sf, *shape), f"{dist}: scale padding not zero"
+
+
+@needs_ref
+def test_bit_exact_vs_reference_kernel_full_size():
+    """BASELINE size 8192 x 8192 (bf16, N(0,1)) and the outlier-channel activations."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((8192, 8192), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    for variant in range(2):
+        if variant == 1:
+            x[:, ::97] *= 50
+        gs = (2688.0 / x.float().abs().max()).reshape(1)
+        r_fp4, r_sf = _ref_quant(x, gs)
+        fp4, sf = capi_quant(x, gs)
+        assert torch.equal(fp4, r_fp4)
+        assert torch.equal(sf, r_sf)   # no padding at this shape: whole tensors must agree
+
+
+def test_matches_committed_reference_kernel_outputs():
+    path = os.path.join(ROOT, "tests", "golden", "ref_kernel_sm100.npz")
+    if not os.path.exists(path):
+        pytest.skip("tests/golden/ref_kernel_sm100.npz not generated yet")
+    gold = np.load(path)
+    for dist in ALL_DISTS:
+        for shape in ((128, 128), (129, 80)):
+            for dt in ("bf16", "fp16"):
+                key = f"{dist}_{shape[0]}x{shape[1]}_{dt}"
+                x = make_input(dist, shape, TORCH_DT[dt], seed=11)
+                gs = torch.from_numpy(gold[key + "_gs"])
+                fp4, sf = capi_quant(x.cuda(), gs.cuda())
+                assert np.array_equal(fp4.cpu().numpy(), gold[key + "_fp4"]), key
+                assert np.array_equal(_valid_sf(sf, *shape), gold[key + "_sf"]), key
+
+
+@pytest.mark.parametrize("dist", ALL_DISTS)
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_bit_exact_vs_cpu_oracle_with_hardware_reciprocal(dist, dt):
+    for shape in ((129, 80), (256, 192)):
+        x = make_input(dist, shape, TORCH_DT[dt], seed=11)
+        gs = _gs_for(x)
+        rin, rout = gpu_rcp_table(gs.item())
+        fp4, sf = capi_quant(x.cuda(), gs.cuda())
+        o_fp4, o_sf, _ = O.nvfp4_quantize_kernel(x, gs.item(), rcp=O.RcpTable(rin, rout))
+        assert np.array_equal(fp4.cpu().numpy(), o_fp4), f"{dist} {shape}"
+        assert np.array_equal(sf.cpu().numpy(), o_sf), f"{dist} {shape}"
+        c_fp4, c_sf = c_oracle.quantize_nvfp4(x, gs.item(), rin, rout)
+        assert np.array_equal(o_fp4, c_fp4) and np.array_equal(o_sf, c_sf)
+
+
+def test_null_global_scale_means_one_and_strided_rows():
+    x = make_input("normal", (64, 256), torch.bfloat16, 4).cuda()
+    one = torch.ones(1, device="cuda")
+    a = capi_quant(x, None)
+    b = capi_quant(x, one)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    wide = make_input("normal", (64, 512), torch.bfloat16, 4).cuda()
+    view = wide[:, 128:384]                 # row stride 512, 16-byte aligned start
+    c = capi_quant(view, one)
+    d = capi_quant(view.contiguous(), one)
+    assert torch.equal(c[0], d[0]) and torch.equal(c[1], d[1])
+
+
+def test_rows_and_tiles_are_independent_full_size():
+    """Size-independent properties at the BASELINE size: permuting rows permutes the
+    output, and any aligned sub-block quantizes to the same bytes as the full tensor."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn((8192, 8192), generator=g, device="cuda").to(torch.bfloat16)
+    gs = (2688.0 / x.float().abs().max()).reshape(1)
+    fp4, sf = capi_quant(x, gs)
+    perm = torch.randperm(8192, generator=g, device="cuda")
+    p_fp4, p_sf = capi_quant(x[perm].contiguous(), gs)
+    assert torch.equal(p_fp4, fp4[perm])
+    lin = sf.reshape(64, 128, 32, 4, 4).transpose(1, 3).reshape(8192, 512)
+    p_lin = p_sf.reshape(64, 128, 32, 4, 4).transpose(1, 3).reshape(8192, 512)
+    assert torch.equal(p_lin, lin[perm])
+    s_fp4, s_sf = capi_quant(x[1024:1536, 2048:3072].contiguous(), gs)
+    assert torch.equal(s_fp4, fp4[1024:1536, 1024:1536])
+    s_lin = s_sf.reshape(4, 16, 32, 4, 4).transpose(1, 3).reshape(512, 64)
+    assert torch.equal(s_lin, lin[1024:1536, 128:192])
+    # quantization error bound: |x - dequant| <= half a quantization step of the block
+    vals = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device="cuda")
+    nib = torch.stack((fp4 & 0xF, fp4 >> 4), -1).reshape(8192, 8192).long()
+    scale = lin.contiguous().view(torch.float8_e4m3fn).float() / gs
+    deq = (vals[nib].reshape(8192, 512, 16) * scale.unsqueeze(-1)).reshape(8192, 8192)
+    err = (deq - x.float()).abs().reshape(8192, 512, 16)
+    assert (err <= scale.unsqueeze(-1) * 1.0 + 1e-6).all()   # coarsest step of e2m1 is 2 -> half step 1
+
+
+@needs_ref
+def test_reciprocal_op_bit_exact_vs_reference_op():
+    g = torch.Generator().manual_seed(3)
+    x = torch.cat([torch.randn(100000, generator=g) * 10, torch.tensor([0.0, -0.0, 1e-40, -1e-40, 6.0, 1e38, 3e38,
+                   float("inf"), -float("inf"), 2.0 ** -126, 2.0 ** 126, 2.0 ** 127])]).cuda()
+    mine = capi_rcp(x)
+    theirs = torch.zeros_like(x)
+    REF.reciprocal_approximate_ftz_tensor(x, theirs)
+    assert torch.equal(mine.view(torch.int32), theirs.view(torch.int32))
+
+
+def test_reciprocal_op_close_to_true_reciprocal():
+    x = torch.linspace(0.001, 1000, 200001, device="cuda")
+    y = capi_rcp(x)
+    rel = ((y.double() - 1.0 / x.double()).abs() * x.double()).max().item()
+    assert rel < 2.0 ** -22
+    assert capi_rcp(torch.zeros(1, device="cuda")).item() == float("inf")
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_global_scale_matches_torch_formula(dt):
+    for dist in ALL_DISTS:
+        for shape in ((1, 4096), (129, 80), (1024, 1024)):
+            x = make_input(dist, shape, TORCH_DT[dt], seed=7).cuda()
+            gs = capi_global_scale(x)
+            amax = torch.abs(x).max().to(torch.float32)           # speed_test.py:46-47 of the reference
+            want = (448.0 * 6.0) / amax
+            assert gs.item() == want.item(), (dist, shape)
+    z = torch.zeros((4, 64), dtype=TORCH_DT[dt], device="cuda")
+    assert capi_global_scale(z).item() == 2688.0
+
+
+@pytest.mark.parametrize("rounding", ["rceil", "floor"])
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_mxfp4_bit_exact_vs_cpu_restatement(rounding, dt):
+    """MXFP4 parity is unpinned by the reference (it has no MXFP4 path): this is
+    CUDA-vs-own-CPU-restatement self-consistency."""
+    for dist in ALL_DISTS + ("student_t3",):
+        for shape in ((128, 128), (129, 96), (1, 4096), (300, 2048)):
+            x = make_input(dist, shape, TORCH_DT[dt], seed=13)
+            fp4, sf = capi_mx_quant(x.cuda(), rounding)
+            o_fp4, o_sf, _ = O.mxfp4_quantize(x, rounding)
+            assert np.array_equal(fp4.cpu().numpy(), o_fp4), (dist, shape)
+            assert np.array_equal(sf.cpu().numpy(), o_sf), (dist, shape)
+
+
+def test_python_api_matches_capi_and_reference_shapes():
+    import nvfp_kernel_b200 as nv
+    x = make_input("normal", (2, 65, 256), torch.bfloat16, 21).cuda()     # leading dims are flattened
+    gs = nv.global_scale(x)
+    fp4, sf = nv.scaled_fp4_quant(x, gs)
+    assert fp4.shape == (130, 128) and fp4.dtype == torch.uint8
+    assert sf.shape == (256, 16) and sf.dtype == torch.float8_e4m3fn
+    c_fp4, c_sf = capi_quant(x.reshape(130, 256), gs)
+    assert torch.equal(fp4, c_fp4) and torch.equal(sf.view(torch.uint8), c_sf)
+    y = nv.reciprocal_approximate_ftz_tensor(torch.tensor([2.0, 4.0], device="cuda"))
+    assert y.tolist() == [0.5, 0.25]
+    m_fp4, m_sf = nv.scaled_mxfp4_quant(x)
+    assert m_sf.dtype == torch.float8_e8m0fnu and m_sf.shape == (256, 8)
+    with pytest.raises(AssertionError, match="multiple of 16"):
+        nv.scaled_fp4_quant(torch.zeros(4, 24, dtype=torch.bfloat16, device="cuda"), gs)
+    with pytest.raises(AssertionError, match="fp16 or bf16"):
+        nv.scaled_fp4_quant(torch.zeros(4, 32, dtype=torch.float32, device="cuda"), gs)
+    with pytest.raises(AssertionError, match="fp32"):
+        nv.scaled_fp4_quant(torch.zeros(4, 32, dtype=torch.bfloat16, device="cuda"), gs.half())
+    assert nv.device_status() == 0
