@@ -109,7 +109,8 @@ int nvfp_mxfp4_mm(void* d, const void* a, const void* b, const void* sfa, const 
 int nvfp_reciprocal_approximate_ftz(float* out, const float* in, int64_t count, void* stream);
 
 /*
- * Per-tensor global scale  gs = (448 * 6) / max|x|  as one fp32 on the device.
+ * Per-tensor global scale  gs = rcp(max|x|) * (448 * 6)  (both steps correctly rounded fp32,
+ * which is how torch evaluates `2688 / amax`) as one fp32 on the device.
  * Replaces the torch sequence abs().max() -> 2688/amax of speed_test.py:40-41,46-47
  * and nvfp/pseudo_quant.py:94-96 with two kernels and no temporary.
  *   amax_bits  device scratch, one uint32; the call resets it on the stream first.

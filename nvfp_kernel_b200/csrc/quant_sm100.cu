@@ -229,7 +229,9 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
 __global__ void finish_global_scale_kernel(float* gs_out, const uint32_t* amax_bits) {
   float amax = __uint_as_float(*amax_bits);
   if (amax == 0.0f) amax = 1.0f;
-  *gs_out = __fdiv_rn(448.0f * 6.0f, amax);
+  // torch evaluates `2688 / amax` (scalar / tensor) as reciprocal(amax) * 2688: two roundings.
+  // The reference forms its global scales that way (speed_test.py:41,47; nvfp/pseudo_quant.py:94-96).
+  *gs_out = __fmul_rn(__frcp_rn(amax), 448.0f * 6.0f);
 }
 
 __global__ void alpha_kernel(float* alpha_out, const float* gs_a, const float* gs_b) {

@@ -248,8 +248,10 @@ def nvfp4_quantize_kernel(x, global_scale, rcp=rcp_true, pad_value: int = 0):
     sf_q = e4m3_decode(sf_byte)                                  # :208
     rg = rcp(np.array([gs], dtype=np.float32))[0]
     denom = mul_ftz(sf_q, rg)
-    with np.errstate(all="ignore"):
-        out_scale = np.where(sf_q != 0, rcp(denom), np.float32(0))  # :213-216
+    out_scale = np.zeros_like(sf_q)                              # :213-216
+    nz = sf_q != 0
+    if nz.any():
+        out_scale[nz] = rcp(denom[nz])
     y = mul_ftz(xb, out_scale[..., None].astype(np.float32))     # :224-235
     nib = e2m1_encode(y).reshape(m, n)                            # :238
     packed = pack_nibbles(nib)
@@ -283,8 +285,9 @@ def nvfp4_quantize_torch_path(x, global_scale, rcp=rcp_true):
 
 
 def global_scale_from_amax(amax) -> np.float32:
-    """gs = (448*6)/amax in fp32 (speed_test.py:40-41, nvfp/pseudo_quant.py:94-96)."""
-    return np.float32(np.float32(E4M3_MAX * E2M1_MAX) / np.float32(amax))
+    """gs = (448*6)/amax as torch evaluates `scalar / tensor`: fp32 reciprocal, then times
+    2688 (speed_test.py:40-41, nvfp/pseudo_quant.py:94-96)."""
+    return np.float32(np.float32(np.float32(1.0) / np.float32(amax)) * np.float32(E4M3_MAX * E2M1_MAX))
 
 
 # --------------------------------------------------------------------------- #

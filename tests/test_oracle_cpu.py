@@ -176,3 +176,27 @@ def test_rcp_table_replay():
     a = O.nvfp4_quantize_kernel(x, gs, rcp=table)
     b = O.nvfp4_quantize_kernel(x, gs)
     assert all(np.array_equal(u, v) for u, v in zip(a, b))
+
+
+KERNEL_GOLD_PATH = os.path.join(os.path.dirname(__file__), "golden", "ref_kernel_sm100.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(KERNEL_GOLD_PATH), reason="reference-kernel fixture not generated")
+@pytest.mark.parametrize("dist", DISTRIBUTIONS + ("zeros_mixed",))
+def test_kernel_restatement_matches_reference_cuda_kernel_outputs(dist):
+    """tests/golden/ref_kernel_sm100.npz holds outputs of the reference's own CUDA quantizer
+    run on a B200, with the hardware reciprocals it used; the numpy and C restatements must
+    reproduce its bytes exactly (tiny, zero and denormal blocks included)."""
+    gold = np.load(KERNEL_GOLD_PATH)
+    for shape in ((128, 128), (129, 80)):
+        for dt in ("bf16", "fp16"):
+            key = f"{dist}_{shape[0]}x{shape[1]}_{dt}"
+            x = make_input(dist, shape, TORCH_DT[dt], seed=11)
+            if key + "_x" in gold:
+                assert np.array_equal(x.view(torch.int16).numpy(), gold[key + "_x"])
+            gs, rin, rout = gold[key + "_gs"][0], gold[key + "_rcp_in"], gold[key + "_rcp_out"]
+            fp4, _, lin = O.nvfp4_quantize_kernel(x, gs, rcp=O.RcpTable(rin, rout))
+            assert np.array_equal(fp4, gold[key + "_fp4"]), key
+            assert np.array_equal(lin, gold[key + "_sf"]), key
+            c_fp4, c_sf = c_oracle.quantize_nvfp4(x, gs, rin, rout)
+            assert np.array_equal(c_fp4, fp4) and np.array_equal(O.unswizzle_128x4(c_sf, shape[0], shape[1] // 16), lin)
