@@ -120,6 +120,21 @@ int nvfp_reciprocal_approximate_ftz(float* out, const float* in, int64_t count, 
 int nvfp_global_scale(float* gs_out, uint32_t* amax_bits, const void* in, int64_t m, int64_t n,
                       int64_t in_row_stride, int in_dtype, void* stream);
 
+/*
+ * Same result as nvfp_global_scale, for callers that cannot hand over scratch memory because
+ * they may not allocate any: code running under an engine whose device allocator is closed
+ * after warm-up, or on host threads where cudaMalloc is forbidden.  No counterpart in the
+ * reference.  The amax word lives in a 256-byte array inside the library (held by every GPU
+ * that loads it, until exit); the call allocates nothing and calls no allocating routine.
+ *   - tensors of more than 2^32 elements are rejected (NVFP_ERR_INVALID_ARGUMENT);
+ *   - the first call on each device looks the array's address up (cudaGetSymbolAddress):
+ *     make that call before any stream capture;
+ *   - all calls on a device share the array: the call clears the word it uses on its stream,
+ *     but two calls that overlap on the GPU (different streams) race.  Serialise them.
+ */
+int nvfp_global_scale_noalloc(float* gs_out, const void* in, int64_t m, int64_t n,
+                              int64_t in_row_stride, int in_dtype, void* stream);
+
 /* alpha_out[0] = 1 / (gs_a[0] * gs_b[0]) in fp32 on the device (speed_test.py:49). */
 int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const float* gs_b, void* stream);
 

@@ -344,3 +344,71 @@ extern "C" int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const
   NVFP_CUDA(cudaGetLastError());
   return NVFP_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Global scale for callers that may not allocate device memory.
+//
+// nvfp_global_scale needs one 32-bit scratch word from its caller.  A caller that lives
+// inside someone else's memory plan -- an inference engine whose allocator is frozen after
+// warm-up, a plugin invoked from a host that forbids cudaMalloc on its threads -- has no word
+// to give.  This variant keeps the word in a file-scope device array that every GPU loading
+// the library holds until the process exits (kNoAllocScratchWords * 4 bytes).
+//
+// In host code `g_noalloc_scratch` is only a stand-in for the device symbol, not a device
+// address; the address is looked up once per device with cudaGetSymbolAddress (that device
+// current) and handed to the kernels.
+namespace nvfp {
+namespace {
+constexpr int kNoAllocScratchWords = 64;              // one 256-byte line; word 0 holds the amax bits
+constexpr int64_t kNoAllocMaxElements = 1ll << 32;    // largest tensor this entry point accepts
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocScratchWords];
+
+int noalloc_scratch_address(uint32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static uint32_t* cache[kMaxDevices] = {};
+  int dev = 0;
+  NVFP_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(NVFP_ERR_CUDA, "device index %d out of range", dev);
+  if (!cache[dev]) {
+    uint32_t* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(NVFP_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed on device %d: %s", dev,
+                  cudaGetErrorString(e));
+    cache[dev] = ptr;
+  }
+  *out = cache[dev];
+  return NVFP_OK;
+}
+}  // namespace
+}  // namespace nvfp
+
+extern "C" int nvfp_global_scale_noalloc(float* gs_out, const void* in, int64_t m, int64_t n,
+                                         int64_t in_row_stride, int in_dtype, void* stream_) {
+  clear_error();
+  if (int rc = check_16bit_input(in, m, n, in_row_stride, in_dtype, 8)) return rc;
+  NVFP_REQUIRE(gs_out != nullptr, "null pointer");
+  NVFP_REQUIRE(m * n <= kNoAllocMaxElements,
+               "nvfp_global_scale_noalloc accepts at most %lld elements, got %lld x %lld; use nvfp_global_scale "
+               "with caller-provided scratch for larger tensors",
+               (long long)kNoAllocMaxElements, (long long)m, (long long)n);
+  uint32_t* scratch = nullptr;
+  if (int rc = noalloc_scratch_address(&scratch)) return rc;    // first call on a device: symbol look-up
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // the array keeps the previous call's maximum: clear the word this call reduces into
+  NVFP_CUDA(cudaMemsetAsync(scratch, 0, sizeof(uint32_t), stream));
+  if (m > 0 && n > 0) {
+    DeviceInfo info;
+    if (int rc = current_device_info(&info)) return rc;
+    const int64_t want = ceil_div(m * (n / 8), 256 * 4);
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 8));
+    if (in_dtype == NVFP_DTYPE_F16)
+      amax_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(in), in_row_stride, m, n, scratch);
+    else
+      amax_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), in_row_stride, m, n, scratch);
+    NVFP_CUDA(cudaGetLastError());
+  }
+  finish_global_scale_kernel<<<1, 1, 0, stream>>>(gs_out, scratch);
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}
