@@ -1,0 +1,302 @@
+// Block-scaled FP4 GEMM on CTA pairs (tcgen05 cta_group::2): one cluster of two CTAs on a
+// TPC computes a 256 x 256 output tile.  Included by gemm_fp4_sm100.cu inside namespace
+// nvfp::<anonymous>; uses its GemmParams, store_row_chunk and tensor-map helpers.
+//
+// Why pairs: per 64 elements of K a single CTA computing 128 x 256 must bring 128 + 256 operand
+// rows through L2 and its own shared memory; a pair computing 256 x 256 brings 128 + 128 rows
+// per CTA for twice the flops, because the tensor cores of the two SMs exchange their halves of B.
+// The reference's kernel (CUTLASS Sm120, cluster 1x1x1, kernel/nvfp4_scaled_mm_sm120_kernels.cu:52-70)
+// has no such mode.
+//
+// Roles per CTA (192 threads):
+//   warp 0   producer: TMA loads of its 128 rows of A, its 128 rows of B, its 128 rows of A
+//            scales and all 256 rows of B scales into its own shared memory; completion is
+//            reported to the LEADER's (cluster rank 0) "full" barrier
+//   warp 1   leader only: issuer of tcgen05.cp / tcgen05.mma for both CTAs
+//   warps 2-5 epilogue of this CTA's 128 accumulator rows
+// Every load is issued by the CTA that consumes it (no cluster-wide broadcast loads).
+#pragma once
+
+constexpr int kPairBM = 256;
+constexpr int kPairBN = 256;
+
+template <bool MX>
+struct PairCfg {
+  static constexpr int kChunksPerStage = MX ? 2 : 4;
+  static constexpr int kMmasPerChunk = MX ? 2 : 1;
+  static constexpr uint32_t kABytes = 128 * kStageKBytes;                    // this CTA's rows of A
+  static constexpr uint32_t kBBytes = 128 * kStageKBytes;                    // this CTA's half of B
+  static constexpr uint32_t kSfaBytes = kChunksPerStage * 512;
+  static constexpr uint32_t kSfbBytes = 2 * kChunksPerStage * 512;           // both 128-row tiles of B scales
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kStages = (kSmemLimit - 2048) / kStageBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 2048;
+  // Tensor-memory columns.  Two 256-column accumulators do not fit beside the scale columns, so they
+  // OVERLAP: even tiles accumulate in [0,256), odd tiles in [208,464), scales live in [464,512).  The
+  // epilogue drains the shared columns [208,256) first and releases the accumulator barrier right
+  // after, so the next tile's MMAs start while the other 208 columns are still being stored.
+  static constexpr uint32_t kSfaCols = 4 * kChunksPerStage;
+  static constexpr uint32_t kSfbCols = 8 * kChunksPerStage;
+  static constexpr uint32_t kSfColBase = kTmemCols - 48;
+  static constexpr uint32_t kOddAccCol = kSfColBase - kPairBN;          // 208
+  static constexpr int kEarlyChunks = 2;   // 32-column chunks that cover the shared columns
+  static_assert(kSfaCols + kSfbCols <= 48, "scale columns");
+  static_assert(kOddAccCol % 16 == 0 && kOddAccCol + 32 * kEarlyChunks >= kPairBN, "overlap covered by the early chunks");
+};
+
+template <bool MX, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                     const GemmParams p) {
+  using C = PairCfg<MX>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  constexpr int kFull = 0, kEmpty = C::kStages, kAccFull = 2 * C::kStages, kAccEmpty = kAccFull + 1,
+                kDrain = kAccEmpty + 1, kNumBars = kDrain + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* never_set = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const uint32_t smem_base = smem_u32(smem);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(bar(kFull + i), 1);     // armed by the leader's producer for the bytes of BOTH CTAs
+      mbar_init(bar(kEmpty + i), 1);    // one commit from the leader's issuer
+    }
+    mbar_init(bar(kAccFull), 1);        // one commit from the leader's issuer
+    mbar_init(bar(kAccEmpty), 8);       // 4 epilogue warps x 2 CTAs (used in the leader)
+    mbar_init(bar(kDrain), 1);
+    *abort_flag = 0;
+    *never_set = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    prefetch_tensormap(&tmap_sfa);
+    prefetch_tensormap(&tmap_sfb);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_alloc_permit_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                    // the peer's barriers and tensor memory exist from here on
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_stages = (p.k + kStageK - 1) / kStageK;
+  const int first_tile = (int)cluster_id_x();
+  const int tile_step = (int)num_clusters_x();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer ---
+    if (elect_one()) {
+      uint32_t kc = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        for (int ks = 0; ks < k_stages; ++ks, ++kc) {
+          const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
+          if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicOr(p.status, kErrProducer);
+            ok = false;
+            break;
+          }
+          const uint32_t st = smem_base + s * C::kStageBytes;
+          const uint32_t full = map_to_cta(bar(kFull + s), 0);
+          // Only the leader arms the barrier (CTA-local, no cluster-scope release on the hot path).  The
+          // peer's bytes may arrive first: the transaction count goes negative for a moment, the phase
+          // cannot complete before the leader's arrival.
+          if (rank == 0) mbar_arrive_expect_tx(bar(kFull + s), 2 * C::kStageBytes);
+          tma_load_2d_pair(st, &tmap_a, full, ks * kStageKBytes, tm * kPairBM + (int)rank * 128);
+          tma_load_2d_pair(st + C::kABytes, &tmap_b, full, ks * kStageKBytes, tn * kPairBN + (int)rank * 128);
+          tma_load_3d_pair(st + C::kABytes + C::kBBytes, &tmap_sfa, full, 0, ks * C::kChunksPerStage,
+                           tm * 2 + (int)rank);
+          tma_load_3d_pair(st + C::kABytes + C::kBBytes + C::kSfaBytes, &tmap_sfb, full, 0,
+                           ks * C::kChunksPerStage, tn * 2);
+        }
+      }
+      if (!ok || *abort_flag) {
+        // The loads already issued report to the leader's barriers, which this thread cannot wait
+        // on from the peer CTA: give them a fixed, bounded time to land before the CTA may exit.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- issuer ---
+    if (rank == 0 && elect_one()) {
+      uint32_t kc = 0;
+      bool ok = true;
+      int it = 0;
+      const uint32_t acc_full_0 = map_to_cta(bar(kAccFull), 0), acc_full_1 = map_to_cta(bar(kAccFull), 1);
+      const uint32_t empty_0 = map_to_cta(bar(kEmpty), 0), empty_1 = map_to_cta(bar(kEmpty), 1);
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++it) {
+        if (!mbar_wait_bounded(bar(kAccEmpty), ((uint32_t)it & 1u) ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(p.status, kErrIssuer);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + ((it & 1) ? C::kOddAccCol : 0u);
+        for (int ks = 0; ks < k_stages; ++ks, ++kc) {
+          const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
+          if (!mbar_wait_bounded(bar(kFull + s), ph, abort_flag)) {
+            *abort_flag = 1;
+            atomicOr(p.status, kErrIssuer);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
+          const int mmas = min(kStageK / kMmaK, (p.k - ks * kStageK + kMmaK - 1) / kMmaK);
+          const uint32_t st = smem_base + s * C::kStageBytes;
+          // one set of scale columns: tcgen05.cp and tcgen05.mma of one thread execute in issue order, so
+          // the copies for this stage cannot overtake the MMAs of the previous one that read the same columns
+          const uint32_t sf_slot = tmem_base + C::kSfColBase;
+          const uint32_t sfa_tmem = sf_slot, sfb_tmem = sf_slot + C::kSfaCols;
+          const uint64_t a_desc = make_smem_desc(st, 16, 1024, 2);
+          const uint64_t b_desc = make_smem_desc(st + C::kABytes, 16, 1024, 2);
+          for (int c = 0; c < chunks; ++c) {
+            tc_copy_sf_32x128b_warpx4_pair(
+                sfa_tmem + 4 * c, make_smem_desc(st + C::kABytes + C::kBBytes + c * 512, 0, 128, 0));
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              tc_copy_sf_32x128b_warpx4_pair(
+                  sfb_tmem + 4 * (c * 2 + h),
+                  make_smem_desc(st + C::kABytes + C::kBBytes + C::kSfaBytes + (h * C::kChunksPerStage + c) * 512,
+                                 0, 128, 0));
+            for (int jj = 0; jj < C::kMmasPerChunk; ++jj) {
+              const int j = c * C::kMmasPerChunk + jj;
+              if (j >= mmas) break;
+              const uint32_t accumulate = (ks | j) != 0 ? 1u : 0u;
+              const uint64_t koff = (uint64_t)((j * (kMmaK / 2)) >> 4);
+              if (MX) {
+                const uint32_t sf_id = (uint32_t)jj * 2u;
+                tc_mma_mxf4_pair(d_tmem, a_desc + koff, b_desc + koff,
+                                 make_idesc_fp4_block_scaled(kPairBM, kPairBN, true, sf_id, sf_id),
+                                 sfa_tmem + 4 * c, sfb_tmem + 8 * c, accumulate);
+              } else {
+                tc_mma_nvf4_pair(d_tmem, a_desc + koff, b_desc + koff,
+                                 make_idesc_fp4_block_scaled(kPairBM, kPairBN, false),
+                                 sfa_tmem + 4 * c, sfb_tmem + 8 * c, accumulate);
+              }
+            }
+          }
+          // the stage is reusable in BOTH CTAs once these MMAs have read it
+          tc_commit_pair(empty_0 + 8 * s);
+          tc_commit_pair(empty_1 + 8 * s);
+        }
+        if (ok) {
+          tc_commit_pair(acc_full_0);
+          tc_commit_pair(acc_full_1);
+        }
+      }
+      if (*abort_flag) {
+        tc_commit_pair(map_to_cta(bar(kDrain), 0));
+        mbar_wait_bounded(bar(kDrain), 0, never_set, 200000000ull);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue ---
+    const int q = warp & 3;
+    const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+    OutT* d = static_cast<OutT*>(p.d);
+    const uint32_t acc_empty_leader = map_to_cta(bar(kAccEmpty), 0);
+    int it = 0;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
+      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull), (uint32_t)it & 1u, abort_flag))) {
+        *abort_flag = 1;
+        if (lane == 0) atomicOr(p.status, kErrEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tm * kPairBM + (int)rank * 128 + q * 32 + lane;
+      const bool odd = (it & 1) != 0;
+      const uint32_t t_row = tmem_base + (odd ? C::kOddAccCol : 0u) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int i = 0; i < kPairBN / 32; ++i) {
+        // even tiles drain from the last chunk down, odd tiles from the first up: either way the
+        // columns shared with the other accumulator go first
+        const int c = odd ? i : kPairBN / 32 - 1 - i;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        if (i == C::kEarlyChunks - 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        }
+        const int col = tn * kPairBN + c * 32;
+        if (row < p.m && col < p.n) store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha);
+      }
+    }
+  }
+
+  // -------------------------------------------------------------- common exit ---
+  // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+}
+
+// Scale tensor as a 3-D map: 512-byte chunk (128 x u32) | chunk index along K | 128-row tile.
+inline int make_scale_map(CUtensorMap* map, const void* base, int64_t k_chunks, int64_t row_tiles,
+                          int box_chunks, int box_tiles) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[3] = {128, (cuuint64_t)k_chunks, (cuuint64_t)row_tiles};
+  const cuuint64_t strides[2] = {512, (cuuint64_t)k_chunks * 512};
+  const cuuint32_t box[3] = {128, (cuuint32_t)box_chunks, (cuuint32_t)box_tiles};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with code %d", (int)r);
+  return NVFP_OK;
+}
+
+template <bool MX, typename OutT>
+int launch_pair(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream) {
+  using C = PairCfg<MX>;
+  GemmParams p = base;
+  p.tiles_m = (int)ceil_div(p.m, kPairBM);
+  p.tiles_n = (int)ceil_div(p.n, kPairBN);
+  CUtensorMap map_a, map_b, map_sfa, map_sfb;
+  if (int rc = make_operand_map(&map_a, a, p.m, p.k, 128)) return rc;
+  if (int rc = make_operand_map(&map_b, b, p.n, p.k, 128)) return rc;
+  if (int rc = make_scale_map(&map_sfa, p.sfa, p.sf_k_chunks, ceil_div(p.m, 128), C::kChunksPerStage, 1)) return rc;
+  if (int rc = make_scale_map(&map_sfb, p.sfb, p.sf_k_chunks, ceil_div(p.n, 128), C::kChunksPerStage, 2)) return rc;
+  auto kernel = fp4_gemm_pair_kernel<MX, OutT>;
+  NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  const unsigned pairs = (unsigned)std::min<int64_t>(tiles, sm_count / 2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, p));
+  return NVFP_OK;
+}

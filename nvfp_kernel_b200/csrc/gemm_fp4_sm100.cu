@@ -368,6 +368,8 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
   return NVFP_OK;
 }
 
+#include "gemm_fp4_pair_sm100.cuh"
+
 template <bool MX>
 int scaled_mm(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream) {
@@ -402,6 +404,15 @@ int scaled_mm(void* d, const void* a, const void* b, const void* sfa, const void
   p.sfb_row_tiles = (int)ceil_div(n, 128);
   p.status = device_status_word();
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
+  // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
+  const int64_t pair_tiles = ceil_div(m, kPairBM) * ceil_div(n, kPairBN);
+  if (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2) {
+    switch (out_dtype) {
+      case NVFP_DTYPE_BF16: return launch_pair<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream);
+      case NVFP_DTYPE_F16: return launch_pair<MX, __half>(p, a, b, info.sm_count, stream);
+      default: return launch_pair<MX, float>(p, a, b, info.sm_count, stream);
+    }
+  }
   // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a
   // single accumulator buffer; use them when there are enough tiles to fill the GPU.
   const int64_t tiles256 = ceil_div(m, kBM) * ceil_div(n, 256);
