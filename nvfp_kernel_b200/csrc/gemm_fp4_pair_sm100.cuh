@@ -136,66 +136,77 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     // -------------------------------------------------------------- issuer ---
     if (rank == 0 && elect_one()) {
-      uint32_t kc = 0;
+      // This one thread feeds the tensor pipe of both SMs; whatever it does between two MMAs that the
+      // pipe's small queue cannot cover shows up as idle tensor cycles.  Hence: stage index and phase
+      // are carried instead of recomputed, descriptors are formed by adding constants, and the next
+      // stage's barrier is polled once BEFORE the last MMAs of the current stage are queued.
       bool ok = true;
       int it = 0;
+      uint32_t s = 0, ph = 0;
+      bool next_ready = false;
       const uint32_t acc_full_0 = map_to_cta(bar(kAccFull), 0), acc_full_1 = map_to_cta(bar(kAccFull), 1);
       const uint32_t empty_0 = map_to_cta(bar(kEmpty), 0), empty_1 = map_to_cta(bar(kEmpty), 1);
+      const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024, 2);
+      const uint64_t b_desc0 = make_smem_desc(smem_base + C::kABytes, 16, 1024, 2);
+      const uint64_t sfa_desc0 = make_smem_desc(smem_base + C::kABytes + C::kBBytes, 0, 128, 0);
+      const uint64_t sfb_desc0 = make_smem_desc(smem_base + C::kABytes + C::kBBytes + C::kSfaBytes, 0, 128, 0);
+      const uint32_t sfa_tmem = tmem_base + C::kSfColBase, sfb_tmem = sfa_tmem + C::kSfaCols;
+      const int tail_mmas = (p.k - (k_stages - 1) * kStageK + kMmaK - 1) / kMmaK;   // MMAs in the last stage
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++it) {
         if (!mbar_wait_bounded(bar(kAccEmpty), ((uint32_t)it & 1u) ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicOr(p.status, kErrIssuer);
           break;
         }
-        tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + ((it & 1) ? C::kOddAccCol : 0u);
-        for (int ks = 0; ks < k_stages; ++ks, ++kc) {
-          const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
-          if (!mbar_wait_bounded(bar(kFull + s), ph, abort_flag)) {
+        const bool more_tiles = tile + tile_step < num_tiles;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if (!next_ready && !mbar_wait_bounded(bar(kFull + s), ph, abort_flag)) {
             *abort_flag = 1;
             atomicOr(p.status, kErrIssuer);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
-          const int mmas = min(kStageK / kMmaK, (p.k - ks * kStageK + kMmaK - 1) / kMmaK);
-          const uint32_t st = smem_base + s * C::kStageBytes;
-          // one set of scale columns: tcgen05.cp and tcgen05.mma of one thread execute in issue order, so
-          // the copies for this stage cannot overtake the MMAs of the previous one that read the same columns
-          const uint32_t sf_slot = tmem_base + C::kSfColBase;
-          const uint32_t sfa_tmem = sf_slot, sfb_tmem = sf_slot + C::kSfaCols;
-          const uint64_t a_desc = make_smem_desc(st, 16, 1024, 2);
-          const uint64_t b_desc = make_smem_desc(st + C::kABytes, 16, 1024, 2);
-          for (int c = 0; c < chunks; ++c) {
-            tc_copy_sf_32x128b_warpx4_pair(
-                sfa_tmem + 4 * c, make_smem_desc(st + C::kABytes + C::kBBytes + c * 512, 0, 128, 0));
+          const int mmas = ks == k_stages - 1 ? tail_mmas : kStageK / kMmaK;
+          const uint64_t stage_off = (uint64_t)((s * C::kStageBytes) >> 4);
+          const uint64_t a_desc = a_desc0 + stage_off, b_desc = b_desc0 + stage_off;
+          const uint64_t sfa_desc = sfa_desc0 + stage_off, sfb_desc = sfb_desc0 + stage_off;
+          const uint32_t s_next = s + 1 == (uint32_t)C::kStages ? 0u : s + 1;
+          const uint32_t ph_next = s_next == 0 ? ph ^ 1u : ph;
+          const bool has_next = more_tiles || ks + 1 < k_stages;
+          next_ready = false;
+          // One set of scale columns: tcgen05.cp and tcgen05.mma of one thread execute in issue order,
+          // so a copy cannot overtake the earlier MMAs that read the columns it overwrites.
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
-              tc_copy_sf_32x128b_warpx4_pair(
-                  sfb_tmem + 4 * (c * 2 + h),
-                  make_smem_desc(st + C::kABytes + C::kBBytes + C::kSfaBytes + (h * C::kChunksPerStage + c) * 512,
-                                 0, 128, 0));
-            for (int jj = 0; jj < C::kMmasPerChunk; ++jj) {
-              const int j = c * C::kMmasPerChunk + jj;
-              if (j >= mmas) break;
-              const uint32_t accumulate = (ks | j) != 0 ? 1u : 0u;
-              const uint64_t koff = (uint64_t)((j * (kMmaK / 2)) >> 4);
-              if (MX) {
-                const uint32_t sf_id = (uint32_t)jj * 2u;
-                tc_mma_mxf4_pair(d_tmem, a_desc + koff, b_desc + koff,
-                                 make_idesc_fp4_block_scaled(kPairBM, kPairBN, true, sf_id, sf_id),
-                                 sfa_tmem + 4 * c, sfb_tmem + 8 * c, accumulate);
-              } else {
-                tc_mma_nvf4_pair(d_tmem, a_desc + koff, b_desc + koff,
-                                 make_idesc_fp4_block_scaled(kPairBM, kPairBN, false),
-                                 sfa_tmem + 4 * c, sfb_tmem + 8 * c, accumulate);
+          for (int c = 0; c < C::kChunksPerStage; ++c) {
+            if (c * C::kMmasPerChunk < mmas) {
+              if (c == C::kChunksPerStage - 1 && has_next) next_ready = mbar_try_wait(bar(kFull + s_next), ph_next);
+              tc_copy_sf_32x128b_warpx4_pair(sfa_tmem + 4 * c, sfa_desc + 32 * c);
+              tc_copy_sf_32x128b_warpx4_pair(sfb_tmem + 8 * c, sfb_desc + 32 * c);
+              tc_copy_sf_32x128b_warpx4_pair(sfb_tmem + 8 * c + 4, sfb_desc + 32 * (C::kChunksPerStage + c));
+#pragma unroll
+              for (int jj = 0; jj < C::kMmasPerChunk; ++jj) {
+                const int j = c * C::kMmasPerChunk + jj;
+                if (j < mmas) {
+                  const uint32_t accumulate = (ks | j) != 0 ? 1u : 0u;
+                  if (MX)
+                    tc_mma_mxf4_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
+                                     make_idesc_fp4_block_scaled(kPairBM, kPairBN, true, 2u * jj, 2u * jj),
+                                     sfa_tmem + 4 * c, sfb_tmem + 8 * c, accumulate);
+                  else
+                    tc_mma_nvf4_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
+                                     make_idesc_fp4_block_scaled(kPairBM, kPairBN, false),
+                                     sfa_tmem + 4 * c, sfb_tmem + 8 * c, accumulate);
+                }
               }
             }
           }
           // the stage is reusable in BOTH CTAs once these MMAs have read it
           tc_commit_pair(empty_0 + 8 * s);
           tc_commit_pair(empty_1 + 8 * s);
+          s = s_next;
+          ph = ph_next;
         }
         if (ok) {
           tc_commit_pair(acc_full_0);

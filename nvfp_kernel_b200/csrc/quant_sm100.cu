@@ -106,29 +106,59 @@ __device__ __forceinline__ uint32_t scale_and_pack(const Pack8<T>& v, float scal
 
 constexpr int kThreads = 256;
 constexpr int kTileRows = 128;
+constexpr int kTileCols = 128;   // 8 threads x 16 elements per row segment
+
+// 16 consecutive elements (32 bytes) of one row.
+template <typename T>
+union Pack16 {
+  uint4 raw[2];
+  typename Vec2<T>::type h2[8];
+};
+
+// One 32-byte load (sm_100 has 256-bit global loads) when the address allows it, else two
+// 16-byte loads.
+template <typename T>
+__device__ __forceinline__ void load16(Pack16<T>& v, const T* src, bool aligned32) {
+  if (aligned32) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v.raw[0].x), "=r"(v.raw[0].y), "=r"(v.raw[0].z), "=r"(v.raw[0].w),
+                   "=r"(v.raw[1].x), "=r"(v.raw[1].y), "=r"(v.raw[1].z), "=r"(v.raw[1].w)
+                 : "l"(src));
+  } else {
+    v.raw[0] = __ldg(reinterpret_cast<const uint4*>(src));
+    v.raw[1] = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+  }
+}
 
 // BLOCK = elements per scale (16: NVFP4 / ue4m3, 32: MXFP4 / ue8m0).
+//
+// One CTA owns 128 rows x 128 columns.  A thread owns 16 consecutive elements of a row: for
+// NVFP4 that is a whole scale block, so the block maximum needs no shuffle and the scale is
+// computed once (the reference computes it twice, in both threads of a pair,
+// kernel/nvfp4_utils.cuh:170-216); for MXFP4 two neighbouring threads share a block.  Each thread
+// issues its four row segments' loads before touching any of them.  The tile's scale bytes (two
+// 512-byte chunks for NVFP4, one for MXFP4) are staged in shared memory and stored with 16-byte
+// stores; packed nibbles leave as 8 bytes per thread, 64 contiguous bytes per row.
 template <typename T, int BLOCK>
 __global__ void __launch_bounds__(kThreads)
 quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __restrict__ gs_ptr,
                  uint8_t* __restrict__ out, uint8_t* __restrict__ sf_out, int m, int n,
-                 int num_k_tiles, int mx_rounding) {
-  constexpr int kTileCols = 4 * BLOCK;              // one scale chunk = 4 scale columns
-  constexpr int kThreadsPerRow = kTileCols / 8;     // 8 elements (16 bytes) per thread
-  constexpr int kRowsPerPass = kThreads / kThreadsPerRow;
-  constexpr int kPasses = kTileRows / kRowsPerPass;
-  constexpr int kBatch = 4;                         // loads in flight per thread
-  constexpr int kThreadsPerBlock = BLOCK / 8;       // threads sharing one scale
-  static_assert(kPasses % kBatch == 0, "pass count");
+                 int num_col_tiles, int num_k_chunks, int mx_rounding, int aligned32) {
+  constexpr int kThreadsPerRow = kTileCols / 16;                    // 8
+  constexpr int kRowsPerPass = kThreads / kThreadsPerRow;           // 32
+  constexpr int kPasses = kTileRows / kRowsPerPass;                 // 4: all in flight at once
+  constexpr int kThreadsPerBlock = BLOCK / 16;                      // 1 or 2 threads per scale
+  constexpr int kChunksPerTile = kTileCols / (4 * BLOCK);           // 2 or 1 scale chunks per tile
 
-  __shared__ __align__(16) uint8_t sf_stage[512];
+  __shared__ __align__(16) uint8_t sf_stage[kChunksPerTile * 512];
 
-  const int kt = blockIdx.x % num_k_tiles;
-  const int mt = blockIdx.x / num_k_tiles;
+  const int ct = blockIdx.x % num_col_tiles;
+  const int mt = blockIdx.x / num_col_tiles;
   const int tid = threadIdx.x;
   const int row_in_pass = tid / kThreadsPerRow;
-  const int col = kt * kTileCols + (tid % kThreadsPerRow) * 8;
-  const int sf_col_in_chunk = (tid % kThreadsPerRow) / kThreadsPerBlock;   // 0..3
+  const int seg = tid % kThreadsPerRow;
+  const int col = ct * kTileCols + seg * 16;
+  const int sf_col_in_tile = seg / kThreadsPerBlock;                // 0..7 (NVFP4) or 0..3 (MXFP4)
   const bool col_ok = col < n;
 
   float gs = 1.0f, rcp_gs = 1.0f;
@@ -140,55 +170,67 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
   // match) uses the correctly rounded constant so that a CPU restatement is exact.
   const float rcp6 = BLOCK == 16 ? rcp_approx_ftz(6.0f) : __uint_as_float(0x3E2AAAABu);
 
+  Pack16<T> v[kPasses];
 #pragma unroll
-  for (int b = 0; b < kPasses / kBatch; ++b) {
-    Pack8<T> v[kBatch];
+  for (int p = 0; p < kPasses; ++p) {
+    const int row = mt * kTileRows + p * kRowsPerPass + row_in_pass;
+    v[p].raw[0] = make_uint4(0u, 0u, 0u, 0u);
+    v[p].raw[1] = make_uint4(0u, 0u, 0u, 0u);
+    if (col_ok && row < m) load16<T>(v[p], in + (int64_t)row * in_stride + col, aligned32 != 0);
+  }
 #pragma unroll
-    for (int p = 0; p < kBatch; ++p) {
-      const int row = mt * kTileRows + (b * kBatch + p) * kRowsPerPass + row_in_pass;
-      v[p].raw = make_uint4(0u, 0u, 0u, 0u);
-      if (col_ok && row < m)
-        v[p].raw = __ldg(reinterpret_cast<const uint4*>(in + (int64_t)row * in_stride + col));
-    }
+  for (int p = 0; p < kPasses; ++p) {
+    const int row_in_tile = p * kRowsPerPass + row_in_pass;
+    const int row = mt * kTileRows + row_in_tile;
+    auto mx2 = __habs2(v[p].h2[0]);
 #pragma unroll
-    for (int p = 0; p < kBatch; ++p) {
-      const int row_in_tile = (b * kBatch + p) * kRowsPerPass + row_in_pass;
-      const int row = mt * kTileRows + row_in_tile;
-      auto mx2 = local_absmax2<T>(v[p]);
+    for (int i = 1; i < 8; ++i) mx2 = __hmax2(mx2, __habs2(v[p].h2[i]));
 #pragma unroll
-      for (int s = 1; s < kThreadsPerBlock; s <<= 1)
-        mx2 = __hmax2(__shfl_xor_sync(0xffffffffu, mx2, s), mx2);
-      const float amax = to_float<T>(__hmax(mx2.x, mx2.y));
+    for (int s = 1; s < kThreadsPerBlock; s <<= 1)
+      mx2 = __hmax2(__shfl_xor_sync(0xffffffffu, mx2, s), mx2);
+    const float amax = to_float<T>(__hmax(mx2.x, mx2.y));
 
-      uint8_t sf_byte;
-      float out_scale;
-      if (BLOCK == 16) {
-        const float sf_value = mul_ftz(gs, mul_ftz(amax, rcp6));
-        sf_byte = (uint8_t)__nv_cvt_float_to_fp8(sf_value, __NV_SATFINITE, __NV_E4M3);
-        const float sf_q = __half2float(__half(__nv_cvt_fp8_to_halfraw(sf_byte, __NV_E4M3)));
-        out_scale = sf_q != 0.0f ? rcp_approx_ftz(mul_ftz(sf_q, rcp_gs)) : 0.0f;
-      } else {
-        const float sf_value = mul_ftz(amax, rcp6);
-        const uint32_t bits = __float_as_uint(sf_value);
-        uint32_t e = (bits >> 23) & 0xffu;
-        if (mx_rounding == NVFP_MX_ROUND_CEIL && (bits & 0x7fffffu) != 0 && e < 254) e += 1;
-        e = min(e, 254u);
-        if (sf_value != sf_value) e = 255u;
-        sf_byte = (uint8_t)e;
-        out_scale = (e > 0 && e < 254) ? __uint_as_float((254u - e) << 23) : 0.0f;
-      }
-
-      const uint32_t packed = scale_and_pack<T>(v[p], out_scale);
-      if (col_ok && row < m)
-        *reinterpret_cast<uint32_t*>(out + (int64_t)row * (n / 2) + col / 2) = packed;
-      if (tid % kThreadsPerBlock == 0)
-        sf_stage[(row_in_tile % 32) * 16 + (row_in_tile / 32) * 4 + sf_col_in_chunk] = sf_byte;
+    uint8_t sf_byte;
+    float out_scale;
+    if (BLOCK == 16) {
+      const float sf_value = mul_ftz(gs, mul_ftz(amax, rcp6));
+      sf_byte = (uint8_t)__nv_cvt_float_to_fp8(sf_value, __NV_SATFINITE, __NV_E4M3);
+      const float sf_q = __half2float(__half(__nv_cvt_fp8_to_halfraw(sf_byte, __NV_E4M3)));
+      out_scale = sf_q != 0.0f ? rcp_approx_ftz(mul_ftz(sf_q, rcp_gs)) : 0.0f;
+    } else {
+      const float sf_value = mul_ftz(amax, rcp6);
+      const uint32_t bits = __float_as_uint(sf_value);
+      uint32_t e = (bits >> 23) & 0xffu;
+      if (mx_rounding == NVFP_MX_ROUND_CEIL && (bits & 0x7fffffu) != 0 && e < 254) e += 1;
+      e = min(e, 254u);
+      if (sf_value != sf_value) e = 255u;
+      sf_byte = (uint8_t)e;
+      out_scale = (e > 0 && e < 254) ? __uint_as_float((254u - e) << 23) : 0.0f;
     }
+
+    float2 f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      f[i] = to_float2<T>(v[p].h2[i]);
+      f[i].x = mul_ftz(f[i].x, out_scale);
+      f[i].y = mul_ftz(f[i].y, out_scale);
+    }
+    uint2 packed;
+    packed.x = cvt_e2m1x8(f[0].x, f[0].y, f[1].x, f[1].y, f[2].x, f[2].y, f[3].x, f[3].y);
+    packed.y = cvt_e2m1x8(f[4].x, f[4].y, f[5].x, f[5].y, f[6].x, f[6].y, f[7].x, f[7].y);
+    if (col_ok && row < m)
+      *reinterpret_cast<uint2*>(out + (int64_t)row * (n / 2) + col / 2) = packed;
+    if (seg % kThreadsPerBlock == 0)
+      sf_stage[(sf_col_in_tile / 4) * 512 + (row_in_tile % 32) * 16 + (row_in_tile / 32) * 4 +
+               (sf_col_in_tile % 4)] = sf_byte;
   }
   __syncthreads();
-  if (tid < 32) {
-    uint4* dst = reinterpret_cast<uint4*>(sf_out + ((int64_t)mt * num_k_tiles + kt) * 512);
-    dst[tid] = reinterpret_cast<const uint4*>(sf_stage)[tid];
+  if (tid < 32 * kChunksPerTile) {
+    const int chunk = ct * kChunksPerTile + tid / 32;
+    if (chunk < num_k_chunks) {
+      uint4* dst = reinterpret_cast<uint4*>(sf_out + ((int64_t)mt * num_k_chunks + chunk) * 512);
+      dst[tid % 32] = reinterpret_cast<const uint4*>(sf_stage)[tid];
+    }
   }
 }
 
@@ -205,12 +247,21 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
   const int64_t vec_per_row = n / 8;
   const int64_t total = m * vec_per_row;
   typename Vec2<T>::type mx2 = zero2<T>();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / vec_per_row, c = i % vec_per_row;
-    Pack8<T> v;
-    v.raw = __ldg(reinterpret_cast<const uint4*>(in + row * in_stride + c * 8));
-    mx2 = __hmax2(mx2, local_absmax2<T>(v));
+  // four independent 16-byte loads in flight per thread per iteration
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += 4 * step) {
+    Pack8<T> v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t j = i + u * step;
+      v[u].raw = make_uint4(0u, 0u, 0u, 0u);
+      if (j < total) {
+        const int64_t row = j / vec_per_row, c = j % vec_per_row;
+        v[u].raw = __ldg(reinterpret_cast<const uint4*>(in + row * in_stride + c * 8));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mx2 = __hmax2(mx2, local_absmax2<T>(v[u]));
   }
   float mx = to_float<T>(__hmax(mx2.x, mx2.y));
 #pragma unroll
@@ -256,22 +307,24 @@ int launch_quant(void* out_fp4, void* out_sf, const void* in, const float* gs, i
                  int64_t stride, int dtype, int rounding, cudaStream_t stream) {
   if (int rc = check_16bit_input(in, m, n, stride, dtype, BLOCK)) return rc;
   NVFP_REQUIRE(out_fp4 != nullptr && out_sf != nullptr, "output pointer is null");
-  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(out_fp4) & 3) == 0 &&
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(out_fp4) & 7) == 0 &&
                    (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0,
-               "outputs must be aligned (fp4: 4 bytes, scales: 16 bytes)");
+               "outputs must be aligned (fp4: 8 bytes, scales: 16 bytes)");
   if (m == 0 || n == 0) return NVFP_OK;
-  const int64_t m_tiles = ceil_div(m, 128);
-  const int64_t k_tiles = ceil_div(n, 4 * BLOCK);
-  NVFP_REQUIRE(m_tiles * k_tiles < (1ll << 31), "too many tiles");
-  const dim3 grid((unsigned)(m_tiles * k_tiles));
+  const int64_t m_tiles = ceil_div(m, kTileRows);
+  const int64_t col_tiles = ceil_div(n, kTileCols);
+  const int64_t k_chunks = ceil_div(n / BLOCK, 4);
+  NVFP_REQUIRE(m_tiles * col_tiles < (1ll << 31), "too many tiles");
+  const dim3 grid((unsigned)(m_tiles * col_tiles));
+  const int aligned32 = (reinterpret_cast<uintptr_t>(in) % 32 == 0 && stride % 16 == 0) ? 1 : 0;
   if (dtype == NVFP_DTYPE_F16) {
     quant_fp4_kernel<__half, BLOCK><<<grid, kThreads, 0, stream>>>(
         static_cast<const __half*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
-        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)k_tiles, rounding);
+        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32);
   } else {
     quant_fp4_kernel<__nv_bfloat16, BLOCK><<<grid, kThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
-        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)k_tiles, rounding);
+        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32);
   }
   NVFP_CUDA(cudaGetLastError());
   return NVFP_OK;
