@@ -215,8 +215,8 @@ def main_ours(args, rank: int, world: int, local_rank: int):
         return float(t.item())
 
     sampler = ClockSampler(local_rank)
-    launches_per_step = 6 + (1 if world > 1 else 0)   # memset, amax, finish, quantize, alpha, gemm (+ all-gather)
-    own_kernels_per_step = 5                           # amax, finish, quantize, alpha, gemm
+    launches_per_step = 5 + (1 if world > 1 else 0)   # memset, amax, quantize, alpha, gemm (+ all-gather)
+    own_kernels_per_step = 4                           # amax, quantize, alpha, gemm
 
     for _ in range(max(3, args.warmup)):
         step(a)
@@ -238,23 +238,27 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     # ---- region 2: the same steps with events between the kernels (kernel breakdown) ---
     # calls the same ops QuantLinear.forward makes, one by one
     ks = min(args.steps, 200)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(ks)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(ks)]
+    w_sf = layer.weight_sf.view(torch.float8_e4m3fn)
     with sampler:
         barrier()
         for i in range(ks):
+            # each window holds exactly one of the big kernels; the small ones (alpha) sit outside, and the
+            # host enqueues ahead of the GPU so that no launch gap falls inside a window
             ev[i][0].record()
             a_gs = nv.global_scale(a)
             ev[i][1].record()
-            a_fp4, a_sf = nv.scaled_fp4_quant(a, a_gs)
-            ev[i][2].record()
             alpha = nv.alpha_from_scales(a_gs, layer.weight_global_scale)
-            y = nv.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, layer.weight_sf.view(torch.float8_e4m3fn),
-                                         alpha, torch.bfloat16)
+            ev[i][2].record()
+            a_fp4, a_sf = nv.scaled_fp4_quant(a, a_gs)
             ev[i][3].record()
+            ev[i][4].record()
+            y = nv.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+            ev[i][5].record()
         barrier()
     t_amax = statistics.mean(ev[i][0].elapsed_time(ev[i][1]) for i in range(ks))
-    t_quant = statistics.mean(ev[i][1].elapsed_time(ev[i][2]) for i in range(ks))
-    t_gemm = statistics.mean(ev[i][2].elapsed_time(ev[i][3]) for i in range(ks))
+    t_quant = statistics.mean(ev[i][2].elapsed_time(ev[i][3]) for i in range(ks))
+    t_gemm = statistics.mean(ev[i][4].elapsed_time(ev[i][5]) for i in range(ks))
     gemm_tflops = 2.0 * M * N_PER_GPU * K / (t_gemm * 1e-3) / 1e12
     quant_bytes = M * K * 2.5625
     quant_gbs = quant_bytes / (t_quant * 1e-3) / 1e9
@@ -305,7 +309,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
                     "quant_frac_of_nominal_8tbs": quant_gbs / NOMINAL_HBM_GBS,
                     "amax_ms": t_amax, "amax_gbs": amax_gbs},
         "roofline": {"bound": "tensor", "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
-                     "frac": gemm_tflops / fp4_peak, "traffic": None, "kernel": "fp4_gemm_kernel",
+                     "frac": gemm_tflops / fp4_peak, "traffic": None, "kernel": "fp4_gemm_pair_kernel",
                      "peak_basis": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s); "
                                    "no FP4 peak is measured on this pool",
                      "frac_of_nominal_9pflops": gemm_tflops / NOMINAL_FP4_TFLOPS,

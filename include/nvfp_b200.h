@@ -112,8 +112,9 @@ int nvfp_reciprocal_approximate_ftz(float* out, const float* in, int64_t count, 
  * Per-tensor global scale  gs = rcp(max|x|) * (448 * 6)  (both steps correctly rounded fp32,
  * which is how torch evaluates `2688 / amax`) as one fp32 on the device.
  * Replaces the torch sequence abs().max() -> 2688/amax of speed_test.py:40-41,46-47
- * and nvfp/pseudo_quant.py:94-96 with two kernels and no temporary.
- *   amax_bits  device scratch, one uint32; the call resets it on the stream first.
+ * and nvfp/pseudo_quant.py:94-96 with one kernel (the last block to finish forms the scale) and no temporary.
+ *   amax_bits  device scratch, TWO uint32 (8 bytes, 8-byte aligned); the call resets them on the stream
+ *              first; afterwards word 0 holds the bit pattern of max|x| as fp32.
  *   gs_out     device, one fp32; amax == 0 gives gs = 2688 (amax treated as 1,
  *              as in test_refactor.py:21-25).
  */

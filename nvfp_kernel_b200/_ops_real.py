@@ -133,7 +133,7 @@ def global_scale(input: torch.Tensor, scratch: torch.Tensor | None = None) -> to
         x = x.contiguous()
     out = torch.empty(1, dtype=torch.float32, device=input.device)
     if scratch is None:
-        scratch = torch.empty(1, dtype=torch.int32, device=input.device)
+        scratch = torch.empty(2, dtype=torch.int32, device=input.device)
     ext = _load_scaled_fp4_ops(("global_scale",))
     ext.global_scale(out, scratch, x)
     return out

@@ -148,7 +148,7 @@ void global_scale(torch::Tensor& gs_out, torch::Tensor& scratch, torch::Tensor c
   TORCH_CHECK(input.dim() == 2 && input.stride(1) == 1, "input must be a matrix with dense rows");
   TORCH_CHECK(gs_out.is_cuda() && scratch.is_cuda() && input.is_cuda(), "all tensors must be CUDA tensors");
   TORCH_CHECK(gs_out.scalar_type() == at::ScalarType::Float && gs_out.numel() >= 1, "gs_out must be fp32");
-  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 4, "scratch must hold 4 bytes");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 8, "scratch must hold 8 bytes");
   const int dt = dtype_code(input, "Unsupported input data type for global_scale.");
   const at::cuda::OptionalCUDAGuard guard(device_of(input));
   check_status(nvfp_global_scale(static_cast<float*>(gs_out.data_ptr()),

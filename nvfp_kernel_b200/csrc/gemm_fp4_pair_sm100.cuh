@@ -237,21 +237,32 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int row = tm * kPairBM + (int)rank * 128 + q * 32 + lane;
       const bool odd = (it & 1) != 0;
       const uint32_t t_row = tmem_base + (odd ? C::kOddAccCol : 0u) + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int i = 0; i < kPairBN / 32; ++i) {
-        // even tiles drain from the last chunk down, odd tiles from the first up: either way the
-        // columns shared with the other accumulator go first
-        const int c = odd ? i : kPairBN / 32 - 1 - i;
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        if (i == C::kEarlyChunks - 1) {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-        }
+      // Even tiles drain from the last 32-column chunk down, odd tiles from the first up: either way the
+      // columns shared with the other accumulator go first.  They are pulled into registers and the
+      // accumulator is handed back BEFORE anything is stored, so the next tile's MMAs start early.
+      auto chunk_at = [&](int i) { return odd ? i : kPairBN / 32 - 1 - i; };
+      auto store_chunk = [&](int c, const uint32_t (&r)[32]) {
         const int col = tn * kPairBN + c * 32;
         if (row < p.m && col < p.n) store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha);
+      };
+      static_assert(C::kEarlyChunks == 2, "two early chunks are held in registers");
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(t_row + chunk_at(0) * 32, r0);
+        tmem_ld_32x32b_x32(t_row + chunk_at(1) * 32, r1);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        store_chunk(chunk_at(0), r0);
+        store_chunk(chunk_at(1), r1);
+      }
+#pragma unroll 1
+      for (int i = C::kEarlyChunks; i < kPairBN / 32; ++i) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + chunk_at(i) * 32, r);
+        tmem_ld_wait();
+        store_chunk(chunk_at(i), r);
       }
     }
   }

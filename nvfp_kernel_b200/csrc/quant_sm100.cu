@@ -243,7 +243,7 @@ __global__ void rcp_kernel(float* __restrict__ out, const float* __restrict__ in
 // order like unsigned integers).
 template <typename T>
 __global__ void __launch_bounds__(256)
-amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, uint32_t* amax_bits) {
+amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, uint32_t* scratch, float* gs_out) {
   const int64_t vec_per_row = n / 8;
   const int64_t total = m * vec_per_row;
   typename Vec2<T>::type mx2 = zero2<T>();
@@ -273,16 +273,33 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
     float r = warp_max[0];
 #pragma unroll
     for (int w = 1; w < 8; ++w) r = fmaxf(r, warp_max[w]);
-    atomicMax(amax_bits, __float_as_uint(r));
+    // scratch[0] = running maximum (fp32 bits), scratch[1] = number of blocks that have contributed
+    atomicMax(&scratch[0], __float_as_uint(r));
+    __threadfence();
+    if (atomicAdd(&scratch[1], 1u) == gridDim.x - 1) {
+      // last block: every contribution is visible; finish here instead of in a second launch
+      __threadfence();
+      float amax = __uint_as_float(*reinterpret_cast<volatile uint32_t*>(&scratch[0]));
+      if (amax == 0.0f) amax = 1.0f;
+      // torch evaluates `2688 / amax` (scalar / tensor) as reciprocal(amax) * 2688: two roundings.
+      // The reference forms its global scales that way (speed_test.py:41,47; nvfp/pseudo_quant.py:94-96).
+      *gs_out = __fmul_rn(__frcp_rn(amax), 448.0f * 6.0f);
+      scratch[1] = 0u;
+    }
   }
 }
 
-__global__ void finish_global_scale_kernel(float* gs_out, const uint32_t* amax_bits) {
-  float amax = __uint_as_float(*amax_bits);
-  if (amax == 0.0f) amax = 1.0f;
-  // torch evaluates `2688 / amax` (scalar / tensor) as reciprocal(amax) * 2688: two roundings.
-  // The reference forms its global scales that way (speed_test.py:41,47; nvfp/pseudo_quant.py:94-96).
-  *gs_out = __fmul_rn(__frcp_rn(amax), 448.0f * 6.0f);
+template <typename T>
+int launch_amax(float* gs_out, uint32_t* scratch, const void* in, int64_t m, int64_t n, int64_t stride,
+                cudaStream_t stream) {
+  DeviceInfo info;
+  if (int rc = current_device_info(&info)) return rc;
+  NVFP_CUDA(cudaMemsetAsync(scratch, 0, 2 * sizeof(uint32_t), stream));
+  const int64_t want = ceil_div(m * (n / 8), 256 * 4);
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 8));
+  amax_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out);
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
 }
 
 __global__ void alpha_kernel(float* alpha_out, const float* gs_a, const float* gs_b) {
@@ -371,22 +388,9 @@ extern "C" int nvfp_global_scale(float* gs_out, uint32_t* amax_bits, const void*
   if (int rc = check_16bit_input(in, m, n, in_row_stride, in_dtype, 8)) return rc;
   NVFP_REQUIRE(gs_out != nullptr && amax_bits != nullptr, "null pointer");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  NVFP_CUDA(cudaMemsetAsync(amax_bits, 0, sizeof(uint32_t), stream));
-  if (m > 0 && n > 0) {
-    DeviceInfo info;
-    if (int rc = current_device_info(&info)) return rc;
-    const int64_t vecs = m * (n / 8);
-    const int64_t want = ceil_div(vecs, 256 * 4);
-    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 8));
-    if (in_dtype == NVFP_DTYPE_F16)
-      amax_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(in), in_row_stride, m, n, amax_bits);
-    else
-      amax_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), in_row_stride, m, n, amax_bits);
-    NVFP_CUDA(cudaGetLastError());
-  }
-  finish_global_scale_kernel<<<1, 1, 0, stream>>>(gs_out, amax_bits);
-  NVFP_CUDA(cudaGetLastError());
-  return NVFP_OK;
+  return in_dtype == NVFP_DTYPE_F16
+             ? launch_amax<__half>(gs_out, amax_bits, in, m, n, in_row_stride, stream)
+             : launch_amax<__nv_bfloat16>(gs_out, amax_bits, in, m, n, in_row_stride, stream);
 }
 
 extern "C" int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const float* gs_b,
@@ -412,7 +416,7 @@ extern "C" int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const
 // current) and handed to the kernels.
 namespace nvfp {
 namespace {
-constexpr int kNoAllocScratchWords = 64;              // one 256-byte line; word 0 holds the amax bits
+constexpr int kNoAllocScratchWords = 64;              // one 256-byte line; words 0-1: amax bits, block counter
 constexpr int64_t kNoAllocMaxElements = 1ll << 32;    // largest tensor this entry point accepts
 static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocScratchWords];
 
@@ -448,20 +452,8 @@ extern "C" int nvfp_global_scale_noalloc(float* gs_out, const void* in, int64_t 
   uint32_t* scratch = nullptr;
   if (int rc = noalloc_scratch_address(&scratch)) return rc;    // first call on a device: symbol look-up
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  // the array keeps the previous call's maximum: clear the word this call reduces into
-  NVFP_CUDA(cudaMemsetAsync(scratch, 0, sizeof(uint32_t), stream));
-  if (m > 0 && n > 0) {
-    DeviceInfo info;
-    if (int rc = current_device_info(&info)) return rc;
-    const int64_t want = ceil_div(m * (n / 8), 256 * 4);
-    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 8));
-    if (in_dtype == NVFP_DTYPE_F16)
-      amax_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(in), in_row_stride, m, n, scratch);
-    else
-      amax_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), in_row_stride, m, n, scratch);
-    NVFP_CUDA(cudaGetLastError());
-  }
-  finish_global_scale_kernel<<<1, 1, 0, stream>>>(gs_out, scratch);
-  NVFP_CUDA(cudaGetLastError());
-  return NVFP_OK;
+  // the array keeps the previous call's contents: launch_amax clears the two words it uses, on the stream
+  return in_dtype == NVFP_DTYPE_F16
+             ? launch_amax<__half>(gs_out, scratch, in, m, n, in_row_stride, stream)
+             : launch_amax<__nv_bfloat16>(gs_out, scratch, in, m, n, in_row_stride, stream);
 }

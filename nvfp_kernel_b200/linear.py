@@ -125,10 +125,11 @@ class QuantLinear(nn.Module):
             # every rank must quantize its K-slice with the scale of the WHOLE activation:
             # max-reduce the per-rank amax bit patterns (non-negative floats order like ints)
             import torch.distributed as dist
-            scratch = torch.empty(1, dtype=torch.int32, device=x2.device)
+            scratch = torch.empty(2, dtype=torch.int32, device=x2.device)
             ops.global_scale(x2, scratch)
-            dist.all_reduce(scratch, op=dist.ReduceOp.MAX, group=self.process_group)
-            amax = scratch.view(torch.float32)
+            bits = scratch[:1]                       # word 0: fp32 bit pattern of this rank's amax
+            dist.all_reduce(bits, op=dist.ReduceOp.MAX, group=self.process_group)
+            amax = bits.view(torch.float32)
             amax = torch.where(amax == 0, torch.ones_like(amax), amax)
             return (448.0 * 6.0) / amax
         return ops.global_scale(x2)

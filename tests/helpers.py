@@ -62,7 +62,7 @@ def capi_mm(a, b, sfa, sfb, alpha, out_dtype=torch.bfloat16, mx: bool = False):
 def capi_global_scale(x: torch.Tensor) -> torch.Tensor:
     lib = _capi.load()
     gs = torch.empty(1, dtype=torch.float32, device=x.device)
-    scratch = torch.empty(1, dtype=torch.int32, device=x.device)
+    scratch = torch.empty(2, dtype=torch.int32, device=x.device)
     m, n = x.shape
     _capi.check(lib.nvfp_global_scale(gs.data_ptr(), scratch.data_ptr(), x.data_ptr(), m, n,
                                       x.stride(0) if m > 1 else n, _dt(x.dtype), _stream()))
