@@ -152,8 +152,11 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
 
   __shared__ __align__(16) uint8_t sf_stage[kChunksPerTile * 512];
 
-  const int ct = blockIdx.x % num_col_tiles;
-  const int mt = blockIdx.x / num_col_tiles;
+  // Tiles are walked from the END of the tensor backwards: the global-scale pass that normally runs
+  // just before this kernel reads the tensor front to back, so its tail is what the L2 still holds.
+  const int tile = (int)(gridDim.x - 1 - blockIdx.x);
+  const int ct = tile % num_col_tiles;
+  const int mt = tile / num_col_tiles;
   const int tid = threadIdx.x;
   const int row_in_pass = tid / kThreadsPerRow;
   const int seg = tid % kThreadsPerRow;
@@ -240,28 +243,34 @@ __global__ void rcp_kernel(float* __restrict__ out, const float* __restrict__ in
 }
 
 // max |x| over the tensor -> atomicMax on the fp32 bit pattern (non-negative floats
-// order like unsigned integers).
-template <typename T>
+// order like unsigned integers).  VEC = elements per load: 16 (one 32-byte load, needs 32-byte
+// aligned rows) or 8.  Every thread keeps four loads in flight; the grid sweeps the tensor front
+// to back.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, uint32_t* scratch, float* gs_out) {
-  const int64_t vec_per_row = n / 8;
+  const int64_t vec_per_row = n / VEC;
   const int64_t total = m * vec_per_row;
   typename Vec2<T>::type mx2 = zero2<T>();
-  // four independent 16-byte loads in flight per thread per iteration
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += 4 * step) {
-    Pack8<T> v[4];
+    Pack16<T> v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int64_t j = i + u * step;
-      v[u].raw = make_uint4(0u, 0u, 0u, 0u);
+      v[u].raw[0] = make_uint4(0u, 0u, 0u, 0u);
+      v[u].raw[1] = make_uint4(0u, 0u, 0u, 0u);
       if (j < total) {
         const int64_t row = j / vec_per_row, c = j % vec_per_row;
-        v[u].raw = __ldg(reinterpret_cast<const uint4*>(in + row * in_stride + c * 8));
+        const T* src = in + row * in_stride + c * VEC;
+        if (VEC == 16) load16<T>(v[u], src, true);
+        else v[u].raw[0] = __ldg(reinterpret_cast<const uint4*>(src));
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) mx2 = __hmax2(mx2, local_absmax2<T>(v[u]));
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int e = 0; e < VEC / 2; ++e) mx2 = __hmax2(mx2, __habs2(v[u].h2[e]));
   }
   float mx = to_float<T>(__hmax(mx2.x, mx2.y));
 #pragma unroll
@@ -295,9 +304,13 @@ int launch_amax(float* gs_out, uint32_t* scratch, const void* in, int64_t m, int
   DeviceInfo info;
   if (int rc = current_device_info(&info)) return rc;
   NVFP_CUDA(cudaMemsetAsync(scratch, 0, 2 * sizeof(uint32_t), stream));
-  const int64_t want = ceil_div(m * (n / 8), 256 * 4);
-  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 8));
-  amax_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out);
+  const bool wide = n % 16 == 0 && stride % 16 == 0 && reinterpret_cast<uintptr_t>(in) % 32 == 0;
+  const int64_t want = ceil_div(m * (n / (wide ? 16 : 8)), 256 * 4);
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 5));
+  if (wide)
+    amax_kernel<T, 16><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out);
+  else
+    amax_kernel<T, 8><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out);
   NVFP_CUDA(cudaGetLastError());
   return NVFP_OK;
 }
