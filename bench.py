@@ -181,7 +181,12 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     gw = torch.Generator(device=dev).manual_seed(1000 + rank)
     w_local = torch.randn((N_PER_GPU, K), generator=gw, device=dev, dtype=torch.float32).to(torch.bfloat16)
 
-    layer = QuantLinear(K, N_PER_GPU, device=dev)          # this rank's column slab
+    if world > 1:
+        # this rank's column slab of a column-parallel layer; the gather is fused into the GEMM epilogue
+        # (peer stores over NVLink) unless --gather nccl asks for the all-gather collective
+        layer = QuantLinear(K, n_total, parallel="column", fused_gather=(args.gather == "fused"), device=dev)
+    else:
+        layer = QuantLinear(K, N_PER_GPU, device=dev)
     if world > 1:
         # one global weight scale for the whole [n_total, K] weight, as a 1-GPU layer would use
         amax = w_local.float().abs().max().reshape(1)
@@ -194,11 +199,12 @@ def main_ours(args, rank: int, world: int, local_rank: int):
         layer.load_weight(w_local)
     del w_local
     gathered = torch.empty((world * M, N_PER_GPU), dtype=torch.bfloat16, device=dev) if world > 1 else None
+    layer.gather_output = args.gather == "fused"
 
     def step(x):
-        y = layer(x)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, y)
+        y = layer(x)                     # fused gather: already the full [M, n_total] matrix
+        if world > 1 and args.gather == "nccl":
+            dist.all_gather_into_tensor(gathered, y)     # layout [world, M, N/world]
             return gathered
         return y
 
@@ -253,7 +259,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
             a_fp4, a_sf = nv.scaled_fp4_quant(a, a_gs)
             ev[i][3].record()
             ev[i][4].record()
-            y = nv.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+            y = nv.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, alpha, torch.bfloat16)   # local slab only
             ev[i][5].record()
         barrier()
     t_amax = statistics.mean(ev[i][0].elapsed_time(ev[i][1]) for i in range(ks))
@@ -266,14 +272,14 @@ def main_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- region 3: end to end through the public API with host buffers -----------------
     a_host = a.cpu().pin_memory()
-    out_host = torch.empty((world * M, N_PER_GPU), dtype=torch.bfloat16).pin_memory()   # gather layout [world, M, N/world]
+    out_host = torch.empty((world * M * N_PER_GPU,), dtype=torch.bfloat16).pin_memory()   # the gathered result
     a_dev = torch.empty_like(a)
     e2e_steps = max(3, min(args.steps, 20))
 
     def e2e_step():
         a_dev.copy_(a_host, non_blocking=True)
         y = step(a_dev)
-        out_host.copy_(y, non_blocking=True)
+        out_host.copy_(y.reshape(-1), non_blocking=True)
 
     for _ in range(2):
         e2e_step()
@@ -302,7 +308,8 @@ def main_ours(args, rank: int, world: int, local_rank: int):
         "config": {"workload": f"nvfp4_quant_linear_M{M}_N{N_PER_GPU}x{world}_K{K}",
                    "step": "amax->global scale, NVFP4 quantize of the bf16 activation, alpha, FP4 GEMM, bf16 out"
                            + (", all-gather of outputs (column-parallel)" if world > 1 else ""),
-                   "parallelism": f"column-parallel x{world}" if world > 1 else "single GPU",
+                   "parallelism": (f"column-parallel x{world}, gather " + ("fused into the GEMM epilogue (peer stores)"
+                                   if args.gather == "fused" else "by NCCL all-gather")) if world > 1 else "single GPU",
                    "l2": "no flush: bf16 activation (134 MB) + output (134 MB) per step exceed the 126 MB L2"},
         "kernels": {"gemm_ms": t_gemm, "gemm_tflops": gemm_tflops, "quant_ms": t_quant, "quant_gbs": quant_gbs,
                     "quant_frac_of_measured_hbm": quant_gbs / peaks["hbm_gbs"],
@@ -335,6 +342,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N>1 only: how the column-parallel outputs are gathered")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

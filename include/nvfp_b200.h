@@ -102,6 +102,22 @@ int nvfp_mxfp4_mm(void* d, const void* a, const void* b, const void* sfa, const 
                   const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, void* stream);
 
 /*
+ * The same GEMM with the [m, n] result written to n_dst (1..8) destinations instead of one, each a
+ * row-major matrix with leading dimension dst_ld elements (>= n, multiple of 8), so that a slab can land
+ * directly in its columns of a wider gathered matrix: dst[0] is
+ * normally local memory, the others point into PEER GPUs' memory (peer-mapped addresses, e.g. of a
+ * symmetric buffer).  This is the column-parallel layer's all-gather fused into the GEMM epilogue:
+ * every output tile leaves shared memory once per destination as a TMA store, over NVLink for peers,
+ * while the next tile is being computed.  The caller synchronises the ranks around the call (nobody
+ * may still read a destination when the call starts; readers wait until every writer's stream has
+ * passed the call).  mxfp4 != 0 selects 32-element blocks with ue8m0 scales.  The reference has no
+ * distributed code; there is no counterpart.
+ */
+int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void* a, const void* b, const void* sfa,
+                             const void* sfb, const float* alpha, int64_t m, int64_t n, int64_t k,
+                             int64_t dst_ld, int out_dtype, int mxfp4, void* stream);
+
+/*
  * y[i] = rcp.approx.ftz.f32(x[i]).  Replaces reciprocal_approximate_ftz_tensor
  * (kernel/reciprocal_kernels.h:4-5, kernel/reciprocal_kernels.cu:91-121); fp32 only,
  * the one dtype reachable through the reference's Python wrapper (nvfp/ops.py:87-92).

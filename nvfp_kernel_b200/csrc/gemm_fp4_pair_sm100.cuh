@@ -29,8 +29,11 @@ struct PairCfg {
   static constexpr uint32_t kSfaBytes = kChunksPerStage * 512;
   static constexpr uint32_t kSfbBytes = 2 * kChunksPerStage * 512;           // both 128-row tiles of B scales
   static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = (kSmemLimit - 2048) / kStageBytes;
-  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 2048;
+  // epilogue staging: per epilogue warp two buffers of 32 rows x 128 bytes (128-byte swizzle)
+  static constexpr uint32_t kStoreBufBytes = 32 * 128;
+  static constexpr uint32_t kStagingBytes = 4 * 2 * kStoreBufBytes;
+  static constexpr int kStages = (kSmemLimit - 2048 - kStagingBytes) / kStageBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + 2048;
   // Tensor-memory columns.  Two 256-column accumulators do not fit beside the scale columns, so they
   // OVERLAP: even tiles accumulate in [0,256), odd tiles in [208,464), scales live in [464,512).  The
   // epilogue drains the shared columns [208,256) first and releases the accumulator barrier right
@@ -44,15 +47,23 @@ struct PairCfg {
   static_assert(kOddAccCol % 16 == 0 && kOddAccCol + 32 * kEarlyChunks >= kPairBN, "overlap covered by the early chunks");
 };
 
+// Output tensor maps: entry 0 is this GPU's [M, N] output; further entries are the same-shaped
+// destinations in peer GPUs' memory (column-parallel layers write their slab straight into every
+// peer's gathered buffer instead of running an all-gather afterwards).
+constexpr int kMaxOutputs = 8;
+struct OutMaps {
+  CUtensorMap map[kMaxOutputs];
+};
+
 template <bool MX, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                     const GemmParams p) {
+                     const __grid_constant__ OutMaps out_maps, const int n_out, const GemmParams p) {
   using C = PairCfg<MX>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kStagingBytes);
   constexpr int kFull = 0, kEmpty = C::kStages, kAccFull = 2 * C::kStages, kAccEmpty = kAccFull + 1,
                 kDrain = kAccEmpty + 1, kNumBars = kDrain + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
@@ -221,10 +232,16 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue ---
+    // Accumulator -> registers (tcgen05.ld) -> x alpha -> OutT -> swizzled staging buffer in shared
+    // memory -> one TMA store per destination.  A warp owns 32 rows and stores 128 bytes of each per step.
+    constexpr int kCols = 128 / (int)sizeof(OutT);          // columns per store: 64 (16-bit) or 32 (fp32)
+    constexpr int kSteps = kPairBN / kCols;
+    constexpr int kEarlySteps = 64 / kCols;                  // steps that cover the 48 shared columns
     const int q = warp & 3;
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
-    OutT* d = static_cast<OutT*>(p.d);
     const uint32_t acc_empty_leader = map_to_cta(bar(kAccEmpty), 0);
+    const uint32_t staging = smem_base + C::kStages * C::kStageBytes + (uint32_t)(warp - 2) * 2 * C::kStoreBufBytes;
+    uint32_t store_count = 0;
     int it = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
@@ -234,37 +251,57 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         break;
       }
       tc_fence_after_sync();
-      const int row = tm * kPairBM + (int)rank * 128 + q * 32 + lane;
+      const int row0 = tm * kPairBM + (int)rank * 128 + q * 32;
       const bool odd = (it & 1) != 0;
       const uint32_t t_row = tmem_base + (odd ? C::kOddAccCol : 0u) + ((uint32_t)(q * 32) << 16);
-      // Even tiles drain from the last 32-column chunk down, odd tiles from the first up: either way the
-      // columns shared with the other accumulator go first.  They are pulled into registers and the
-      // accumulator is handed back BEFORE anything is stored, so the next tile's MMAs start early.
-      auto chunk_at = [&](int i) { return odd ? i : kPairBN / 32 - 1 - i; };
-      auto store_chunk = [&](int c, const uint32_t (&r)[32]) {
-        const int col = tn * kPairBN + c * 32;
-        if (row < p.m && col < p.n) store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha);
-      };
-      static_assert(C::kEarlyChunks == 2, "two early chunks are held in registers");
-      {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(t_row + chunk_at(0) * 32, r0);
-        tmem_ld_32x32b_x32(t_row + chunk_at(1) * 32, r1);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-        store_chunk(chunk_at(0), r0);
-        store_chunk(chunk_at(1), r1);
-      }
 #pragma unroll 1
-      for (int i = C::kEarlyChunks; i < kPairBN / 32; ++i) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + chunk_at(i) * 32, r);
+      for (int i = 0; i < kSteps; ++i) {
+        // Even tiles drain from the last columns down, odd tiles from the first up: either way the
+        // columns shared with the other accumulator are read first, and the accumulator is handed
+        // back as soon as they are in registers, so the next tile's MMAs start early.
+        const int c = odd ? i : kSteps - 1 - i;
+        uint32_t r[kCols];
+#pragma unroll
+        for (int h = 0; h < kCols / 32; ++h)
+          tmem_ld_32x32b_x32(t_row + c * kCols + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[h * 32]));
         tmem_ld_wait();
-        store_chunk(chunk_at(i), r);
+        if (i == kEarlySteps - 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        }
+        // the buffer used two steps ago must have been read out by its TMA store
+        const uint32_t buf = staging + (store_count & 1u) * C::kStoreBufBytes;
+        if (lane == 0) bulk_wait_group_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {     // eight 16-byte pieces of this thread's 128-byte row
+          uint4 o;
+          if constexpr (sizeof(OutT) == 4) {
+            o.x = __float_as_uint(__uint_as_float(r[4 * j + 0]) * alpha);
+            o.y = __float_as_uint(__uint_as_float(r[4 * j + 1]) * alpha);
+            o.z = __float_as_uint(__uint_as_float(r[4 * j + 2]) * alpha);
+            o.w = __float_as_uint(__uint_as_float(r[4 * j + 3]) * alpha);
+          } else {
+            o.x = pack2<OutT>(__uint_as_float(r[8 * j + 0]) * alpha, __uint_as_float(r[8 * j + 1]) * alpha);
+            o.y = pack2<OutT>(__uint_as_float(r[8 * j + 2]) * alpha, __uint_as_float(r[8 * j + 3]) * alpha);
+            o.z = pack2<OutT>(__uint_as_float(r[8 * j + 4]) * alpha, __uint_as_float(r[8 * j + 5]) * alpha);
+            o.w = pack2<OutT>(__uint_as_float(r[8 * j + 6]) * alpha, __uint_as_float(r[8 * j + 7]) * alpha);
+          }
+          st_shared_v4(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4), o);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          for (int o = 0; o < n_out; ++o)
+            tma_store_2d(&out_maps.map[o], buf, tn * kPairBN + c * kCols, row0);
+          bulk_commit_group();
+        }
+        ++store_count;
       }
     }
+    if (lane == 0) bulk_wait_group<0>();    // all stores performed before the CTA may exit
+    __syncwarp();
   }
 
   // -------------------------------------------------------------- common exit ---
@@ -292,8 +329,28 @@ inline int make_scale_map(CUtensorMap* map, const void* base, int64_t k_chunks, 
   return NVFP_OK;
 }
 
+// Row-major [rows, cols] output of OutT; box = 128 bytes x 32 rows, 128-byte swizzle.
+template <typename OutT>
+int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(OutT)};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / sizeof(OutT)), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = sizeof(OutT) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : std::is_same<OutT, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = enc(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
+  return NVFP_OK;
+}
+
+// `outputs`: n_out destination matrices [m, n] with leading dimension ld; outputs[0] is normally p.d.
 template <bool MX, typename OutT>
-int launch_pair(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream) {
+int launch_pair(const GemmParams& base, const void* a, const void* b, void* const* outputs, int n_out,
+                int64_t ld, int sm_count, cudaStream_t stream) {
   using C = PairCfg<MX>;
   GemmParams p = base;
   p.tiles_m = (int)ceil_div(p.m, kPairBM);
@@ -303,6 +360,10 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, int sm_cou
   if (int rc = make_operand_map(&map_b, b, p.n, p.k, 128)) return rc;
   if (int rc = make_scale_map(&map_sfa, p.sfa, p.sf_k_chunks, ceil_div(p.m, 128), C::kChunksPerStage, 1)) return rc;
   if (int rc = make_scale_map(&map_sfb, p.sfb, p.sf_k_chunks, ceil_div(p.n, 128), C::kChunksPerStage, 2)) return rc;
+  OutMaps out_maps;
+  memset(&out_maps, 0, sizeof(out_maps));
+  for (int o = 0; o < n_out; ++o)
+    if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], p.m, p.n, ld)) return rc;
   auto kernel = fp4_gemm_pair_kernel<MX, OutT>;
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
@@ -319,6 +380,6 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, int sm_cou
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, p));
+  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, out_maps, n_out, p));
   return NVFP_OK;
 }

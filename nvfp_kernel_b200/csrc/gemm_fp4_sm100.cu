@@ -20,7 +20,9 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "common.h"
 #include "ptx_sm100.cuh"
@@ -370,9 +372,18 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
 
 #include "gemm_fp4_pair_sm100.cuh"
 
+// `outputs`: n_out destination matrices [m, n] (row-major, out_dtype); more than one only for the
+// column-parallel gather, where the extra ones are peer GPUs' buffers.
 template <bool MX>
-int scaled_mm(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream) {
+  NVFP_REQUIRE(outputs != nullptr && n_out >= 1 && n_out <= kMaxOutputs,
+               "between 1 and %d output matrices are supported, got %d", kMaxOutputs, n_out);
+  for (int o = 0; o < n_out; ++o)
+    NVFP_REQUIRE(outputs[o] != nullptr && (reinterpret_cast<uintptr_t>(outputs[o]) & 15) == 0,
+                 "output %d is null or not 16-byte aligned", o);
+  NVFP_REQUIRE(ld >= n && ld % 8 == 0, "leading dimension %lld must be >= n and a multiple of 8", (long long)ld);
+  void* d = outputs[0];
   constexpr int kBlock = MX ? 32 : 16;
   constexpr int kAlign = MX ? 64 : 32;
   NVFP_REQUIRE(m >= 0 && n >= 0 && k >= 0, "negative shape");
@@ -406,11 +417,11 @@ int scaled_mm(void* d, const void* a, const void* b, const void* sfa, const void
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
   // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
   const int64_t pair_tiles = ceil_div(m, kPairBM) * ceil_div(n, kPairBN);
-  if (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2) {
+  if (n_out > 1 || ld != n || (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2)) {
     switch (out_dtype) {
-      case NVFP_DTYPE_BF16: return launch_pair<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream);
-      case NVFP_DTYPE_F16: return launch_pair<MX, __half>(p, a, b, info.sm_count, stream);
-      default: return launch_pair<MX, float>(p, a, b, info.sm_count, stream);
+      case NVFP_DTYPE_BF16: return launch_pair<MX, __nv_bfloat16>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
+      case NVFP_DTYPE_F16: return launch_pair<MX, __half>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
+      default: return launch_pair<MX, float>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
     }
   }
   // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a
@@ -440,12 +451,20 @@ extern "C" int nvfp_scaled_fp4_mm(void* d, const void* a, const void* b, const v
                                   const void* sfb, const float* alpha, int64_t m, int64_t n,
                                   int64_t k, int out_dtype, void* stream) {
   clear_error();
-  return scaled_mm<false>(d, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
+  return scaled_mm<false>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nvfp_mxfp4_mm(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
                              const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype,
                              void* stream) {
   clear_error();
-  return scaled_mm<true>(d, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
+  return scaled_mm<true>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void* a, const void* b,
+                                        const void* sfa, const void* sfb, const float* alpha, int64_t m,
+                                        int64_t n, int64_t k, int64_t dst_ld, int out_dtype, int mxfp4, void* stream) {
+  clear_error();
+  return mxfp4 ? scaled_mm<true>(dst, n_dst, dst_ld, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream))
+               : scaled_mm<false>(dst, n_dst, dst_ld, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
 }

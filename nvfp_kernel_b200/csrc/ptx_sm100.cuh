@@ -216,6 +216,32 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 }
 
 
+
+// ------------------------------------------------------------- TMA stores ---
+// 2-D tiled store shared -> global (this GPU's memory or a peer's); out-of-range parts of the box
+// are dropped.  Completion is tracked by the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src_smem), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until at most N of this thread's bulk groups are still READING shared memory.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until at most N of this thread's bulk groups are incomplete (writes performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // ------------------------------------------------- CTA pairs (cta_group::2) ---
 // A cluster of two CTAs on one TPC issues one MMA of M = 256: each CTA holds its 128
 // rows of A, its half of the B rows, and its 128 lanes of the accumulator.

@@ -22,7 +22,8 @@ class QuantLinear(nn.Module):
     def __init__(self, in_features: int, out_features: int, bias: bool = False, mode: str = "real",
                  format: str = "nvfp4", parallel: str | None = None, process_group=None,
                  out_dtype: torch.dtype = torch.bfloat16, mx_rounding: str = "rceil",
-                 gather_output: bool = True, input_is_parallel: bool = False, device=None):
+                 gather_output: bool = True, input_is_parallel: bool = False, fused_gather: bool = False,
+                 device=None):
         super().__init__()
         if mode != "real":
             raise ValueError(f"mode={mode!r}: only the real-kernel path exists (no emulation, no pseudo-quant fallback)")
@@ -35,6 +36,10 @@ class QuantLinear(nn.Module):
         self.parallel, self.process_group = parallel, process_group
         self.out_dtype, self.mx_rounding = out_dtype, mx_rounding
         self.gather_output, self.input_is_parallel = gather_output, input_is_parallel
+        # column-parallel only: the GEMM epilogue writes this rank's slab into every rank's gathered
+        # buffer over NVLink instead of running an all-gather afterwards (see peer.py)
+        self.fused_gather = fused_gather and parallel == "column"
+        self._gather_buffers = {}
         self.world, self.rank = 1, 0
         if parallel is not None:
             import torch.distributed as dist
@@ -99,6 +104,8 @@ class QuantLinear(nn.Module):
             lo, hi = shard_range(self.in_features, self.rank, self.world, 4 * self.block, "in_features")
             x2 = x2[:, lo:hi]
         acc_dtype = torch.float32 if self.parallel == "row" and self.world > 1 else self.out_dtype
+        if self.fused_gather and self.world > 1 and self.gather_output:
+            return self._forward_fused_gather(x2, lead)
         if self.format == "nvfp4":
             a_gs = self._activation_global_scale(x2)
             a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
@@ -112,6 +119,33 @@ class QuantLinear(nn.Module):
         if self.bias is not None:
             y = y + (self.bias if y.shape[-1] == self.out_features else self._bias_shard())
         return y.reshape(*lead, y.shape[-1]) if y.shape[0] == x2.shape[0] else y
+
+    def _forward_fused_gather(self, x2: torch.Tensor, lead) -> torch.Tensor:
+        """Column-parallel forward whose result is the gathered [M, N] matrix; the returned tensor
+        aliases a peer-visible buffer that the next call with the same M overwrites."""
+        from ._ops_real import _load_scaled_fp4_ops
+        from .peer import GatherBuffer
+        m = x2.shape[0]
+        gb = self._gather_buffers.get(m)
+        if gb is None:
+            gb = self._gather_buffers[m] = GatherBuffer(m, self.n_local, self.out_dtype, x2.device, self.process_group)
+        ext = _load_scaled_fp4_ops(("scaled_fp4_mm_multi",))
+        code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[self.out_dtype]
+        if self.format == "nvfp4":
+            a_gs = self._activation_global_scale(x2)
+            a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
+            alpha = ops.alpha_from_scales(a_gs, self.weight_global_scale)
+        else:
+            a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
+            alpha = None
+        gb.barrier()          # every rank has finished reading the previous contents
+        ext.scaled_fp4_mm_multi(gb.dst_ptrs, gb.ld, code, a_fp4, self.weight_fp4, a_sf.view(torch.uint8), self.weight_sf,
+                                alpha, self.format == "mxfp4")
+        gb.barrier()          # every rank's slab has arrived
+        y = gb.gathered()
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*lead, y.shape[-1])
 
     def _mm_f32(self, a_fp4, a_sf, alpha):
         from ._ops_real import _load_scaled_fp4_ops
