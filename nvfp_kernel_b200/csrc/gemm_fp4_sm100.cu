@@ -371,6 +371,7 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
 }
 
 #include "gemm_fp4_pair_sm100.cuh"
+#include "gemm_fp4_skinny_sm100.cuh"
 
 // `outputs`: n_out destination matrices [m, n] (row-major, out_dtype); more than one only for the
 // column-parallel gather, where the extra ones are peer GPUs' buffers.
@@ -415,6 +416,14 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.sfb_row_tiles = (int)ceil_div(n, 128);
   p.status = device_status_word();
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
+  // Few activation rows (decode): weights are streamed once; swap the operands and split K over a cluster.
+  if (n_out == 1 && ld == n && m <= kSkinnyMaxTokens && k >= 8192 && ceil_div(n, 128) * 2 <= info.sm_count) {
+    switch (out_dtype) {
+      case NVFP_DTYPE_BF16: return launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream);
+      case NVFP_DTYPE_F16: return launch_skinny<MX, __half>(p, a, b, info.sm_count, stream);
+      default: return launch_skinny<MX, float>(p, a, b, info.sm_count, stream);
+    }
+  }
   // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
   const int64_t pair_tiles = ceil_div(m, kPairBM) * ceil_div(n, kPairBN);
   if (n_out > 1 || ld != n || (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2)) {

@@ -101,6 +101,22 @@ def test_edge_shapes_vs_cpu_oracle(m, n, k):
         check_gemm(out.cpu(), torch.from_numpy(ref))
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 96, 8192), (17, 128, 8448), (48, 4096, 14336), (64, 160, 9216)])
+@pytest.mark.parametrize("mx", [False, True])
+def test_split_k_cluster_path_for_few_rows_and_long_k(m, n, k, mx):
+    """Shapes the dispatcher sends to the swap-operands / cluster split-K kernel."""
+    a, w = gemm_inputs(m, n, k, seed=m + k, w_std=0.05)
+    if mx:
+        a_fp4, a_sf = capi_mx_quant(a.cuda())
+        w_fp4, w_sf = capi_mx_quant(w.cuda())
+        alpha = None
+    else:
+        a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
+        out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, dt, mx=mx)
+        check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha, block=32 if mx else 16, ue8m0=mx))
+
+
 def test_config1_vs_reference_pseudo_quant_path():
     """BASELINE config 1 (1024^3, seed 0): real path vs the port of the reference's torch
     pseudo-quant path on CPU (oracle/pseudo_path.py, itself pinned to the reference's output)."""
