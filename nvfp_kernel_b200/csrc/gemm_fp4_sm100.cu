@@ -238,7 +238,11 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint32_t st = smem_base + s * C::kStageBytes;
           const uint32_t sf_slot = tmem_base + C::kSfColBase + (kc & 1u) * C::kSfSlotCols;
           const uint32_t sfa_tmem = sf_slot, sfb_tmem = sf_slot + C::kSfaCols;
-          // scales: shared -> tensor memory, one 512-byte chunk (128 rows x 4 scales) per copy
+          // scales: shared -> tensor memory, one 512-byte chunk (128 rows x 4 scales) per copy, each
+          // chunk's copies queued right before the MMAs that consume them so that later copies run
+          // under earlier MMAs
+          const uint64_t a_desc = make_smem_desc(st, 16, 1024, 2);
+          const uint64_t b_desc = make_smem_desc(st + C::kABytes, 16, 1024, 2);
           for (int c = 0; c < chunks; ++c) {
             tc_copy_sf_32x128b_warpx4(
                 sfa_tmem + 4 * c,
@@ -248,22 +252,21 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                   sfb_tmem + 4 * (c * C::kHalves + h),
                   make_smem_desc(st + C::kABytes + C::kBBytes + C::kSfaBytes +
                                      (h * C::kChunksPerStage + c) * 512, 0, 128, 0));
-          }
-          const uint64_t a_desc = make_smem_desc(st, 16, 1024, 2);
-          const uint64_t b_desc = make_smem_desc(st + C::kABytes, 16, 1024, 2);
-          for (int j = 0; j < mmas; ++j) {
-            const uint32_t accumulate = (ks | j) != 0 ? 1u : 0u;
-            const uint64_t koff = (uint64_t)((j * (kMmaK / 2)) >> 4);   // 32 bytes of K per MMA
-            const int c = j / C::kMmasPerChunk;
-            if (MX) {
-              const uint32_t sf_id = (uint32_t)(j % C::kMmasPerChunk) * 2u;
-              tc_mma_mxf4(d_tmem, a_desc + koff, b_desc + koff,
-                          make_idesc_fp4_block_scaled(kBM, BN, true, sf_id, sf_id),
-                          sfa_tmem + 4 * c, sfb_tmem + 4 * c * C::kHalves, accumulate);
-            } else {
-              tc_mma_nvf4(d_tmem, a_desc + koff, b_desc + koff,
-                          make_idesc_fp4_block_scaled(kBM, BN, false),
-                          sfa_tmem + 4 * c, sfb_tmem + 4 * c * C::kHalves, accumulate);
+            for (int jj = 0; jj < C::kMmasPerChunk; ++jj) {
+              const int j = c * C::kMmasPerChunk + jj;
+              if (j >= mmas) break;
+              const uint32_t accumulate = (ks | j) != 0 ? 1u : 0u;
+              const uint64_t koff = (uint64_t)((j * (kMmaK / 2)) >> 4);   // 32 bytes of K per MMA
+              if (MX) {
+                const uint32_t sf_id = (uint32_t)jj * 2u;
+                tc_mma_mxf4(d_tmem, a_desc + koff, b_desc + koff,
+                            make_idesc_fp4_block_scaled(kBM, BN, true, sf_id, sf_id),
+                            sfa_tmem + 4 * c, sfb_tmem + 4 * c * C::kHalves, accumulate);
+              } else {
+                tc_mma_nvf4(d_tmem, a_desc + koff, b_desc + koff,
+                            make_idesc_fp4_block_scaled(kBM, BN, false),
+                            sfa_tmem + 4 * c, sfb_tmem + 4 * c * C::kHalves, accumulate);
+              }
             }
           }
           tc_commit(bar(kEmpty + s));   // stage reusable once these MMAs have read it

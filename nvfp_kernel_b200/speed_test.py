@@ -1,0 +1,108 @@
+"""Timing tables for the FP4 path, after the reference's speed_test.py.
+
+    python -m nvfp_kernel_b200.speed_test                 # BF16 torch.mm vs FP4 (online activation quantize + GEMM)
+    python -m nvfp_kernel_b200.speed_test --table decode  # Llama-3-8B decode shapes, M in {1, 16, 128}
+    python -m nvfp_kernel_b200.speed_test --table quant   # quantizer alone, GB/s
+
+The first table is the reference's sweep (speed_test.py:56-98 there): M = --batch_size (default 4096),
+K = N = size, weight quantized once, activation amax + quantize + GEMM timed per call.  Differences:
+CUDA events instead of torch.utils.benchmark, an L2 flush between timed calls, and the FP4 TFLOPS column is
+computed from the FP4 time (the reference divides by the BF16 time, speed_test.py:94, so its two TFLOPS
+columns are equal).
+"""
+from __future__ import annotations
+
+import argparse
+import statistics
+
+import torch
+
+from . import QuantLinear, ops
+
+_FLUSH = None
+
+
+def _flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def time_us(fn, repeats: int, flush: bool = True) -> float:
+    """Median device time of fn() in microseconds (CUDA events, 5 warm-up calls)."""
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(repeats):
+        if flush:
+            _flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(times)
+
+
+def sweep(batch_size: int, repeats: int):
+    print(f"{'Size (K=N)':<10} {'BF16 (us)':<12} {'FP4 (us)':<12} {'Speedup':<10} {'BF16 TFLOPS':<14} {'FP4 TFLOPS':<12}")
+    print("-" * 74)
+    for size in (64, 128, 256, 512, 1024, 2048, 4096, 8192):
+        m, k, n = batch_size, size, size
+        a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
+        w = torch.randn(n, k, dtype=torch.bfloat16, device="cuda")
+        wt = w.t().contiguous()
+        flops = 2.0 * m * k * n
+        t_bf16 = time_us(lambda: torch.mm(a, wt), repeats)
+        layer = QuantLinear(k, n, device="cuda").load_weight(w)
+        t_fp4 = time_us(lambda: layer(a), repeats)
+        print(f"{size:<10} {t_bf16:<12.1f} {t_fp4:<12.1f} {t_bf16 / t_fp4:<10.2f} "
+              f"{flops / t_bf16 / 1e6:<14.1f} {flops / t_fp4 / 1e6:<12.1f}")
+
+
+def decode(repeats: int):
+    print(f"{'M':<5} {'K':<7} {'N':<7} {'GEMM (us)':<11} {'GB/s':<9} {'forward (us)':<13}")
+    print("-" * 56)
+    for m in (1, 16, 128):
+        for k, n in ((4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)):
+            a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
+            w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+            layer = QuantLinear(k, n, device="cuda").load_weight(w)
+            gs = ops.global_scale(a)
+            a_fp4, a_sf = ops.scaled_fp4_quant(a, gs)
+            alpha = ops.alpha_from_scales(gs, layer.weight_global_scale)
+            w_sf = layer.weight_sf.view(torch.float8_e4m3fn)
+            t_mm = time_us(lambda: ops.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, alpha, torch.bfloat16),
+                           repeats)
+            t_fwd = time_us(lambda: layer(a), repeats)
+            nbytes = n * k * 0.5625 + m * k * 0.5625 + 2.0 * m * n
+            print(f"{m:<5} {k:<7} {n:<7} {t_mm:<11.1f} {nbytes / t_mm / 1e3:<9.0f} {t_fwd:<13.1f}")
+
+
+def quant(repeats: int):
+    print(f"{'M':<7} {'K':<7} {'quantize (us)':<15} {'GB/s (2.5625 B/elt)':<20} {'amax (us)':<10}")
+    print("-" * 62)
+    for m, k in ((1, 4096), (128, 4096), (4096, 4096), (8192, 8192), (8192, 28672)):
+        a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
+        gs = ops.global_scale(a)
+        t_q = time_us(lambda: ops.scaled_fp4_quant(a, gs), repeats)
+        t_a = time_us(lambda: ops.global_scale(a), repeats)
+        print(f"{m:<7} {k:<7} {t_q:<15.1f} {m * k * 2.5625 / t_q / 1e3:<20.0f} {t_a:<10.1f}")
+
+
+def main():
+    ap = argparse.ArgumentParser(description="BF16 GEMM vs FP4 GEMM with online activation quantization")
+    ap.add_argument("--batch_size", type=int, default=4096, help="M dimension of the sweep")
+    ap.add_argument("--repeats", type=int, default=50)
+    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant"])
+    args = ap.parse_args()
+    torch.cuda.empty_cache()
+    {"sweep": lambda: sweep(args.batch_size, args.repeats), "decode": lambda: decode(args.repeats),
+     "quant": lambda: quant(args.repeats)}[args.table]()
+
+
+if __name__ == "__main__":
+    main()
