@@ -138,6 +138,18 @@ int nvfp_global_scale(float* gs_out, uint32_t* amax_bits, const void* in, int64_
                       int64_t in_row_stride, int in_dtype, void* stream);
 
 /*
+ * One launch for everything the activation side of a layer needs before quantizing (the reference
+ * spends 4-5 launches on it, speed_test.py:46-49): gs_out = rcp(max|x|) * 2688 and
+ * alpha_out = 1 / (gs_out * gs_weight[0]).
+ *   scratch  EIGHT uint32 (32 bytes), zeroed ONCE by the caller before the first use and then left
+ *            alone: the kernel keeps two (maximum, counter) pairs and a toggle in it and cleans up
+ *            after itself, so no memset runs between calls.  Calls sharing a scratch must be ordered
+ *            on one stream.
+ */
+int nvfp_activation_scales(float* gs_out, float* alpha_out, uint32_t* scratch, const void* in, int64_t m,
+                           int64_t n, int64_t in_row_stride, int in_dtype, const float* gs_weight, void* stream);
+
+/*
  * Same result as nvfp_global_scale, for callers that cannot hand over scratch memory because
  * they may not allocate any: code running under an engine whose device allocator is closed
  * after warm-up, or on host threads where cudaMalloc is forbidden.  No counterpart in the

@@ -1,6 +1,7 @@
 """B200-native NVFP4 / MXFP4 quantize-and-GEMM: drop-in for the `nvfp` package of
 huweim/nvfp_kernel on its real-kernel path (nvfp/__init__.py:1-27 there)."""
 from .ops import (
+    activation_scales,
     alpha_from_scales,
     cutlass_scaled_fp4_mm,
     device_status,
@@ -22,6 +23,7 @@ __all__ = [
     "mxfp4_scaled_mm",
     "global_scale",
     "alpha_from_scales",
+    "activation_scales",
     "device_status",
     "QuantLinear",
 ]

@@ -139,6 +139,22 @@ def global_scale(input: torch.Tensor, scratch: torch.Tensor | None = None) -> to
     return out
 
 
+def activation_scales(input: torch.Tensor, gs_weight: torch.Tensor, scratch: torch.Tensor):
+    """(gs, alpha) = (2688/max|input|, 1/(gs*gs_weight)) in ONE launch.  `scratch`: 8 int32 on the device,
+    zeroed once by the caller (torch.zeros) and then reused for every call on the same stream."""
+    assert input.is_cuda, "input must be a CUDA tensor"
+    assert input.dtype in (torch.float16, torch.bfloat16), f"input.dtype needs to be fp16 or bf16 but got {input.dtype}."
+    x = input.reshape(1 if input.ndim == 1 else -1, input.shape[-1])
+    assert x.shape[-1] % 8 == 0, f"last dim has to be multiple of 8, but got {x.shape[-1]}."
+    if x.stride(-1) != 1 or (x.shape[0] > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    out = torch.empty(2, dtype=torch.float32, device=input.device)
+    gs, alpha = out[:1], out[1:]
+    ext = _load_scaled_fp4_ops(("activation_scales",))
+    ext.activation_scales(gs, alpha, scratch, x, gs_weight)
+    return gs, alpha
+
+
 def alpha_from_scales(gs_a: torch.Tensor, gs_b: torch.Tensor) -> torch.Tensor:
     out = torch.empty(1, dtype=torch.float32, device=gs_a.device)
     ext = _load_scaled_fp4_ops(("alpha_from_scales",))

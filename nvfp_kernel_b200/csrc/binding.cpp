@@ -179,6 +179,22 @@ void global_scale(torch::Tensor& gs_out, torch::Tensor& scratch, torch::Tensor c
                                  current_stream(input)));
 }
 
+void activation_scales(torch::Tensor& gs_out, torch::Tensor& alpha_out, torch::Tensor& scratch,
+                       torch::Tensor const& input, torch::Tensor const& gs_weight) {
+  TORCH_CHECK(input.dim() == 2 && input.stride(1) == 1, "input must be a matrix with dense rows");
+  TORCH_CHECK(gs_out.is_cuda() && alpha_out.is_cuda() && scratch.is_cuda() && input.is_cuda() && gs_weight.is_cuda(),
+              "all tensors must be CUDA tensors");
+  TORCH_CHECK(gs_out.scalar_type() == at::ScalarType::Float && alpha_out.scalar_type() == at::ScalarType::Float &&
+                  gs_weight.scalar_type() == at::ScalarType::Float, "scales must be fp32");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 32, "scratch must hold 32 bytes");
+  const int dt = dtype_code(input, "Unsupported input data type for activation_scales.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_status(nvfp_activation_scales(static_cast<float*>(gs_out.data_ptr()), static_cast<float*>(alpha_out.data_ptr()),
+                                      static_cast<uint32_t*>(scratch.data_ptr()), input.data_ptr(), input.size(0),
+                                      input.size(1), input.size(0) > 1 ? input.stride(0) : input.size(1), dt,
+                                      static_cast<const float*>(gs_weight.data_ptr()), current_stream(input)));
+}
+
 void alpha_from_scales(torch::Tensor& alpha_out, torch::Tensor const& gs_a, torch::Tensor const& gs_b) {
   TORCH_CHECK(alpha_out.is_cuda() && gs_a.is_cuda() && gs_b.is_cuda(), "all tensors must be CUDA tensors");
   TORCH_CHECK(alpha_out.scalar_type() == at::ScalarType::Float && gs_a.scalar_type() == at::ScalarType::Float &&
@@ -206,6 +222,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mxfp4_scaled_mm", &mxfp4_scaled_mm);
   m.def("scaled_fp4_mm_multi", &scaled_fp4_mm_multi);
   m.def("global_scale", &global_scale);
+  m.def("activation_scales", &activation_scales);
   m.def("alpha_from_scales", &alpha_from_scales);
   m.def("device_status", &device_status);
 }

@@ -248,7 +248,10 @@ __global__ void rcp_kernel(float* __restrict__ out, const float* __restrict__ in
 // to back.
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
-amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, uint32_t* scratch, float* gs_out) {
+amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, uint32_t* scratch, float* gs_out,
+            uint32_t* toggle, const float* gs_other, float* alpha_out) {
+  // self-cleaning mode: scratch holds two (maximum, counter) pairs; *toggle says which one this launch uses
+  if (toggle) scratch += 2u * (*reinterpret_cast<volatile uint32_t*>(toggle) & 1u);
   const int64_t vec_per_row = n / VEC;
   const int64_t total = m * vec_per_row;
   typename Vec2<T>::type mx2 = zero2<T>();
@@ -292,25 +295,40 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
       if (amax == 0.0f) amax = 1.0f;
       // torch evaluates `2688 / amax` (scalar / tensor) as reciprocal(amax) * 2688: two roundings.
       // The reference forms its global scales that way (speed_test.py:41,47; nvfp/pseudo_quant.py:94-96).
-      *gs_out = __fmul_rn(__frcp_rn(amax), 448.0f * 6.0f);
+      const float gs = __fmul_rn(__frcp_rn(amax), 448.0f * 6.0f);
+      *gs_out = gs;
+      if (alpha_out) *alpha_out = __fdiv_rn(1.0f, __fmul_rn(gs, *gs_other));     // speed_test.py:49 of the reference
       scratch[1] = 0u;
+      if (toggle) {
+        // leave the OTHER pair clean for the next launch and point the toggle at it: no memset between calls
+        const uint32_t t = *toggle & 1u;
+        uint32_t* other = scratch + (t ? -2 : 2);
+        other[0] = 0u;
+        other[1] = 0u;
+        __threadfence();
+        *toggle = t ^ 1u;
+      }
     }
   }
 }
 
 template <typename T>
 int launch_amax(float* gs_out, uint32_t* scratch, const void* in, int64_t m, int64_t n, int64_t stride,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool self_cleaning = false, const float* gs_other = nullptr,
+                float* alpha_out = nullptr) {
   DeviceInfo info;
   if (int rc = current_device_info(&info)) return rc;
-  NVFP_CUDA(cudaMemsetAsync(scratch, 0, 2 * sizeof(uint32_t), stream));
+  uint32_t* toggle = self_cleaning ? scratch + 4 : nullptr;
+  if (!self_cleaning) NVFP_CUDA(cudaMemsetAsync(scratch, 0, 2 * sizeof(uint32_t), stream));
   const bool wide = n % 16 == 0 && stride % 16 == 0 && reinterpret_cast<uintptr_t>(in) % 32 == 0;
   const int64_t want = ceil_div(m * (n / (wide ? 16 : 8)), 256 * 4);
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 5));
   if (wide)
-    amax_kernel<T, 16><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out);
+    amax_kernel<T, 16><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out, toggle,
+                                                 gs_other, alpha_out);
   else
-    amax_kernel<T, 8><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out);
+    amax_kernel<T, 8><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out, toggle,
+                                                gs_other, alpha_out);
   NVFP_CUDA(cudaGetLastError());
   return NVFP_OK;
 }
@@ -404,6 +422,18 @@ extern "C" int nvfp_global_scale(float* gs_out, uint32_t* amax_bits, const void*
   return in_dtype == NVFP_DTYPE_F16
              ? launch_amax<__half>(gs_out, amax_bits, in, m, n, in_row_stride, stream)
              : launch_amax<__nv_bfloat16>(gs_out, amax_bits, in, m, n, in_row_stride, stream);
+}
+
+extern "C" int nvfp_activation_scales(float* gs_out, float* alpha_out, uint32_t* scratch, const void* in,
+                                      int64_t m, int64_t n, int64_t in_row_stride, int in_dtype,
+                                      const float* gs_weight, void* stream_) {
+  clear_error();
+  if (int rc = check_16bit_input(in, m, n, in_row_stride, in_dtype, 8)) return rc;
+  NVFP_REQUIRE(gs_out && alpha_out && scratch && gs_weight, "null pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  return in_dtype == NVFP_DTYPE_F16
+             ? launch_amax<__half>(gs_out, scratch, in, m, n, in_row_stride, stream, true, gs_weight, alpha_out)
+             : launch_amax<__nv_bfloat16>(gs_out, scratch, in, m, n, in_row_stride, stream, true, gs_weight, alpha_out);
 }
 
 extern "C" int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const float* gs_b,

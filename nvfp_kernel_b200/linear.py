@@ -58,6 +58,8 @@ class QuantLinear(nn.Module):
         self.register_buffer("weight_fp4", torch.zeros((n_local, k_local // 2), dtype=torch.uint8, device=device))
         self.register_buffer("weight_sf", torch.zeros((rn, rk), dtype=torch.uint8, device=device))
         self.register_buffer("weight_global_scale", torch.ones(1, dtype=torch.float32, device=device))
+        # scratch of the fused amax -> (global scale, alpha) kernel: zeroed once, self-cleaning afterwards
+        self.register_buffer("_scale_scratch", torch.zeros(8, dtype=torch.int32, device=device), persistent=False)
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=out_dtype, device=device)) if bias else None
 
     # ------------------------------------------------------------------ weights ---
@@ -107,9 +109,8 @@ class QuantLinear(nn.Module):
         if self.fused_gather and self.world > 1 and self.gather_output:
             return self._forward_fused_gather(x2, lead)
         if self.format == "nvfp4":
-            a_gs = self._activation_global_scale(x2)
+            a_gs, alpha = self._activation_scales(x2)
             a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
-            alpha = ops.alpha_from_scales(a_gs, self.weight_global_scale)
             y = ops.cutlass_scaled_fp4_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha, acc_dtype) \
                 if acc_dtype != torch.float32 else self._mm_f32(a_fp4, a_sf, alpha)
         else:
@@ -132,9 +133,8 @@ class QuantLinear(nn.Module):
         ext = _load_scaled_fp4_ops(("scaled_fp4_mm_multi",))
         code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[self.out_dtype]
         if self.format == "nvfp4":
-            a_gs = self._activation_global_scale(x2)
+            a_gs, alpha = self._activation_scales(x2)
             a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
-            alpha = ops.alpha_from_scales(a_gs, self.weight_global_scale)
         else:
             a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
             alpha = None
@@ -153,6 +153,13 @@ class QuantLinear(nn.Module):
         _load_scaled_fp4_ops(("cutlass_scaled_fp4_mm",)).cutlass_scaled_fp4_mm(
             out, a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha)
         return out
+
+    def _activation_scales(self, x2: torch.Tensor):
+        """(gs_a, alpha): one launch, except for row-parallel layers whose amax needs an all-reduce."""
+        if self.parallel == "row" and self.world > 1:
+            a_gs = self._activation_global_scale(x2)
+            return a_gs, ops.alpha_from_scales(a_gs, self.weight_global_scale)
+        return ops.activation_scales(x2, self.weight_global_scale, self._scale_scratch)
 
     def _activation_global_scale(self, x2: torch.Tensor) -> torch.Tensor:
         if self.parallel == "row" and self.world > 1:

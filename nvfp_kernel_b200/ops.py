@@ -39,6 +39,7 @@ scaled_mxfp4_quant = _impl.scaled_mxfp4_quant
 mxfp4_scaled_mm = _impl.mxfp4_scaled_mm
 global_scale = _impl.global_scale
 alpha_from_scales = _impl.alpha_from_scales
+activation_scales = _impl.activation_scales
 
 
 def device_status() -> int:

@@ -195,6 +195,24 @@ def test_global_scale_matches_torch_formula(dt):
     assert capi_global_scale(z).item() == 2688.0
 
 
+def test_fused_activation_scales_repeated_calls():
+    """One launch for gs and alpha with a scratch that is zeroed once and cleans itself: many calls in a
+    row on tensors with rising and falling maxima must each equal the torch formulas of the reference
+    (speed_test.py:46-49)."""
+    import nvfp_kernel_b200 as nv
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    gs_w = torch.tensor([37.25], device="cuda")
+    for i, (dist, shape) in enumerate([("large", (300, 2048)), ("small", (129, 80)), ("normal", (1, 4096)),
+                                       ("abs_large", (1024, 1024)), ("small", (16, 16)), ("outliers", (4096, 512))] * 2):
+        x = make_input(dist, shape, torch.bfloat16 if i % 2 else torch.float16, seed=i).cuda()
+        gs, alpha = nv.activation_scales(x, gs_w, scratch)
+        a_scale = (448.0 * 6.0) / torch.abs(x).max().to(torch.float32)
+        assert gs.item() == a_scale.item(), (i, dist, shape)
+        assert alpha.item() == (1.0 / (a_scale * gs_w)).item(), (i, dist, shape)
+    z = torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda")
+    assert nv.activation_scales(z, gs_w, scratch)[0].item() == 2688.0
+
+
 @pytest.mark.parametrize("rounding", ["rceil", "floor"])
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
 def test_mxfp4_bit_exact_vs_cpu_restatement(rounding, dt):
