@@ -118,6 +118,19 @@ int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void* a, const v
                              int64_t dst_ld, int out_dtype, int mxfp4, void* stream);
 
 /*
+ * Row-parallel (K-split) layers: this rank's GEMM yields a PARTIAL [m, n] product; destination r
+ * (r = 0..n_dst-1, a [m / n_dst, n] fp32 matrix in rank r's memory, peer-mapped for r != own rank)
+ * owns rows [r*m/n_dst, (r+1)*m/n_dst) of the sum.  The epilogue adds every 32-row block of the
+ * partial product into its owner's matrix with a TMA reduction (fp32 add at the destination's memory,
+ * over NVLink for peers): the reduce-scatter fused into the GEMM.  The caller zeroes the destinations
+ * and synchronises the ranks before the call, and again before reading.  m % (32 * n_dst) == 0.
+ * No counterpart in the reference.
+ */
+int nvfp_scaled_fp4_mm_scatter_add(void* const* dst, int n_dst, const void* a, const void* b, const void* sfa,
+                                   const void* sfb, const float* alpha, int64_t m, int64_t n, int64_t k,
+                                   int mxfp4, void* stream);
+
+/*
  * y[i] = rcp.approx.ftz.f32(x[i]).  Replaces reciprocal_approximate_ftz_tensor
  * (kernel/reciprocal_kernels.h:4-5, kernel/reciprocal_kernels.cu:91-121); fp32 only,
  * the one dtype reachable through the reference's Python wrapper (nvfp/ops.py:87-92).

@@ -34,6 +34,7 @@ PROTOTYPES = {
     "nvfp_scaled_fp4_mm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_mxfp4_mm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_scaled_fp4_mm_multi": (_int, [ctypes.POINTER(ctypes.c_void_p), _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp]),
+    "nvfp_scaled_fp4_mm_scatter_add": (_int, [ctypes.POINTER(ctypes.c_void_p), _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_reciprocal_approximate_ftz": (_int, [_vp, _vp, _i64, _vp]),
     "nvfp_global_scale": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_activation_scales": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),

@@ -151,6 +151,26 @@ void scaled_fp4_mm_multi(std::vector<int64_t> const& dst_ptrs, int64_t dst_ld, i
                                         current_stream(A)));
 }
 
+// K-split partial product added into per-rank fp32 destinations (raw device addresses, one per rank):
+// the row-parallel reduce-scatter fused into the epilogue.
+void scaled_fp4_mm_scatter_add(std::vector<int64_t> const& dst_ptrs, torch::Tensor const& A, torch::Tensor const& B,
+                               torch::Tensor const& A_sf, torch::Tensor const& B_sf,
+                               c10::optional<torch::Tensor> const& alpha, bool mx) {
+  CHECK_OPERAND(A, at::ScalarType::Byte, "a");
+  CHECK_OPERAND(B, at::ScalarType::Byte, "b");
+  TORCH_CHECK(A_sf.is_cuda() && A_sf.is_contiguous() && B_sf.is_cuda() && B_sf.is_contiguous(),
+              "scales must be contiguous CUDA tensors");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.sizes()[1] == B.sizes()[1], "a and b shapes cannot be multiplied");
+  TORCH_CHECK(mx || alpha.has_value(), "alpha is required");
+  const int64_t m = A.sizes()[0], n = B.sizes()[0], k = A.sizes()[1] * 2;
+  std::vector<void*> dst;
+  for (int64_t p : dst_ptrs) dst.push_back(reinterpret_cast<void*>(p));
+  const at::cuda::OptionalCUDAGuard guard(device_of(A));
+  const float* alpha_ptr = alpha.has_value() ? static_cast<const float*>(alpha->data_ptr()) : nullptr;
+  check_status(nvfp_scaled_fp4_mm_scatter_add(dst.data(), (int)dst.size(), A.data_ptr(), B.data_ptr(), A_sf.data_ptr(),
+                                              B_sf.data_ptr(), alpha_ptr, m, n, k, mx ? 1 : 0, current_stream(A)));
+}
+
 // kernel/reciprocal_kernels.cu:91-121 of the reference (fp32, the only reachable dtype).
 void reciprocal_approximate_ftz_tensor(torch::Tensor const& input, torch::Tensor& output) {
   TORCH_CHECK(input.scalar_type() == at::ScalarType::Float, "Input tensor must be float");
@@ -221,6 +241,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scaled_mxfp4_quant", &scaled_mxfp4_quant);
   m.def("mxfp4_scaled_mm", &mxfp4_scaled_mm);
   m.def("scaled_fp4_mm_multi", &scaled_fp4_mm_multi);
+  m.def("scaled_fp4_mm_scatter_add", &scaled_fp4_mm_scatter_add);
   m.def("global_scale", &global_scale);
   m.def("activation_scales", &activation_scales);
   m.def("alpha_from_scales", &alpha_from_scales);

@@ -54,12 +54,19 @@ constexpr int kMaxOutputs = 8;
 struct OutMaps {
   CUtensorMap map[kMaxOutputs];
 };
+// How the epilogue uses the output maps:
+//   kOutStoreAll    every tile is stored to all n_out destinations (1 = plain GEMM, >1 = fused gather)
+//   kOutScatterAdd  row-parallel (K-split) layers: destination r owns rows [r*rows_per_owner, ...) of the
+//                   result; each 32-row block of this rank's fp32 partial product is ADDED (TMA reduce)
+//                   into its owner's buffer -- the reduce-scatter fused into the epilogue
+constexpr int kOutStoreAll = 0, kOutScatterAdd = 1;
 
-template <bool MX, typename OutT>
+template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                     const __grid_constant__ OutMaps out_maps, const int n_out, const GemmParams p) {
+                     const __grid_constant__ OutMaps out_maps, const int n_out, const int rows_per_owner,
+                     const GemmParams p) {
   using C = PairCfg<MX>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -293,8 +300,14 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          for (int o = 0; o < n_out; ++o)
-            tma_store_2d(&out_maps.map[o], buf, tn * kPairBN + c * kCols, row0);
+          if constexpr (OUT_MODE == kOutScatterAdd) {
+            const int owner = row0 / rows_per_owner;
+            if (owner < n_out)
+              tma_reduce_add_2d(&out_maps.map[owner], buf, tn * kPairBN + c * kCols, row0 - owner * rows_per_owner);
+          } else {
+            for (int o = 0; o < n_out; ++o)
+              tma_store_2d(&out_maps.map[o], buf, tn * kPairBN + c * kCols, row0);
+          }
           bulk_commit_group();
         }
         ++store_count;
@@ -347,8 +360,9 @@ int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, in
   return NVFP_OK;
 }
 
-// `outputs`: n_out destination matrices [m, n] with leading dimension ld; outputs[0] is normally p.d.
-template <bool MX, typename OutT>
+// `outputs`: n_out destination matrices with leading dimension ld: [m, n] each (kOutStoreAll; outputs[0]
+// is normally p.d) or [m / n_out, n] each (kOutScatterAdd).
+template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 int launch_pair(const GemmParams& base, const void* a, const void* b, void* const* outputs, int n_out,
                 int64_t ld, int sm_count, cudaStream_t stream) {
   using C = PairCfg<MX>;
@@ -362,9 +376,10 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   if (int rc = make_scale_map(&map_sfb, p.sfb, p.sf_k_chunks, ceil_div(p.n, 128), C::kChunksPerStage, 2)) return rc;
   OutMaps out_maps;
   memset(&out_maps, 0, sizeof(out_maps));
+  const int rows_per_owner = OUT_MODE == kOutScatterAdd ? p.m / n_out : p.m;
   for (int o = 0; o < n_out; ++o)
-    if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], p.m, p.n, ld)) return rc;
-  auto kernel = fp4_gemm_pair_kernel<MX, OutT>;
+    if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], rows_per_owner, p.n, ld)) return rc;
+  auto kernel = fp4_gemm_pair_kernel<MX, OutT, OUT_MODE>;
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const unsigned pairs = (unsigned)std::min<int64_t>(tiles, sm_count / 2);
@@ -380,6 +395,6 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, out_maps, n_out, p));
+  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, out_maps, n_out, rows_per_owner, p));
   return NVFP_OK;
 }

@@ -480,3 +480,37 @@ extern "C" int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void*
   return mxfp4 ? scaled_mm<true>(dst, n_dst, dst_ld, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream))
                : scaled_mm<false>(dst, n_dst, dst_ld, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int nvfp_scaled_fp4_mm_scatter_add(void* const* dst, int n_dst, const void* a, const void* b,
+                                              const void* sfa, const void* sfb, const float* alpha, int64_t m,
+                                              int64_t n, int64_t k, int mxfp4, void* stream) {
+  clear_error();
+  NVFP_REQUIRE(dst != nullptr && n_dst >= 1 && n_dst <= kMaxOutputs, "between 1 and %d destinations are supported, got %d",
+               kMaxOutputs, n_dst);
+  NVFP_REQUIRE(m > 0 && n > 0 && k > 0 && m % (32 * n_dst) == 0,
+               "m (%lld) must be a positive multiple of 32 x the number of destinations (%d)", (long long)m, n_dst);
+  NVFP_REQUIRE(k % (mxfp4 ? 64 : 32) == 0 && n % 32 == 0, "k must be divisible by %d and n by 32", mxfp4 ? 64 : 32);
+  NVFP_REQUIRE(mxfp4 || alpha != nullptr, "alpha pointer is null");
+  NVFP_REQUIRE(a && b && sfa && sfb, "null pointer");
+  for (int o = 0; o < n_dst; ++o)
+    NVFP_REQUIRE(dst[o] != nullptr && (reinterpret_cast<uintptr_t>(dst[o]) & 15) == 0,
+                 "destination %d is null or not 16-byte aligned", o);
+  DeviceInfo info;
+  if (int rc = current_device_info(&info)) return rc;
+  if (info.cc_major != 10)
+    return fail(NVFP_ERR_UNSUPPORTED, "No compiled nvfp4 mm kernel for compute capability %d.%d (needs sm_100)",
+                info.cc_major, info.cc_minor);
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.alpha = alpha;
+  p.d = dst[0];
+  p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.sf_k_chunks = (int)ceil_div(k / (mxfp4 ? 32 : 16), 4);
+  p.sfb_row_tiles = (int)ceil_div(n, 128);
+  p.status = device_status_word();
+  NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return mxfp4 ? launch_pair<true, float, kOutScatterAdd>(p, a, b, dst, n_dst, n, info.sm_count, st)
+               : launch_pair<false, float, kOutScatterAdd>(p, a, b, dst, n_dst, n, info.sm_count, st);
+}

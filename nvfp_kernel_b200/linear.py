@@ -23,7 +23,7 @@ class QuantLinear(nn.Module):
                  format: str = "nvfp4", parallel: str | None = None, process_group=None,
                  out_dtype: torch.dtype = torch.bfloat16, mx_rounding: str = "rceil",
                  gather_output: bool = True, input_is_parallel: bool = False, fused_gather: bool = False,
-                 device=None):
+                 fused_reduce_scatter: bool = False, device=None):
         super().__init__()
         if mode != "real":
             raise ValueError(f"mode={mode!r}: only the real-kernel path exists (no emulation, no pseudo-quant fallback)")
@@ -40,6 +40,10 @@ class QuantLinear(nn.Module):
         # buffer over NVLink instead of running an all-gather afterwards (see peer.py)
         self.fused_gather = fused_gather and parallel == "column"
         self._gather_buffers = {}
+        # row-parallel only: partial products are added straight into the owning rank's fp32 buffer by the
+        # GEMM epilogue (TMA reduce over NVLink) instead of an NCCL reduce-scatter afterwards
+        self.fused_reduce_scatter = fused_reduce_scatter and parallel == "row"
+        self._reduce_buffers = {}
         self.world, self.rank = 1, 0
         if parallel is not None:
             import torch.distributed as dist
@@ -108,6 +112,8 @@ class QuantLinear(nn.Module):
         acc_dtype = torch.float32 if self.parallel == "row" and self.world > 1 else self.out_dtype
         if self.fused_gather and self.world > 1 and self.gather_output:
             return self._forward_fused_gather(x2, lead)
+        if self.fused_reduce_scatter and self.world > 1 and x2.shape[0] % (32 * self.world) == 0:
+            return self._forward_fused_reduce_scatter(x2)
         if self.format == "nvfp4":
             a_gs, alpha = self._activation_scales(x2)
             a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
@@ -146,6 +152,31 @@ class QuantLinear(nn.Module):
         if self.bias is not None:
             y = y + self.bias
         return y.reshape(*lead, y.shape[-1])
+
+    def _forward_fused_reduce_scatter(self, x2: torch.Tensor) -> torch.Tensor:
+        """Row-parallel forward: returns this rank's [M / world, N] rows of the sum over ranks."""
+        from ._ops_real import _load_scaled_fp4_ops
+        from .peer import ReduceBuffer
+        m = x2.shape[0]
+        rb = self._reduce_buffers.get(m)
+        if rb is None:
+            rb = self._reduce_buffers[m] = ReduceBuffer(m, self.out_features, x2.device, self.process_group)
+        ext = _load_scaled_fp4_ops(("scaled_fp4_mm_scatter_add",))
+        if self.format == "nvfp4":
+            a_gs, alpha = self._activation_scales(x2)
+            a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
+        else:
+            a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
+            alpha = None
+        rb.buf.zero_()
+        rb.barrier()          # every rank's buffer is zero and nobody reads the previous result any more
+        ext.scaled_fp4_mm_scatter_add(rb.dst_ptrs, a_fp4, self.weight_fp4, a_sf.view(torch.uint8), self.weight_sf,
+                                      alpha, self.format == "mxfp4")
+        rb.barrier()          # every rank's contributions have arrived
+        y = rb.buf.to(self.out_dtype)
+        if self.bias is not None:
+            y = y + self.bias
+        return y
 
     def _mm_f32(self, a_fp4, a_sf, alpha):
         from ._ops_real import _load_scaled_fp4_ops

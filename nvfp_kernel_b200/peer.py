@@ -39,3 +39,24 @@ class GatherBuffer:
     def gathered(self) -> torch.Tensor:
         """The local [M, N] buffer."""
         return self.buf
+
+
+class ReduceBuffer:
+    """fp32 [M / world, N] accumulation buffer of the row-parallel layer's fused reduce-scatter: every
+    rank's GEMM epilogue adds its partial product's rows into the buffer of the rank that owns them."""
+
+    def __init__(self, m: int, n: int, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert m % (32 * self.world) == 0, "fused reduce-scatter needs M to be a multiple of 32 x world size"
+        self.buf = symm_mem.empty((m // self.world, n), dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.dst_ptrs = [int(p) for p in self.handle.buffer_ptrs]     # destination r = rank r's buffer
+
+    def barrier(self) -> None:
+        self.handle.barrier(channel=0)

@@ -42,6 +42,11 @@ def _worker(rank, world, port, ret):
         y_row = row(a)                                # [m / world, n]: this rank's rows
         lo, hi = rank * m // world, (rank + 1) * m // world
         check_gemm(y_row, single[lo:hi].double(), rel=2e-2)
+        row_fused = QuantLinear(k, n, parallel="row", fused_reduce_scatter=True, device="cuda").load_weight(w)
+        for scale in (1.0, 0.25):                   # two calls: the accumulation buffer is reused
+            y_rf = row_fused(a * scale)
+            ref = QuantLinear(k, n, device="cuda").load_weight(w)(a * scale)
+            check_gemm(y_rf, ref[lo:hi].double(), rel=2e-2)
         torch.cuda.synchronize()
         ret[rank] = (bool(torch.equal(y_nccl, single)), bool(torch.equal(y_fused, single)),
                      bool(torch.equal(y_fused2, single2)), tuple(y_row.shape))
