@@ -3,6 +3,8 @@
     python -m nvfp_kernel_b200.speed_test                 # BF16 torch.mm vs FP4 (online activation quantize + GEMM)
     python -m nvfp_kernel_b200.speed_test --table decode  # Llama-3-8B decode shapes, M in {1, 16, 128}
     python -m nvfp_kernel_b200.speed_test --table quant   # quantizer alone, GB/s
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m nvfp_kernel_b200.speed_test --table tp
+                                                          # Llama-3-70B prefill layers, tensor-parallel
 
 The first table is the reference's sweep (speed_test.py:56-98 there): M = --batch_size (default 4096),
 K = N = size, weight quantized once, activation amax + quantize + GEMM timed per call.  Differences:
@@ -93,15 +95,75 @@ def quant(repeats: int):
         print(f"{m:<7} {k:<7} {t_q:<15.1f} {m * k * 2.5625 / t_q / 1e3:<20.0f} {t_a:<10.1f}")
 
 
+def tensor_parallel(repeats: int):
+    """Llama-3-70B prefill layers (M = 8192) sharded over the ranks of this launch (torchrun):
+    gate_up [N = 57344, K = 8192] column-parallel, down [N = 8192, K = 28672] row-parallel, each with the
+    NCCL collective after the GEMM and with the collective fused into the GEMM epilogue.  Every rank builds
+    only its own weight shard (random values: this table times, the tests check values)."""
+    import os
+    import torch.distributed as dist
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    m = 8192
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def timed(layer, x):
+        for _ in range(3):
+            layer(x)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(repeats):
+            layer(x)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / repeats], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def make(parallel, n, k, **kw):
+        layer = QuantLinear(k, n, parallel=parallel, device="cuda", **kw)
+        shard = (torch.randn((layer.n_local, layer.k_local), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        gs = ops.global_scale(shard)
+        w_fp4, w_sf = ops.scaled_fp4_quant(shard, gs)
+        layer.weight_fp4, layer.weight_sf = w_fp4, w_sf.view(torch.uint8)
+        layer.weight_global_scale.copy_(gs)
+        return layer
+
+    rows = []
+    x = torch.randn((m, 8192), generator=g, device="cuda").to(torch.bfloat16)
+    flops = 2.0 * m * 57344 * 8192
+    for name, kw in (("NCCL all-gather", {}), ("fused gather", {"fused_gather": True})):
+        if world == 1 and kw:
+            continue
+        t = timed(make("column" if world > 1 else None, 57344, 8192, **kw), x)
+        rows.append(("gate_up column-parallel", name if world > 1 else "single GPU", t, flops / t / 1e9))
+    x = torch.randn((m, 28672), generator=g, device="cuda").to(torch.bfloat16)
+    flops = 2.0 * m * 8192 * 28672
+    for name, kw in (("NCCL reduce-scatter", {}), ("fused reduce-scatter", {"fused_reduce_scatter": True})):
+        if world == 1 and kw:
+            continue
+        t = timed(make("row" if world > 1 else None, 8192, 28672, **kw), x)
+        rows.append(("down row-parallel", name if world > 1 else "single GPU", t, flops / t / 1e9))
+    if rank == 0:
+        print(f"Llama-3-70B prefill layers, M = {m}, {world} GPU(s); time = max over ranks, includes activation quantize")
+        print(f"{'layer':<26} {'collective':<22} {'ms':<9} {'TFLOP/s (all ranks)':<20}")
+        for r in rows:
+            print(f"{r[0]:<26} {r[1]:<22} {r[2]:<9.3f} {r[3]:<20.0f}")
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser(description="BF16 GEMM vs FP4 GEMM with online activation quantization")
     ap.add_argument("--batch_size", type=int, default=4096, help="M dimension of the sweep")
     ap.add_argument("--repeats", type=int, default=50)
-    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant"])
+    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp"])
     args = ap.parse_args()
     torch.cuda.empty_cache()
     {"sweep": lambda: sweep(args.batch_size, args.repeats), "decode": lambda: decode(args.repeats),
-     "quant": lambda: quant(args.repeats)}[args.table]()
+     "quant": lambda: quant(args.repeats), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
 
 
 if __name__ == "__main__":
