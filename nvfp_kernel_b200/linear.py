@@ -40,6 +40,7 @@ class QuantLinear(nn.Module):
         # buffer over NVLink instead of running an all-gather afterwards (see peer.py)
         self.fused_gather = fused_gather and parallel == "column"
         self._gather_buffers = {}
+        self._use_graph, self._graphs = False, {}
         # row-parallel only: partial products are added straight into the owning rank's fp32 buffer by the
         # GEMM epilogue (TMA reduce over NVLink) instead of an NCCL reduce-scatter afterwards
         self.fused_reduce_scatter = fused_reduce_scatter and parallel == "row"
@@ -102,8 +103,47 @@ class QuantLinear(nn.Module):
     def _sf_view(self, t: torch.Tensor) -> torch.Tensor:
         return t.view(torch.float8_e4m3fn if self.format == "nvfp4" else torch.float8_e8m0fnu)
 
+    # -------------------------------------------------------------- CUDA graphs ---
+    def enable_cuda_graph(self, enabled: bool = True) -> "QuantLinear":
+        """Replay one captured CUDA graph per input shape instead of launching the forward's kernels
+        one by one (small, launch-bound shapes: the reference's forward has a 40 us floor from 8 launches,
+        README.md:34-37 there).  The result aliases a buffer owned by the layer and is overwritten by the
+        next call with the same shape.  Not available for tensor-parallel layers."""
+        if enabled and self.parallel is not None:
+            raise ValueError("CUDA-graph replay is only offered for single-GPU layers")
+        self._use_graph = enabled
+        if not enabled:
+            self._graphs = {}
+        return self
+
+    def _graphed_forward(self, x: torch.Tensor) -> torch.Tensor:
+        key = (tuple(x.shape), x.dtype)
+        entry = self._graphs.get(key)
+        if entry is None:
+            static_in = torch.empty_like(x, memory_format=torch.contiguous_format)
+            static_in.copy_(x)
+            stream = torch.cuda.Stream(device=x.device)
+            stream.wait_stream(torch.cuda.current_stream(x.device))
+            with torch.cuda.stream(stream):
+                for _ in range(2):                     # warm-up outside capture (lazy initialisation, allocator)
+                    self._forward_impl(static_in)
+            torch.cuda.current_stream(x.device).wait_stream(stream)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_out = self._forward_impl(static_in)
+            entry = self._graphs[key] = (graph, static_in, static_out)
+        graph, static_in, static_out = entry
+        static_in.copy_(x)
+        graph.replay()
+        return static_out
+
     # ------------------------------------------------------------------ forward ---
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if getattr(self, "_use_graph", False):
+            return self._graphed_forward(x)
+        return self._forward_impl(x)
+
+    def _forward_impl(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
         if self.parallel == "row" and not self.input_is_parallel:

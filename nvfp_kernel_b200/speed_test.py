@@ -66,8 +66,8 @@ def sweep(batch_size: int, repeats: int):
 
 
 def decode(repeats: int):
-    print(f"{'M':<5} {'K':<7} {'N':<7} {'GEMM (us)':<11} {'GB/s':<9} {'forward (us)':<13}")
-    print("-" * 56)
+    print(f"{'M':<5} {'K':<7} {'N':<7} {'GEMM (us)':<11} {'GB/s':<9} {'forward (us)':<13} {'graph replay (us)':<13}")
+    print("-" * 76)
     for m in (1, 16, 128):
         for k, n in ((4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)):
             a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
@@ -80,8 +80,10 @@ def decode(repeats: int):
             t_mm = time_us(lambda: ops.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, alpha, torch.bfloat16),
                            repeats)
             t_fwd = time_us(lambda: layer(a), repeats)
+            layer.enable_cuda_graph()
+            t_graph = time_us(lambda: layer(a), repeats)
             nbytes = n * k * 0.5625 + m * k * 0.5625 + 2.0 * m * n
-            print(f"{m:<5} {k:<7} {n:<7} {t_mm:<11.1f} {nbytes / t_mm / 1e3:<9.0f} {t_fwd:<13.1f}")
+            print(f"{m:<5} {k:<7} {n:<7} {t_mm:<11.1f} {nbytes / t_mm / 1e3:<9.0f} {t_fwd:<13.1f} {t_graph:<13.1f}")
 
 
 def quant(repeats: int):

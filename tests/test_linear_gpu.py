@@ -52,3 +52,38 @@ def test_quant_linear_mxfp4():
     y = q(a)
     dense = a.float() @ w.float().T
     assert y.dtype == torch.bfloat16 and (y.float() - dense).abs().max() < 0.3 * dense.abs().max()
+
+
+def test_cuda_graph_replay_matches_eager_and_handles_several_shapes():
+    from nvfp_kernel_b200 import QuantLinear
+    a, w = gemm_inputs(16, 512, 1024, seed=5, w_std=0.05)
+    a, w = a.cuda(), w.cuda()
+    eager = QuantLinear(1024, 512, device="cuda").load_weight(w)
+    graphed = QuantLinear(1024, 512, device="cuda").load_weight(w).enable_cuda_graph()
+    for scale in (1.0, 0.3, 7.0):                       # replays must pick up new input values
+        assert torch.equal(graphed(a * scale), eager(a * scale))
+    b = (a[:4] * 2).contiguous()                        # a second shape gets its own graph
+    assert torch.equal(graphed(b), eager(b))
+    assert torch.equal(graphed(a), eager(a))
+    import nvfp_kernel_b200 as nv
+    assert nv.device_status() == 0
+
+
+def test_quantize_linear_layers_of_a_model():
+    import torch.nn as nn
+    from nvfp_kernel_b200 import QuantLinear
+    from nvfp_kernel_b200.convert import quantize_linear_layers
+    torch.manual_seed(0)
+    model = nn.Sequential()
+    model.add_module("up", nn.Linear(256, 512, bias=False))
+    model.add_module("act", nn.SiLU())
+    model.add_module("down", nn.Linear(512, 256, bias=True))
+    model.add_module("lm_head", nn.Linear(256, 96, bias=False))
+    model = model.cuda().to(torch.bfloat16)
+    x = torch.randn(40, 256, device="cuda", dtype=torch.bfloat16)
+    dense = model(x)
+    names = quantize_linear_layers(model)
+    assert names == ["up", "down"] and isinstance(model.up, QuantLinear) and isinstance(model.lm_head, nn.Linear)
+    y = model(x)
+    assert y.shape == dense.shape
+    assert (y.float() - dense.float()).abs().max() < 0.35 * dense.float().abs().max()
