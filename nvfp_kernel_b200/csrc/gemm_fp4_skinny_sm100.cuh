@@ -1,45 +1,75 @@
-// Block-scaled FP4 GEMM for few activation rows (decode, M <= 128).  Included by
+// Block-scaled FP4 GEMM for few activation rows (decode, M <= 64).  Included by
 // gemm_fp4_sm100.cu inside namespace nvfp::<anonymous>.
 //
 // With a handful of tokens the product is bound by streaming the weights once, and the
 // reference's answer -- the same 128-row tile kernel, no split-K
 // (kernel/nvfp4_scaled_mm_sm120_kernels.cu:190-220) -- leaves most SMs idle.  Here:
 //   * operands are swapped: the 128 rows of the MMA are WEIGHT rows, the MMA's N is the token count
-//     (rounded up to 16), so a stage holds 16 KB of weights and only NT x 128 bytes of activations;
-//   * K is split over a cluster of up to 4 CTAs; each computes a partial [128 weight rows x NT tokens]
-//     in tensor memory, the non-leaders write theirs into the leader's shared memory (distributed
-//     shared memory, plain st.shared::cluster), the leader adds, scales by alpha and stores.  No
-//     global scratch, no second kernel, no atomics.
+//     (rounded up to 16), so shared memory holds weights, not padding;
+//   * a pipeline stage covers 1024 elements of K (four 128-byte-swizzled boxes per operand), so every
+//     weight row contributes 512 contiguous bytes per stage: DRAM pages are read in long bursts instead
+//     of 128-byte slivers, and the issuer pays one barrier round trip per 16 MMAs;
+//   * the epilogue warps, idle during the main loop, prefetch this CTA's whole slab of weights into L2
+//     with plain prefetch instructions (the ring only keeps two stages in flight, too few to cover DRAM
+//     latency), and each box has its own barrier, so the first MMAs start when 1/4 of a stage has landed;
+//   * K is split over a cluster of CTAs; each computes a partial [128 weight rows x NT tokens]
+//     in tensor memory, the non-leaders stage theirs in their own shared memory and send it to the
+//     leader with one bulk copy per warp (shared memory to shared memory inside the cluster, completion
+//     on an mbarrier of the leader), the leader adds, scales by alpha and stores.  No global scratch, no
+//     second kernel, no atomics.
 #pragma once
 
-// Measured on B200 inside a CUDA graph (warm L2), M=16: N=4096,K=14336 takes 14.4 us here against 25 us with
-// the tile kernel; at K=4096 (N=4096: 9.6 vs 9.2 us, N=28672: 21.7 vs 20.6 us) there is nothing to gain, so the
-// dispatcher only comes here for long K and few weight tiles.
 constexpr int kSkinnyMaxTokens = 64;
-constexpr uint32_t kSkinnyReduceBytes = 64 * 1024;   // leader's buffer for the peers' partial sums
+constexpr int kSkinnyMaxSplit = 8;
+constexpr int kSkinnyBoxes = 4;                                   // 256-element K boxes per stage
+constexpr int kSkinnyStageK = kSkinnyBoxes * kStageK;             // 1024
+// "Full" barriers per stage.  One per box (4) lets the first MMAs start earlier but measured 60 % slower per
+// stage than one barrier (all scale copies of a stage queued before its MMAs), so the whole stage reports to one.
+constexpr int kSkinnyGroups = 1;
+constexpr int kSkinnyGroupBoxes = kSkinnyBoxes / kSkinnyGroups;   // boxes reported to one barrier
 constexpr uint32_t kSkinnyTmemCols = 256;
+constexpr uint32_t kSkinnyOutTileBytes = 16 * 128 * 4;            // output staging: 16 tokens x 128 columns fp32
+constexpr uint32_t kSkinnyAccCols = 64;                           // accumulator: columns [0, NT)
 
 template <bool MX>
 struct SkinnyCfg {
-  static constexpr int kChunksPerStage = MX ? 2 : 4;
+  static constexpr int kChunksPerBox = MX ? 2 : 4;                // 512-byte scale chunks per 256 elements of K
+  static constexpr int kChunksPerStage = kSkinnyBoxes * kChunksPerBox;
   static constexpr int kMmasPerChunk = MX ? 2 : 1;
-  static constexpr uint32_t kWBytes = 128 * kStageKBytes;            // weight tile of a stage
-  static constexpr uint32_t kXBytesMax = kSkinnyMaxTokens * kStageKBytes;
-  static constexpr uint32_t kSfBytes = kChunksPerStage * 512;        // per operand
-  static constexpr uint32_t kSfColBase = 128;                        // accumulator: columns [0, NT)
+  static constexpr uint32_t kWBoxBytes = 128 * kStageKBytes;      // 16 KB
+  static constexpr uint32_t kSfBytes = kChunksPerStage * 512;     // per operand per stage
+  static constexpr int kChunksPerGroup = kSkinnyGroupBoxes * kChunksPerBox;
+  static constexpr uint32_t kSfGroupBytes = kChunksPerGroup * 512; // per operand per barrier group
+  static constexpr uint32_t kSfwCol = kSkinnyAccCols;             // weight scales: 4 columns per chunk
+  static constexpr uint32_t kSfxCol = kSfwCol + 4 * kChunksPerStage;
+  static_assert(kSfxCol + 4 * kChunksPerStage <= kSkinnyTmemCols, "tensor memory budget");
 };
 
 struct SkinnyParams {
   GemmParams g;
   int nt;               // MMA N = tokens rounded up to 16
   int split;            // cluster size = K splits
-  int stages_per_rank;  // K stages (of 256 elements) each rank of a cluster processes
+  int stages_per_rank;  // stages (of 1024 elements of K) each rank of a cluster processes
   int num_stages;       // pipeline depth
   uint32_t stage_bytes;
+  const void* w;           // weights [n, k/2], for the L2 prefetch
+  uint32_t reduce_offset;  // leader's buffer for the peers' partial sums: 0 = it reuses the drained stage area
 };
 
-__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+// Partial sums in the leader: [peer][weight row][NT + 4] fp32.  The 4 floats of padding make the row stride an
+// odd number of 16-byte units, so 32 lanes reading one float4 each from consecutive rows hit distinct banks.
+__host__ __device__ constexpr uint32_t skinny_reduce_ld(int nt) { return (uint32_t)nt + 4u; }
+__host__ __device__ constexpr uint32_t skinny_reduce_bytes(int nt, int split) {
+  return (uint32_t)(split - 1) * 128u * skinny_reduce_ld(nt) * 4u;
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
 }
 
 template <bool MX, typename OutT>
@@ -50,35 +80,74 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const GemmParams& p = sp.g;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // [reduce buffer 64 KB][stages][barriers]
-  float* reduce_buf = reinterpret_cast<float*>(smem);
-  uint8_t* stage0 = smem + kSkinnyReduceBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage0 + sp.num_stages * sp.stage_bytes);
-  const int kFull = 0, kEmpty = sp.num_stages, kAccFull = 2 * sp.num_stages, kNumBars = kAccFull + 1;
+  // [stages ...][leader's reduce buffer, unless it reuses the stage area][barriers]
+  const bool alias = sp.reduce_offset == 0;
+  const uint32_t reduce_bytes = skinny_reduce_bytes(sp.nt, sp.split);
+  float* reduce_buf = reinterpret_cast<float*>(smem + sp.reduce_offset);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + sp.num_stages * sp.stage_bytes + (alias ? 0u : reduce_bytes));
+  const int kFull = 0, kEmpty = kSkinnyGroups * sp.num_stages, kAccFull = kEmpty + sp.num_stages, kReduce = kAccFull + 1;
+  const int kNumBars = kReduce + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const int n_tile = (int)cluster_id_x();
-  const uint32_t stage_base = smem_u32(stage0);
+  const uint32_t rank = sp.split > 1 ? cluster_ctarank() : 0u;
+  const int n_tile = sp.split > 1 ? (int)cluster_id_x() : (int)blockIdx.x;
+  const uint32_t stage_base = smem_u32(smem);
   auto bar = [&](int i) { return smem_u32(bars + i); };
-  const uint32_t x_bytes = (uint32_t)sp.nt * kStageKBytes;
-  const uint32_t off_x = C::kWBytes, off_sfw = C::kWBytes + x_bytes, off_sfx = off_sfw + C::kSfBytes;
+  const uint32_t x_box_bytes = (uint32_t)sp.nt * kStageKBytes;
+  const uint32_t off_x = kSkinnyBoxes * C::kWBoxBytes;
+  const uint32_t off_sfw = off_x + kSkinnyBoxes * x_box_bytes, off_sfx = off_sfw + C::kSfBytes;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < sp.num_stages; ++i) {
-      mbar_init(bar(kFull + i), 1);
-      mbar_init(bar(kEmpty + i), 1);
+  const int total_stages = (p.k + kSkinnyStageK - 1) / kSkinnyStageK;
+  const int ks_begin = min((int)rank * sp.stages_per_rank, total_stages);
+  const int ks_end = min(ks_begin + sp.stages_per_rank, total_stages);
+  const int my_stages = ks_end - ks_begin;
+  const int k_boxes_total = (p.k + kStageK - 1) / kStageK;
+  const uint8_t* sfw_tile = p.sfb + (int64_t)n_tile * p.sf_k_chunks * 512;
+
+  // Loads of local stage i (K range [ks * 1024, ks * 1024 + 1024)) into ring slot s; the boxes of one group
+  // report to one barrier.
+  auto load_stage = [&](int i) {
+    const int ks = ks_begin + i;
+    const uint32_t s = (uint32_t)i % sp.num_stages;
+    const uint32_t st = stage_base + s * sp.stage_bytes;
+    const int boxes = min(kSkinnyBoxes, k_boxes_total - ks * kSkinnyBoxes);
+    for (int g = 0; g * kSkinnyGroupBoxes < boxes; ++g) {
+      const int b0 = g * kSkinnyGroupBoxes, nb = min(kSkinnyGroupBoxes, boxes - b0);
+      const int chunk0 = ks * C::kChunksPerStage + g * C::kChunksPerGroup;
+      const uint32_t sf_bytes = (uint32_t)min(C::kChunksPerGroup, p.sf_k_chunks - chunk0) * 512u;
+      const uint32_t full = bar(kFull + (int)s * kSkinnyGroups + g);
+      mbar_arrive_expect_tx(full, (uint32_t)nb * (C::kWBoxBytes + x_box_bytes) + 2 * sf_bytes);
+      for (int b = b0; b < b0 + nb; ++b) {
+        const int kbyte = (ks * kSkinnyBoxes + b) * kStageKBytes;
+        tma_load_2d(st + b * C::kWBoxBytes, &tmap_w, full, kbyte, n_tile * 128);
+        tma_load_2d(st + off_x + b * x_box_bytes, &tmap_x, full, kbyte, 0);
+      }
+      bulk_load(st + off_sfw + g * C::kSfGroupBytes, sfw_tile + (int64_t)chunk0 * 512, sf_bytes, full);
+      bulk_load(st + off_sfx + g * C::kSfGroupBytes, p.sfa + (int64_t)chunk0 * 512, sf_bytes, full);
     }
-    mbar_init(bar(kAccFull), 1);
-    *abort_flag = 0;
-    fence_mbar_init();
-    prefetch_tensormap(&tmap_w);
-    prefetch_tensormap(&tmap_x);
-  }
-  if (warp == 1) {
+  };
+  if (warp == 0) {
+    // The producer thread initialises the barriers itself and starts the first loads before the rest of
+    // the CTA (tensor memory allocation, the other warps) is ready.
+    if (elect_one()) {
+      for (int i = 0; i < kEmpty; ++i) mbar_init(bar(kFull + i), 1);
+      for (int i = 0; i < sp.num_stages; ++i) mbar_init(bar(kEmpty + i), 1);
+      mbar_init(bar(kAccFull), 1);
+      mbar_init(bar(kReduce), 1);
+      *abort_flag = 0;
+      fence_mbar_init();
+      fence_proxy_async_smem();
+      if (sp.split > 1 && rank == 0) mbar_arrive_expect_tx(bar(kReduce), reduce_bytes);
+      prefetch_tensormap(&tmap_w);
+      prefetch_tensormap(&tmap_x);
+      const int first = min(my_stages, sp.num_stages);
+      for (int i = 0; i < first; ++i) load_stage(i);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kSkinnyTmemCols);
     tmem_relinquish_alloc_permit();
   }
@@ -86,75 +155,73 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-
-  const int total_stages = (p.k + kStageK - 1) / kStageK;
-  const int ks_begin = min((int)rank * sp.stages_per_rank, total_stages);
-  const int ks_end = min(ks_begin + sp.stages_per_rank, total_stages);
-  const int my_stages = ks_end - ks_begin;
+  // With a buffer of its own the leader is ready for the peers' partial sums from here on.
+  if (sp.split > 1 && !alias) cluster_arrive();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer ---
     if (elect_one()) {
-      for (int i = 0; i < my_stages; ++i) {
-        const int ks = ks_begin + i;
+      for (int i = sp.num_stages; i < my_stages; ++i) {
         const uint32_t s = (uint32_t)i % sp.num_stages, ph = ((uint32_t)i / sp.num_stages) & 1u;
         if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicOr(p.status, kErrProducer);
           break;
         }
-        const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
-        const uint32_t sf_bytes = (uint32_t)chunks * 512u;
-        const uint32_t st = stage_base + s * sp.stage_bytes;
-        mbar_arrive_expect_tx(bar(kFull + s), C::kWBytes + x_bytes + 2 * sf_bytes);
-        tma_load_2d(st, &tmap_w, bar(kFull + s), ks * kStageKBytes, n_tile * 128);
-        tma_load_2d(st + off_x, &tmap_x, bar(kFull + s), ks * kStageKBytes, 0);
-        const int64_t chunk0 = (int64_t)ks * C::kChunksPerStage;
-        bulk_load(st + off_sfw, p.sfb + ((int64_t)n_tile * p.sf_k_chunks + chunk0) * 512, sf_bytes, bar(kFull + s));
-        bulk_load(st + off_sfx, p.sfa + chunk0 * 512, sf_bytes, bar(kFull + s));
+        load_stage(i);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------------- issuer ---
     if (elect_one()) {
-      const uint32_t sfw_tmem = tmem_base + C::kSfColBase, sfx_tmem = sfw_tmem + 16;
+      const uint32_t sfw_tmem = tmem_base + C::kSfwCol, sfx_tmem = tmem_base + C::kSfxCol;
+      const uint32_t idesc0 = make_idesc_fp4_block_scaled(128, sp.nt, MX, 0u, 0u);
+      const uint32_t idesc1 = MX ? make_idesc_fp4_block_scaled(128, sp.nt, true, 2u, 2u) : idesc0;
       bool ok = true;
       for (int i = 0; i < my_stages && ok; ++i) {
         const int ks = ks_begin + i;
         const uint32_t s = (uint32_t)i % sp.num_stages, ph = ((uint32_t)i / sp.num_stages) & 1u;
-        if (!mbar_wait_bounded(bar(kFull + s), ph, abort_flag)) {
-          *abort_flag = 1;
-          atomicOr(p.status, kErrIssuer);
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
-        const int mmas = min(kStageK / kMmaK, (p.k - ks * kStageK + kMmaK - 1) / kMmaK);
         const uint32_t st = stage_base + s * sp.stage_bytes;
-        const uint64_t w_desc = make_smem_desc(st, 16, 1024, 2);
-        const uint64_t x_desc = make_smem_desc(st + off_x, 16, 1024, 2);
-        // tiny MMAs are latency-bound: queue all scale copies of the stage first (into one of two
-        // alternating sets of columns), then the MMAs back to back
-        const uint32_t slot = (uint32_t)(i & 1) * 32u;
-        for (int c = 0; c < chunks; ++c) {
-          tc_copy_sf_32x128b_warpx4(sfw_tmem + slot + 4 * c, make_smem_desc(st + off_sfw + c * 512, 0, 128, 0));
-          tc_copy_sf_32x128b_warpx4(sfx_tmem + slot + 4 * c, make_smem_desc(st + off_sfx + c * 512, 0, 128, 0));
+        const int boxes = min(kSkinnyBoxes, k_boxes_total - ks * kSkinnyBoxes);
+        for (int g = 0; g * kSkinnyGroupBoxes < boxes; ++g) {
+          if (!mbar_wait_bounded(bar(kFull + (int)s * kSkinnyGroups + g), ph, abort_flag)) {
+            *abort_flag = 1;
+            atomicOr(p.status, kErrIssuer);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const int b0 = g * kSkinnyGroupBoxes, nb = min(kSkinnyGroupBoxes, boxes - b0);
+          const int chunk0 = ks * C::kChunksPerStage + g * C::kChunksPerGroup;
+          const int chunks = min(C::kChunksPerGroup, p.sf_k_chunks - chunk0);
+          // one set of scale columns per position in the stage: the tensor pipe runs one thread's copies and
+          // MMAs in issue order, so a later stage's copies cannot overtake this stage's MMAs
+          const uint32_t col = 4u * (uint32_t)(g * C::kChunksPerGroup);
+          const uint64_t sfw_desc = make_smem_desc(st + off_sfw + g * C::kSfGroupBytes, 0, 128, 0);
+          const uint64_t sfx_desc = make_smem_desc(st + off_sfx + g * C::kSfGroupBytes, 0, 128, 0);
+          for (int c = 0; c < chunks; ++c) {
+            tc_copy_sf_32x128b_warpx4(sfw_tmem + col + 4 * c, sfw_desc + (uint64_t)(c * 32));
+            tc_copy_sf_32x128b_warpx4(sfx_tmem + col + 4 * c, sfx_desc + (uint64_t)(c * 32));
+          }
+          for (int b = b0; b < b0 + nb; ++b) {
+            const int mmas = min(kStageK / kMmaK, (p.k - (ks * kSkinnyBoxes + b) * kStageK + kMmaK - 1) / kMmaK);
+            const uint64_t w_desc = make_smem_desc(st + b * C::kWBoxBytes, 16, 1024, 2);
+            const uint64_t x_desc = make_smem_desc(st + off_x + b * x_box_bytes, 16, 1024, 2);
+            const uint32_t bcol = 4u * (uint32_t)(b * C::kChunksPerBox);
+            for (int j = 0; j < mmas; ++j) {
+              const int c = j / C::kMmasPerChunk;
+              const uint32_t accumulate = (i | b | j) != 0 ? 1u : 0u;
+              if (MX)
+                tc_mma_mxf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), (j & 1) ? idesc1 : idesc0,
+                            sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
+              else
+                tc_mma_nvf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), idesc0,
+                            sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
+            }
+          }
         }
-        for (int j = 0; j < mmas; ++j) {
-          const int c = j / C::kMmasPerChunk, jj = j % C::kMmasPerChunk;
-          const uint32_t accumulate = (i | j) != 0 ? 1u : 0u;
-          const uint64_t koff = (uint64_t)((j * (kMmaK / 2)) >> 4);
-          if (MX)
-            tc_mma_mxf4(tmem_base, w_desc + koff, x_desc + koff,
-                        make_idesc_fp4_block_scaled(128, sp.nt, true, 2u * jj, 2u * jj), sfw_tmem + slot + 4 * c,
-                        sfx_tmem + slot + 4 * c, accumulate);
-          else
-            tc_mma_nvf4(tmem_base, w_desc + koff, x_desc + koff, make_idesc_fp4_block_scaled(128, sp.nt, false),
-                        sfw_tmem + slot + 4 * c, sfx_tmem + slot + 4 * c, accumulate);
-        }
-        tc_commit(bar(kEmpty + s));
+        if (ok) tc_commit(bar(kEmpty + s));
       }
       if (ok) tc_commit(bar(kAccFull));
     }
@@ -162,12 +229,23 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   }
 
   // ------------------------------------------------- partial sums -> leader ---
-  // Epilogue warps of every rank pull their partial out of tensor memory; non-leaders push it
-  // into the leader's reduce buffer laid out [rank-1][token][weight row].
   const bool epi = warp >= 2;
   const int q = warp & 3;
   const int wrow = q * 32 + lane;                 // weight row within the tile = accumulator lane
+  const uint32_t ld = skinny_reduce_ld(sp.nt);
   bool have_acc = false;
+  float alpha = 1.0f;
+  if (epi) {
+    // Rows of this tile beyond the ring's first fill, one 128-byte line per instruction; thread = weight row.
+    const int row = n_tile * 128 + wrow;
+    if (row < p.n) {
+      const uint8_t* w_row = static_cast<const uint8_t*>(sp.w) + (int64_t)row * (p.k / 2);
+      const int byte_begin = (ks_begin + min(my_stages, sp.num_stages)) * (kSkinnyStageK / 2);
+      const int byte_end = min(ks_end * (kSkinnyStageK / 2), p.k / 2);
+      for (int off = byte_begin; off < byte_end; off += 128) prefetch_l2(w_row + off);
+    }
+    if (rank == 0 && p.alpha) alpha = __ldg(p.alpha);
+  }
   if (epi && my_stages > 0) {
     have_acc = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull), 0, abort_flag));
     if (!have_acc) {
@@ -177,66 +255,122 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
     tc_fence_after_sync();
   }
   const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
-  if (epi && rank != 0) {
-    const uint32_t dst0 = map_to_cta(smem_u32(reduce_buf), 0) + ((rank - 1) * (uint32_t)sp.nt * 128u + (uint32_t)wrow) * 4u;
-    for (int c = 0; c < sp.nt; c += 16) {
-      uint32_t r[16];
-      if (have_acc) {
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-            : "r"(t_row + c)
-            : "memory");
-        tmem_ld_wait();
-      } else {
+  bool have_peers = true;
+  if (sp.split > 1) {
+    // A leader whose buffer reuses the stage area is ready only now: its epilogue warps arrive after its
+    // last MMA has completed (all TMA writes landed, all MMA reads done).
+    if (alias) cluster_arrive();
+    cluster_wait();
+    if (epi && rank != 0) {
+      // own partial -> own (drained) stage area, laid out like the leader's buffer, then one bulk copy per warp
+      const uint32_t stage_row = stage_base + (uint32_t)wrow * ld * 4u;
+      for (int c = 0; c < sp.nt; c += 16) {
+        uint32_t r[16];
+        if (have_acc) {
+          tmem_ld_32x32b_x16(t_row + c, r);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int t = 0; t < 16; ++t) r[t] = 0u;
+          for (int t = 0; t < 16; ++t) r[t] = 0u;
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          st_shared_v4(stage_row + (uint32_t)(c + 4 * v) * 4u, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
       }
-#pragma unroll
-      for (int t = 0; t < 16; ++t) st_cluster_f32(dst0 + (uint32_t)(c + t) * 512u, __uint_as_float(r[t]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t warp_bytes = 32u * ld * 4u, warp_off = (uint32_t)q * warp_bytes;
+        bulk_copy_to_cta(map_to_cta(smem_u32(reduce_buf), 0) + (rank - 1) * 128u * ld * 4u + warp_off, stage_base + warp_off,
+                         warp_bytes, map_to_cta(bar(kReduce), 0));
+      }
+      __syncwarp();
     }
+    if (epi && rank == 0) {
+      have_peers = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kReduce), 0, abort_flag));
+      if (!have_peers) {
+        *abort_flag = 1;
+        if (lane == 0) atomicOr(p.status, kErrEpilogue);
+      }
+    }
+    // Second phase: a peer may leave only after the leader has received every copy (its source is the
+    // peer's shared memory); the leader arrives here and adds while the peers wait.  Nothing written before
+    // this arrival is read by another CTA afterwards, so it needs no release.
+    cluster_arrive_relaxed();
   }
-  // all partials are in the leader's shared memory after this barrier (release / acquire at cluster scope)
-  tc_fence_before_sync();
-  cluster_sync_all();
-  tc_fence_after_sync();
   if (epi && rank == 0) {
-    const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
     OutT* d = static_cast<OutT*>(p.d);
-    const int n_global = n_tile * 128 + wrow;
+    // staging tile [16 tokens][128 columns] in the drained stage area, behind the partial sums if they are there
+    OutT* out_tile = reinterpret_cast<OutT*>(smem + (alias ? reduce_bytes : 0u));
     for (int c = 0; c < sp.nt; c += 16) {
       uint32_t r[16];
       if (have_acc) {
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-            : "r"(t_row + c)
-            : "memory");
+        tmem_ld_32x32b_x16(t_row + c, r);
         tmem_ld_wait();
       } else {
 #pragma unroll
         for (int t = 0; t < 16; ++t) r[t] = 0u;
       }
+      float part[16];
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        float acc = __uint_as_float(r[t]);
-        for (int pr = 0; pr < sp.split - 1; ++pr) acc += reduce_buf[(pr * sp.nt + c + t) * 128 + wrow];
-        const int tok = c + t;
-        if (tok < p.m && n_global < p.n) {
-          const float v = acc * alpha;
-          if constexpr (sizeof(OutT) == 4) d[(int64_t)tok * p.n + n_global] = v;
-          else if constexpr (std::is_same<OutT, __half>::value) d[(int64_t)tok * p.n + n_global] = __float2half_rn(v);
-          else d[(int64_t)tok * p.n + n_global] = __float2bfloat16_rn(v);
+      for (int t = 0; t < 16; ++t) part[t] = __uint_as_float(r[t]);
+      if (have_peers) {
+        for (int pr = 0; pr < sp.split - 1; ++pr) {
+          const float4* src = reinterpret_cast<const float4*>(reduce_buf + (pr * 128 + wrow) * ld + c);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const float4 f = src[v];
+            part[4 * v] += f.x; part[4 * v + 1] += f.y; part[4 * v + 2] += f.z; part[4 * v + 3] += f.w;
+          }
         }
       }
+      // Transpose through shared memory: this thread holds 16 tokens of one output column, the output rows are
+      // tokens.  Writing them as they are costs 16 two-byte stores per thread; staged, a thread stores 16 bytes.
+      if (c != 0) named_barrier_sync(1, 128);            // the previous chunk has left the staging tile
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const float v = part[t] * alpha;
+        if constexpr (sizeof(OutT) == 4) out_tile[t * 128 + wrow] = v;
+        else if constexpr (std::is_same<OutT, __half>::value) out_tile[t * 128 + wrow] = __float2half_rn(v);
+        else out_tile[t * 128 + wrow] = __float2bfloat16_rn(v);
+      }
+      named_barrier_sync(1, 128);
+      constexpr int kSegs = 128 * (int)sizeof(OutT) / 16;   // 16-byte segments per token row
+      constexpr int kSegElems = 16 / (int)sizeof(OutT);
+      for (int sidx = (int)threadIdx.x - 64; sidx < 16 * kSegs; sidx += 128) {
+        const int t = sidx / kSegs, seg = sidx % kSegs;
+        const int tok = c + t, col = n_tile * 128 + seg * kSegElems;
+        if (tok < p.m && col < p.n)
+          *reinterpret_cast<uint4*>(d + (int64_t)tok * p.n + col) = *reinterpret_cast<const uint4*>(out_tile + t * 128 + seg * kSegElems);
+      }
     }
   }
+  if (sp.split > 1) cluster_wait();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 1) tmem_dealloc(tmem_base, kSkinnyTmemCols);
+}
+
+// Cluster size for n_tiles weight tiles and total_stages stages of K: double it while all CTAs still run in
+// one wave and every rank keeps enough stages to pay for the exchange of partial sums, whose cost grows with
+// the token count.  Measured on B200 (cold L2, 128 x 1024 stages): K = 14336, N = 4096 takes 20 / 15.5 / 12.6 us
+// with 1 / 2 / 4 ranks at 16 tokens and 21.4 / 16.5 / 17.2 us at 64 tokens; at K = 4096 splitting gains
+// nothing at 64 tokens and up to 0.5 us at 16.
+inline int skinny_split(int nt, int n_tiles, int total_stages, int sm_count) {
+  const int min_stages_per_rank = nt <= 32 ? 2 : 4;
+  int split = 1;
+  while (split < kSkinnyMaxSplit && n_tiles * split * 2 <= sm_count &&
+         total_stages >= split * 2 * min_stages_per_rank)
+    split *= 2;
+  return split;
+}
+
+// Shapes this kernel is the better choice for: up to 64 tokens, unless the weight tiles alone need more than
+// one wave of CTAs and the tokens fill half of a 128-row tile anyway.
+inline bool skinny_preferred(int64_t m, int64_t n, int sm_count) {
+  if (m > kSkinnyMaxTokens) return false;
+  return m <= 32 || ceil_div(n, 128) <= sm_count;
 }
 
 template <bool MX, typename OutT>
@@ -244,39 +378,49 @@ int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_c
   using C = SkinnyCfg<MX>;
   SkinnyParams sp{};
   sp.g = base;
+  sp.w = b;
   const int m = base.m, n = base.n, k = base.k;
   sp.nt = (int)round_up(m, 16);
   const int n_tiles = (int)ceil_div(n, 128);
-  const int total_stages = (int)ceil_div(k, kStageK);
-  // K split: enough CTAs to cover the SMs, at least two stages per rank, and the peers' partial sums
-  // must fit the leader's reduce buffer
-  int split = 1;
-  while (split < 4 && n_tiles * split < sm_count && total_stages / (split * 2) >= 2 &&
-         (uint32_t)sp.nt * (uint32_t)(split * 2 - 1) * 512u <= kSkinnyReduceBytes)
-    split *= 2;
-  sp.split = split;
-  sp.stages_per_rank = (int)ceil_div(total_stages, split);
-  sp.stage_bytes = (uint32_t)round_up(C::kWBytes + (uint32_t)sp.nt * kStageKBytes + 2 * C::kSfBytes, 1024);
-  sp.num_stages = (int)std::min<int64_t>(sp.stages_per_rank, (kSmemLimit - 2048 - kSkinnyReduceBytes) / sp.stage_bytes);
-  sp.num_stages = std::max(1, std::min(sp.num_stages, 8));
-  const uint32_t smem_bytes = kSkinnyReduceBytes + (uint32_t)sp.num_stages * sp.stage_bytes + 2048;
+  const int total_stages = (int)ceil_div(k, kSkinnyStageK);
+  sp.stage_bytes =
+      (uint32_t)round_up(kSkinnyBoxes * (C::kWBoxBytes + (uint32_t)sp.nt * kStageKBytes) + 2 * C::kSfBytes, 1024);
+  const uint32_t budget = (uint32_t)kSmemLimit - 2048u;
+  const int max_stages = (int)(budget / sp.stage_bytes);
+  sp.split = skinny_split(sp.nt, n_tiles, total_stages, sm_count);
+  sp.stages_per_rank = (int)ceil_div(total_stages, sp.split);
+  sp.num_stages = std::max(1, std::min(sp.stages_per_rank, max_stages));
+  // The peers' partial sums get a buffer of their own behind the ring when it fits; otherwise they go into
+  // the leader's drained stage area (one more cluster barrier on the critical path).
+  const uint32_t reduce_bytes = sp.split > 1 ? skinny_reduce_bytes(sp.nt, sp.split) : 0u;
+  const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
+  uint32_t smem_bytes;
+  if (ring_bytes + reduce_bytes <= budget) {
+    sp.reduce_offset = sp.split > 1 ? ring_bytes : 1u;   // any non-zero value when there is nothing to reduce
+    smem_bytes = ring_bytes + reduce_bytes + 2048;
+  } else {
+    NVFP_REQUIRE(reduce_bytes + kSkinnyOutTileBytes <= ring_bytes,
+                 "internal: partial sums of %u bytes do not fit %u bytes of stages", reduce_bytes, ring_bytes);
+    sp.reduce_offset = 0;
+    smem_bytes = ring_bytes + 2048;
+  }
   CUtensorMap map_w, map_x;
   if (int rc = make_operand_map(&map_w, b, n, k, 128)) return rc;
   if (int rc = make_operand_map(&map_x, a, m, k, sp.nt)) return rc;
   auto kernel = fp4_gemm_skinny_kernel<MX, OutT>;
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(n_tiles * split));
+  cfg.gridDim = dim3((unsigned)(n_tiles * sp.split));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.x = (unsigned)sp.split;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = sp.split > 1 ? 1 : 0;
   NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, sp));
   return NVFP_OK;
 }

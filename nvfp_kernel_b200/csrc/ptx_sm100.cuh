@@ -243,6 +243,10 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+// Barrier `id` (1..15; 0 is __syncthreads) among `threads` threads of the CTA, whole warps only.
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
@@ -269,6 +273,27 @@ __device__ __forceinline__ uint32_t num_clusters_x() {
 // All threads of all CTAs of the cluster.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The two halves of cluster_sync_all, for work that can be done between arriving and waiting.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Bulk copy from this CTA's shared memory into the shared memory of a CTA of the cluster (both given as
+// 16-byte aligned addresses, size a multiple of 16); the bytes are reported to an mbarrier of the destination CTA.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_smem, uint32_t bytes,
+                                                 uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(src_smem), "r"(bytes), "r"(cluster_bar) : "memory");
+}
+// The 128-byte line holding src into L2; nothing to wait for.
+__device__ __forceinline__ void prefetch_l2(const void* src) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(src) : "memory");
 }
 // shared::cta address -> shared::cluster address of the same offset in CTA `rank`.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
