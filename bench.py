@@ -37,6 +37,11 @@ M = N_PER_GPU = K = 8192
 METRIC = "nvfp4_gemm_tflops_m8192_n8192_k8192"
 NOMINAL_FP4_TFLOPS = 9000.0
 NOMINAL_HBM_GBS = 8000.0
+# DRAM bytes the GEMM launch of this workload moved under ncu (90.4 MB read + 104.0 MB written: both operands and
+# their scales read once; of the 134 MB of output, 104 MB reached DRAM before the kernel ended, the rest sat in L2).
+GEMM_DRAM_BYTES_PER_LAUNCH = 194.4e6
+# operands (2 x M*K/2) + scales (2 x M*K/16) + bf16 output
+GEMM_ALGORITHMIC_BYTES = 2 * (M * K // 2) + 2 * (M * K // 16) + 2 * M * N_PER_GPU
 
 
 def load_peaks():
@@ -315,7 +320,11 @@ def main_ours(args, rank: int, world: int, local_rank: int):
                     "quant_frac_of_nominal_8tbs": quant_gbs / NOMINAL_HBM_GBS,
                     "amax_ms": t_amax, "amax_gbs": amax_gbs},
         "roofline": {"bound": "tensor", "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
-                     "frac": gemm_tflops / fp4_peak, "traffic": None, "kernel": "fp4_gemm_pair_kernel",
+                     "frac": gemm_tflops / fp4_peak, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH,
+                     "traffic_unit": "bytes per launch, dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture "
+                                     "of this launch (profiles/fp4_gemm_pair_kernel_8192.txt); algorithmic bytes: "
+                                     f"{GEMM_ALGORITHMIC_BYTES / 1e6:.1f} MB",
+                     "kernel": "fp4_gemm_pair_kernel",
                      "peak_basis": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s); "
                                    "no FP4 peak is measured on this pool",
                      "frac_of_nominal_9pflops": gemm_tflops / NOMINAL_FP4_TFLOPS,
