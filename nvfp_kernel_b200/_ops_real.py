@@ -155,6 +155,18 @@ def activation_scales(input: torch.Tensor, gs_weight: torch.Tensor, scratch: tor
     return gs, alpha
 
 
+def dynamic_scaled_fp4_quant(input: torch.Tensor, scratch: torch.Tensor, gs_weight: torch.Tensor | None = None):
+    """Per-tensor dynamic NVFP4 quantization in one pass over the input:
+    (fp4, scales, gs, alpha) with gs = 2688/max|input|, (fp4, scales) = scaled_fp4_quant(input, gs) bit for bit and
+    alpha = 1/(gs*gs_weight) (None without gs_weight).  `scratch` as for activation_scales."""
+    input, output, output_scale = _quant_common(input, 16)
+    out = torch.empty(2, dtype=torch.float32, device=input.device)
+    gs, alpha = out[:1], out[1:]
+    ext = _load_scaled_fp4_ops(("dynamic_scaled_fp4_quant",))
+    ext.dynamic_scaled_fp4_quant(output, output_scale, gs, alpha, scratch, input, gs_weight)
+    return output, output_scale.view(torch.float8_e4m3fn), gs, (alpha if gs_weight is not None else None)
+
+
 def alpha_from_scales(gs_a: torch.Tensor, gs_b: torch.Tensor) -> torch.Tensor:
     out = torch.empty(1, dtype=torch.float32, device=gs_a.device)
     ext = _load_scaled_fp4_ops(("alpha_from_scales",))

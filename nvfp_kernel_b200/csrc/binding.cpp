@@ -215,6 +215,34 @@ void activation_scales(torch::Tensor& gs_out, torch::Tensor& alpha_out, torch::T
                                       static_cast<const float*>(gs_weight.data_ptr()), current_stream(input)));
 }
 
+// output / output_sf as for scaled_fp4_quant_sm1xxa; gs_out and alpha_out: fp32 [1]; gs_weight: fp32 [1] or
+// an undefined tensor (then alpha_out is not written).
+void dynamic_scaled_fp4_quant(torch::Tensor& output, torch::Tensor& output_sf, torch::Tensor& gs_out,
+                              torch::Tensor& alpha_out, torch::Tensor& scratch, torch::Tensor const& input,
+                              std::optional<torch::Tensor> const& gs_weight) {
+  TORCH_CHECK(input.dim() == 2 && input.stride(1) == 1, "input must be a matrix with dense rows");
+  TORCH_CHECK(output.is_cuda() && output_sf.is_cuda() && gs_out.is_cuda() && alpha_out.is_cuda() && scratch.is_cuda() &&
+                  input.is_cuda(), "all tensors must be CUDA tensors");
+  TORCH_CHECK(output.is_contiguous() && output_sf.is_contiguous(), "outputs must be contiguous");
+  TORCH_CHECK(gs_out.scalar_type() == at::ScalarType::Float && alpha_out.scalar_type() == at::ScalarType::Float,
+              "scales must be fp32");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 32, "scratch must hold 32 bytes");
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(output.scalar_type() == at::ScalarType::Byte && output.numel() == m * (n / 2), "output must be uint8 [m, n/2]");
+  TORCH_CHECK(output_sf.element_size() * output_sf.numel() >= nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(n, 16),
+              "output_sf is too small for the padded scale layout");
+  const float* gsw = nullptr;
+  if (gs_weight.has_value() && gs_weight->defined()) {
+    TORCH_CHECK(gs_weight->is_cuda() && gs_weight->scalar_type() == at::ScalarType::Float, "gs_weight must be CUDA fp32");
+    gsw = static_cast<const float*>(gs_weight->data_ptr());
+  }
+  const int dt = dtype_code(input, "Unsupported input data type for quantize_to_fp4.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(input));
+  check_status(nvfp_dynamic_fp4_quant(output.data_ptr(), output_sf.data_ptr(), static_cast<float*>(gs_out.data_ptr()),
+                                      static_cast<float*>(alpha_out.data_ptr()), static_cast<uint32_t*>(scratch.data_ptr()),
+                                      input.data_ptr(), m, n, m > 1 ? input.stride(0) : n, dt, gsw, current_stream(input)));
+}
+
 void alpha_from_scales(torch::Tensor& alpha_out, torch::Tensor const& gs_a, torch::Tensor const& gs_b) {
   TORCH_CHECK(alpha_out.is_cuda() && gs_a.is_cuda() && gs_b.is_cuda(), "all tensors must be CUDA tensors");
   TORCH_CHECK(alpha_out.scalar_type() == at::ScalarType::Float && gs_a.scalar_type() == at::ScalarType::Float &&
@@ -244,6 +272,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scaled_fp4_mm_scatter_add", &scaled_fp4_mm_scatter_add);
   m.def("global_scale", &global_scale);
   m.def("activation_scales", &activation_scales);
+  m.def("dynamic_scaled_fp4_quant", &dynamic_scaled_fp4_quant);
   m.def("alpha_from_scales", &alpha_from_scales);
   m.def("device_status", &device_status);
 }

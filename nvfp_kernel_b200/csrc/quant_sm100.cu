@@ -19,6 +19,7 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "common.h"
 
@@ -29,6 +30,12 @@ __device__ __forceinline__ float rcp_approx_ftz(float a) {
   float b;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(a));
   return b;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns_q() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
 
 __device__ __forceinline__ float mul_ftz(float a, float b) {
@@ -139,11 +146,28 @@ __device__ __forceinline__ void load16(Pack16<T>& v, const T* src, bool aligned3
 // issues its four row segments' loads before touching any of them.  The tile's scale bytes (two
 // 512-byte chunks for NVFP4, one for MXFP4) are staged in shared memory and stored with 16-byte
 // stores; packed nibbles leave as 8 bytes per thread, 64 contiguous bytes per row.
-template <typename T, int BLOCK>
+//
+// DYNAMIC (NVFP4 only): the global scale is not an input but 2688 / max|x| of this very tensor.  Every CTA
+// holds its whole tile in registers after the loads, so the launch (a cooperative one: all CTAs resident)
+// reduces the tile maxima through two words of global memory, waits for the last CTA, and quantizes from
+// the registers: the tensor is read once, in one launch, where a global-scale pass plus a quantize pass read
+// it twice in two.  The wait is bounded; when it runs out the CTA reports through the device status word and
+// goes on with the maximum it sees.
+struct DynamicScale {
+  uint32_t* scratch;      // [max bits, arrivals] x 2 pairs, [4] = which pair this launch uses (self-cleaning)
+  float* gs_out;          // 2688 / max|x|
+  const float* gs_other;  // the other operand's global scale, or null
+  float* alpha_out;       // 1 / (gs_out * gs_other), written when gs_other is given
+  uint32_t* status;       // device status word
+};
+constexpr uint32_t kErrQuantBarrier = 1u << 8;
+
+template <typename T, int BLOCK, bool DYNAMIC>
 __global__ void __launch_bounds__(kThreads)
 quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __restrict__ gs_ptr,
                  uint8_t* __restrict__ out, uint8_t* __restrict__ sf_out, int m, int n,
-                 int num_col_tiles, int num_k_chunks, int mx_rounding, int aligned32) {
+                 int num_col_tiles, int num_k_chunks, int mx_rounding, int aligned32, const DynamicScale dyn) {
+  static_assert(!DYNAMIC || BLOCK == 16, "only NVFP4 has a global scale");
   constexpr int kThreadsPerRow = kTileCols / 16;                    // 8
   constexpr int kRowsPerPass = kThreads / kThreadsPerRow;           // 32
   constexpr int kPasses = kTileRows / kRowsPerPass;                 // 4: all in flight at once
@@ -165,7 +189,7 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
   const bool col_ok = col < n;
 
   float gs = 1.0f, rcp_gs = 1.0f;
-  if (BLOCK == 16) {
+  if (BLOCK == 16 && !DYNAMIC) {
     gs = gs_ptr ? __ldg(gs_ptr) : 1.0f;
     rcp_gs = rcp_approx_ftz(gs);
   }
@@ -180,6 +204,60 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
     v[p].raw[0] = make_uint4(0u, 0u, 0u, 0u);
     v[p].raw[1] = make_uint4(0u, 0u, 0u, 0u);
     if (col_ok && row < m) load16<T>(v[p], in + (int64_t)row * in_stride + col, aligned32 != 0);
+  }
+  if constexpr (DYNAMIC) {
+    __shared__ float warp_max[kThreads / 32];
+    __shared__ float gs_shared;
+    auto mx2 = __habs2(v[0].h2[0]);
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx2 = __hmax2(mx2, __habs2(v[p].h2[i]));
+    float mx = to_float<T>(__hmax(mx2.x, mx2.y));
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    if ((tid & 31) == 0) warp_max[tid >> 5] = mx;
+    __syncthreads();
+    if (tid == 0) {
+      float r = warp_max[0];
+#pragma unroll
+      for (int w = 1; w < kThreads / 32; ++w) r = fmaxf(r, warp_max[w]);
+      uint32_t* toggle = dyn.scratch + 4;
+      const uint32_t t = *reinterpret_cast<volatile uint32_t*>(toggle) & 1u;
+      uint32_t* pair = dyn.scratch + 2u * t;
+      atomicMax(&pair[0], __float_as_uint(r));
+      __threadfence();
+      const bool last = atomicAdd(&pair[1], 1u) == gridDim.x - 1;
+      if (!last) {
+        const uint64_t t0 = global_timer_ns_q();
+        for (uint32_t spin = 0; *reinterpret_cast<volatile uint32_t*>(&pair[1]) < gridDim.x; ++spin) {
+          if ((spin & 255u) == 255u && global_timer_ns_q() - t0 > 2000000000ull) {
+            atomicOr(dyn.status, kErrQuantBarrier);
+            break;
+          }
+        }
+      }
+      __threadfence();
+      float amax = __uint_as_float(*reinterpret_cast<volatile uint32_t*>(&pair[0]));
+      if (amax == 0.0f) amax = 1.0f;
+      // same two roundings as amax_kernel: reciprocal(amax) * 2688
+      const float g = __fmul_rn(__frcp_rn(amax), 448.0f * 6.0f);
+      gs_shared = g;
+      if (last) {
+        *dyn.gs_out = g;
+        if (dyn.gs_other) *dyn.alpha_out = __fdiv_rn(1.0f, __fmul_rn(g, *dyn.gs_other));
+        // This pair stays as it is (the others are still reading it); the OTHER pair is made clean for the
+        // next launch, which the flipped toggle points at.  Every CTA read the toggle before it arrived.
+        uint32_t* other = dyn.scratch + 2u * (t ^ 1u);
+        other[0] = 0u;
+        other[1] = 0u;
+        __threadfence();
+        *toggle = t ^ 1u;
+      }
+    }
+    __syncthreads();
+    gs = gs_shared;
+    rcp_gs = rcp_approx_ftz(gs);
   }
 #pragma unroll
   for (int p = 0; p < kPasses; ++p) {
@@ -366,15 +444,67 @@ int launch_quant(void* out_fp4, void* out_sf, const void* in, const float* gs, i
   const dim3 grid((unsigned)(m_tiles * col_tiles));
   const int aligned32 = (reinterpret_cast<uintptr_t>(in) % 32 == 0 && stride % 16 == 0) ? 1 : 0;
   if (dtype == NVFP_DTYPE_F16) {
-    quant_fp4_kernel<__half, BLOCK><<<grid, kThreads, 0, stream>>>(
+    quant_fp4_kernel<__half, BLOCK, false><<<grid, kThreads, 0, stream>>>(
         static_cast<const __half*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
-        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32);
+        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32, DynamicScale{});
   } else {
-    quant_fp4_kernel<__nv_bfloat16, BLOCK><<<grid, kThreads, 0, stream>>>(
+    quant_fp4_kernel<__nv_bfloat16, BLOCK, false><<<grid, kThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
-        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32);
+        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32, DynamicScale{});
   }
   NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}
+
+// CTAs of the one-pass kernel that can be resident at once on the current device (0 on error).
+template <typename T>
+int dynamic_quant_capacity(int device, int sm_count) {
+  static int cached[64] = {};
+  if (device < 0 || device >= 64) return 0;
+  if (cached[device] == 0) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_fp4_kernel<T, 16, true>, kThreads, 0) != cudaSuccess)
+      return 0;
+    // Two tiles per SM at most: measured on B200 inside a layer's forward, 256 tiles (4096 x 1024) take 23.6 us
+    // in one pass against 27.6 us in two; at 512 tiles the wait for the slowest CTA costs more than the second
+    // read of a tensor that is still in L2 (35.8 against 33.9 us).
+    cached[device] = std::max(1, std::min(per_sm, 2) * sm_count);
+  }
+  return cached[device];
+}
+
+template <typename T>
+int launch_dynamic_quant(void* out_fp4, void* out_sf, float* gs_out, float* alpha_out, uint32_t* scratch, const void* in,
+                         int64_t m, int64_t n, int64_t stride, const float* gs_other, cudaStream_t stream) {
+  DeviceInfo info;
+  if (int rc = current_device_info(&info)) return rc;
+  const int64_t m_tiles = ceil_div(m, kTileRows), col_tiles = ceil_div(n, kTileCols);
+  const int64_t tiles = m_tiles * col_tiles;
+  int device = 0;
+  NVFP_CUDA(cudaGetDevice(&device));
+  if (tiles == 0 || tiles > dynamic_quant_capacity<T>(device, info.sm_count)) {
+    // too large to keep in registers across the grid: global-scale pass, then quantize pass
+    if (int rc = launch_amax<T>(gs_out, scratch, in, m, n, stride, stream, true, gs_other, gs_other ? alpha_out : nullptr))
+      return rc;
+    return launch_quant<16>(out_fp4, out_sf, in, gs_out, m, n, stride,
+                            std::is_same<T, __half>::value ? NVFP_DTYPE_F16 : NVFP_DTYPE_BF16, 0, stream);
+  }
+  DynamicScale dyn{scratch, gs_out, gs_other, alpha_out, device_status_word()};
+  NVFP_REQUIRE(dyn.status != nullptr, "cannot locate the device status word");
+  const int aligned32 = (reinterpret_cast<uintptr_t>(in) % 32 == 0 && stride % 16 == 0) ? 1 : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)tiles);
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  NVFP_CUDA(cudaLaunchKernelEx(&cfg, quant_fp4_kernel<T, 16, true>, static_cast<const T*>(in), stride,
+                               static_cast<const float*>(nullptr), static_cast<uint8_t*>(out_fp4),
+                               static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles,
+                               (int)ceil_div(n / 16, 4), 0, aligned32, dyn));
   return NVFP_OK;
 }
 
@@ -434,6 +564,23 @@ extern "C" int nvfp_activation_scales(float* gs_out, float* alpha_out, uint32_t*
   return in_dtype == NVFP_DTYPE_F16
              ? launch_amax<__half>(gs_out, scratch, in, m, n, in_row_stride, stream, true, gs_weight, alpha_out)
              : launch_amax<__nv_bfloat16>(gs_out, scratch, in, m, n, in_row_stride, stream, true, gs_weight, alpha_out);
+}
+
+extern "C" int nvfp_dynamic_fp4_quant(void* out_fp4, void* out_sf, float* gs_out, float* alpha_out, uint32_t* scratch,
+                                      const void* in, int64_t m, int64_t n, int64_t in_row_stride, int in_dtype,
+                                      const float* gs_weight, void* stream_) {
+  clear_error();
+  if (int rc = check_16bit_input(in, m, n, in_row_stride, in_dtype, 16)) return rc;
+  NVFP_REQUIRE(out_fp4 != nullptr && out_sf != nullptr && gs_out != nullptr && scratch != nullptr, "null pointer");
+  NVFP_REQUIRE(gs_weight == nullptr || alpha_out != nullptr, "alpha output is null although a weight scale is given");
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(out_fp4) & 7) == 0 && (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0,
+               "outputs must be aligned (fp4: 8 bytes, scales: 16 bytes)");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  return in_dtype == NVFP_DTYPE_F16
+             ? launch_dynamic_quant<__half>(out_fp4, out_sf, gs_out, alpha_out, scratch, in, m, n, in_row_stride,
+                                            gs_weight, stream)
+             : launch_dynamic_quant<__nv_bfloat16>(out_fp4, out_sf, gs_out, alpha_out, scratch, in, m, n,
+                                                   in_row_stride, gs_weight, stream);
 }
 
 extern "C" int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const float* gs_b,

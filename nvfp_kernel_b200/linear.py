@@ -155,8 +155,7 @@ class QuantLinear(nn.Module):
         if self.fused_reduce_scatter and self.world > 1 and x2.shape[0] % (32 * self.world) == 0:
             return self._forward_fused_reduce_scatter(x2)
         if self.format == "nvfp4":
-            a_gs, alpha = self._activation_scales(x2)
-            a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
+            a_fp4, a_sf, alpha = self._quantize_activation(x2)
             y = ops.cutlass_scaled_fp4_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha, acc_dtype) \
                 if acc_dtype != torch.float32 else self._mm_f32(a_fp4, a_sf, alpha)
         else:
@@ -179,8 +178,7 @@ class QuantLinear(nn.Module):
         ext = _load_scaled_fp4_ops(("scaled_fp4_mm_multi",))
         code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[self.out_dtype]
         if self.format == "nvfp4":
-            a_gs, alpha = self._activation_scales(x2)
-            a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
+            a_fp4, a_sf, alpha = self._quantize_activation(x2)
         else:
             a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
             alpha = None
@@ -203,8 +201,7 @@ class QuantLinear(nn.Module):
             rb = self._reduce_buffers[m] = ReduceBuffer(m, self.out_features, x2.device, self.process_group)
         ext = _load_scaled_fp4_ops(("scaled_fp4_mm_scatter_add",))
         if self.format == "nvfp4":
-            a_gs, alpha = self._activation_scales(x2)
-            a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
+            a_fp4, a_sf, alpha = self._quantize_activation(x2)
         else:
             a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
             alpha = None
@@ -225,12 +222,15 @@ class QuantLinear(nn.Module):
             out, a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha)
         return out
 
-    def _activation_scales(self, x2: torch.Tensor):
-        """(gs_a, alpha): one launch, except for row-parallel layers whose amax needs an all-reduce."""
+    def _quantize_activation(self, x2: torch.Tensor):
+        """(fp4, scales, alpha) of the NVFP4 activation.  One pass over x2 (global scale, alpha and quantization in
+        one call) except for row-parallel layers, whose maximum needs an all-reduce between the two steps."""
         if self.parallel == "row" and self.world > 1:
             a_gs = self._activation_global_scale(x2)
-            return a_gs, ops.alpha_from_scales(a_gs, self.weight_global_scale)
-        return ops.activation_scales(x2, self.weight_global_scale, self._scale_scratch)
+            a_fp4, a_sf = ops.scaled_fp4_quant(x2, a_gs)
+            return a_fp4, a_sf, ops.alpha_from_scales(a_gs, self.weight_global_scale)
+        a_fp4, a_sf, _, alpha = ops.dynamic_scaled_fp4_quant(x2, self._scale_scratch, self.weight_global_scale)
+        return a_fp4, a_sf, alpha
 
     def _activation_global_scale(self, x2: torch.Tensor) -> torch.Tensor:
         if self.parallel == "row" and self.world > 1:

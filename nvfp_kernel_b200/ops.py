@@ -40,6 +40,7 @@ mxfp4_scaled_mm = _impl.mxfp4_scaled_mm
 global_scale = _impl.global_scale
 alpha_from_scales = _impl.alpha_from_scales
 activation_scales = _impl.activation_scales
+dynamic_scaled_fp4_quant = _impl.dynamic_scaled_fp4_quant
 
 
 def device_status() -> int:

@@ -69,6 +69,21 @@ def capi_global_scale(x: torch.Tensor) -> torch.Tensor:
     return gs
 
 
+def capi_dynamic_quant(x: torch.Tensor, scratch: torch.Tensor, gs_weight: torch.Tensor | None = None, fill: int = 0xAA):
+    """One-pass dynamic NVFP4 quantization through nvfp_dynamic_fp4_quant: (fp4, scales, gs, alpha)."""
+    lib = _capi.load()
+    m, n = x.shape
+    out = torch.full((m, n // 2), fill, dtype=torch.uint8, device=x.device)
+    sf = torch.full(sf_shape(m, n, 16), fill, dtype=torch.uint8, device=x.device)
+    scal = torch.full((2,), float("nan"), dtype=torch.float32, device=x.device)
+    _capi.check(lib.nvfp_dynamic_fp4_quant(out.data_ptr(), sf.data_ptr(), scal[:1].data_ptr(), scal[1:].data_ptr(),
+                                           scratch.data_ptr(), x.data_ptr(), m, n, x.stride(0) if m > 1 else n,
+                                           _dt(x.dtype), gs_weight.data_ptr() if gs_weight is not None else None,
+                                           _stream()))
+    assert _capi.device_status() == 0, "a kernel gave up on a bounded wait"
+    return out, sf, scal[:1], scal[1:]
+
+
 def capi_rcp(x: torch.Tensor) -> torch.Tensor:
     lib = _capi.load()
     y = torch.empty_like(x)

@@ -213,6 +213,40 @@ def test_fused_activation_scales_repeated_calls():
     assert nv.activation_scales(z, gs_w, scratch)[0].item() == 2688.0
 
 
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_one_pass_dynamic_quant_equals_global_scale_then_quantize(dt):
+    """nvfp_dynamic_fp4_quant (maximum, global scale, alpha and quantization in one cooperative launch while the
+    tensor's tiles fit the GPU at once, two launches beyond) must give the bytes of the two-step flow of the
+    reference (speed_test.py:46-49): gs = 2688/max|x|, then scaled_fp4_quant(x, gs).  One scratch, zeroed once,
+    serves all calls, large and small shapes interleaved."""
+    from helpers import capi_dynamic_quant
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    gs_w = torch.tensor([37.25], device="cuda")
+    shapes = [(1, 4096), (16, 4096), (128, 14336), (129, 80), (300, 2064), (2368, 4096), (1, 16), (2432, 4096),
+              (4096, 4096), (17, 8192), (8192, 1024)]
+    for i, shape in enumerate(shapes):
+        dist = ALL_DISTS[i % len(ALL_DISTS)]
+        x = make_input(dist, shape, TORCH_DT[dt], seed=100 + i).cuda()
+        fp4, sf, gs, alpha = capi_dynamic_quant(x, scratch, gs_w)
+        want_gs = (448.0 * 6.0) / torch.abs(x).max().to(torch.float32)
+        assert gs.item() == want_gs.item(), (dist, shape)
+        assert alpha.item() == (1.0 / (want_gs * gs_w)).item(), (dist, shape)
+        ref_fp4, ref_sf = capi_quant(x, gs)
+        assert torch.equal(fp4, ref_fp4), (dist, shape)
+        assert torch.equal(sf, ref_sf), (dist, shape)
+    # strided rows, no weight scale (alpha untouched), all-zero input
+    big = make_input("normal", (64, 512), TORCH_DT[dt], seed=5).cuda()
+    view = big[:, 128:384]
+    fp4, sf, gs, alpha = capi_dynamic_quant(view, scratch, None)
+    assert torch.isnan(alpha).all()
+    ref_fp4, ref_sf = capi_quant(view, gs)
+    assert torch.equal(fp4, ref_fp4) and torch.equal(sf, ref_sf)
+    assert gs.item() == ((448.0 * 6.0) / torch.abs(view).max().to(torch.float32)).item()
+    z = torch.zeros((4, 64), dtype=TORCH_DT[dt], device="cuda")
+    fp4, sf, gs, _ = capi_dynamic_quant(z, scratch, gs_w)
+    assert gs.item() == 2688.0 and not fp4.any()
+
+
 @pytest.mark.parametrize("rounding", ["rceil", "floor"])
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
 def test_mxfp4_bit_exact_vs_cpu_restatement(rounding, dt):
