@@ -5,6 +5,7 @@ from .ops import (
     alpha_from_scales,
     cutlass_scaled_fp4_mm,
     device_status,
+    dynamic_scaled_fp4_quant,
     get_active_backend,
     global_scale,
     mxfp4_scaled_mm,
@@ -13,6 +14,7 @@ from .ops import (
     scaled_mxfp4_quant,
 )
 from .linear import QuantLinear
+from .host_pipeline import HostPipeline
 
 __all__ = [
     "scaled_fp4_quant",
@@ -25,5 +27,7 @@ __all__ = [
     "alpha_from_scales",
     "activation_scales",
     "device_status",
+    "dynamic_scaled_fp4_quant",
     "QuantLinear",
+    "HostPipeline",
 ]

@@ -87,3 +87,35 @@ def test_quantize_linear_layers_of_a_model():
     y = model(x)
     assert y.shape == dense.shape
     assert (y.float() - dense.float()).abs().max() < 0.35 * dense.float().abs().max()
+
+
+def test_host_pipeline_matches_direct_calls():
+    """Calls on pinned host buffers with copy-in, compute and copy-out of consecutive calls overlapped: every
+    result equals layer(x.cuda()).cpu() bit for bit, also when shapes change between calls and when the layer
+    hands back one reused output buffer."""
+    import nvfp_kernel_b200 as nv
+    from nvfp_kernel_b200 import HostPipeline, QuantLinear
+    torch.manual_seed(3)
+    layer = QuantLinear(512, 384, device="cuda").load_weight((torch.randn(384, 512) * 0.05).to(torch.bfloat16).cuda())
+    xs = [(torch.randn(m, 512) * (1 + i)).to(torch.bfloat16).pin_memory() for i, m in enumerate((256, 256, 256, 64, 256, 1))]
+    outs = [torch.empty((x.shape[0], 384), dtype=torch.bfloat16).pin_memory() for x in xs]
+    pipe = HostPipeline(layer, depth=2)
+    for x, o in zip(xs, outs):
+        pipe.submit(x, o)
+    pipe.synchronize()
+    for x, o in zip(xs, outs):
+        assert torch.equal(o, layer(x.cuda()).cpu())
+    static_out = torch.empty((256, 384), dtype=torch.bfloat16, device="cuda")
+
+    def reusing(x):
+        static_out.copy_(layer(x))
+        return static_out
+
+    pipe = HostPipeline(reusing, depth=2, device="cuda", reuses_output=True)
+    outs2 = [torch.empty((256, 384), dtype=torch.bfloat16).pin_memory() for _ in range(3)]
+    for x, o in zip(xs[:3], outs2):
+        pipe.submit(x, o)
+    pipe.synchronize()
+    for x, o in zip(xs[:3], outs2):
+        assert torch.equal(o, layer(x.cuda()).cpu())
+    assert nv.device_status() == 0
