@@ -102,6 +102,16 @@ int nvfp_mxfp4_mm(void* d, const void* a, const void* b, const void* sfa, const 
                   const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, void* stream);
 
 /*
+ * The same product with a bias added in the epilogue: D = alpha * acc + bias[n], rounded once to the output type
+ * (the reference adds a bias, when a layer has one, in a separate pass over D; no counterpart there).
+ *   bias   device, n values of the OUTPUT type (fp16 / bf16 / fp32), 16-byte aligned; NULL = no bias
+ *   mxfp4  0: NVFP4 operands (as nvfp_scaled_fp4_mm), 1: MXFP4 operands (as nvfp_mxfp4_mm; alpha may be NULL)
+ */
+int nvfp_scaled_fp4_mm_bias(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+                            const float* alpha, const void* bias, int64_t m, int64_t n, int64_t k,
+                            int out_dtype, int mxfp4, void* stream);
+
+/*
  * The same GEMM with the [m, n] result written to n_dst (1..8) destinations instead of one, each a
  * row-major matrix with leading dimension dst_ld elements (>= n, multiple of 8), so that a slab can land
  * directly in its columns of a wider gathered matrix: dst[0] is

@@ -38,6 +38,7 @@ PROTOTYPES = {
     "nvfp_reciprocal_approximate_ftz": (_int, [_vp, _vp, _i64, _vp]),
     "nvfp_global_scale": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_activation_scales": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
+    "nvfp_scaled_fp4_mm_bias": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "nvfp_dynamic_fp4_quant": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "nvfp_global_scale_noalloc": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_alpha_from_scales": (_int, [_vp, _vp, _vp, _vp]),

@@ -102,22 +102,37 @@ def _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, sf_dtype):
     assert out_dtype in (torch.float16, torch.bfloat16), f"out_dtype needs to be fp16 or bf16 but got {out_dtype}"
 
 
-def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype) -> torch.Tensor:
-    """out[m,n] = alpha * (a*sfa) @ (b*sfb)^T.  The name is the reference's; the kernel is
-    the hand-written tcgen05 one (no CUTLASS)."""
+def _check_bias(bias, n, out_dtype):
+    assert bias.is_cuda, "bias must be a CUDA tensor"
+    assert bias.ndim == 1 and bias.shape[0] == n, f"bias must have shape ({n},) but got {tuple(bias.shape)}"
+    assert bias.dtype == out_dtype, f"bias.dtype needs to be {out_dtype} but got {bias.dtype}"
+    return bias.contiguous()
+
+
+def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype, bias=None) -> torch.Tensor:
+    """out[m,n] = alpha * (a*sfa) @ (b*sfb)^T (+ bias[n], added in the epilogue before the single rounding).
+    The name is the reference's; the kernel is the hand-written tcgen05 one (no CUTLASS); `bias` is an addition."""
     assert alpha is not None, "alpha must be a CUDA tensor"
     _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, torch.float8_e4m3fn)
     m, n = a.shape[0], b.shape[0]
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if bias is not None:
+        ext = _load_scaled_fp4_ops(("scaled_fp4_mm_bias",))
+        ext.scaled_fp4_mm_bias(out, a, b, block_scale_a, block_scale_b, alpha, _check_bias(bias, n, out_dtype), False)
+        return out
     ext = _load_scaled_fp4_ops(("cutlass_scaled_fp4_mm",))
     ext.cutlass_scaled_fp4_mm(out, a, b, block_scale_a, block_scale_b, alpha)
     return out
 
 
-def mxfp4_scaled_mm(a, b, block_scale_a, block_scale_b, out_dtype, alpha=None) -> torch.Tensor:
+def mxfp4_scaled_mm(a, b, block_scale_a, block_scale_b, out_dtype, alpha=None, bias=None) -> torch.Tensor:
     _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, torch.float8_e8m0fnu)
     m, n = a.shape[0], b.shape[0]
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if bias is not None:
+        ext = _load_scaled_fp4_ops(("scaled_fp4_mm_bias",))
+        ext.scaled_fp4_mm_bias(out, a, b, block_scale_a, block_scale_b, alpha, _check_bias(bias, n, out_dtype), True)
+        return out
     ext = _load_scaled_fp4_ops(("mxfp4_scaled_mm",))
     ext.mxfp4_scaled_mm(out, a, b, block_scale_a, block_scale_b, alpha)
     return out

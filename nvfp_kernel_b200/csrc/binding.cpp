@@ -75,7 +75,8 @@ void scaled_mxfp4_quant(torch::Tensor const& output, torch::Tensor const& input,
 // Argument checks of kernel/nvfp4_scaled_mm_sm120_kernels.cu:222-273 of the reference.
 void scaled_mm_impl(torch::Tensor& D, torch::Tensor const& A, torch::Tensor const& B,
                     torch::Tensor const& A_sf, torch::Tensor const& B_sf,
-                    c10::optional<torch::Tensor> const& alpha, bool mx) {
+                    c10::optional<torch::Tensor> const& alpha, bool mx,
+                    c10::optional<torch::Tensor> const& bias = c10::nullopt) {
   const auto sf_dtype = mx ? at::ScalarType::Float8_e8m0fnu : at::ScalarType::Float8_e4m3fn;
   CHECK_OPERAND(A, at::ScalarType::Byte, "a");
   CHECK_OPERAND(B, at::ScalarType::Byte, "b");
@@ -113,9 +114,24 @@ void scaled_mm_impl(torch::Tensor& D, torch::Tensor const& A, torch::Tensor cons
   else TORCH_CHECK(false, "Unsupported output data type of nvfp4 mm (", D.scalar_type(), ")");
   const at::cuda::OptionalCUDAGuard guard(device_of(A));
   const float* alpha_ptr = alpha.has_value() ? static_cast<const float*>(alpha->data_ptr()) : nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->dim() == 1 && bias->sizes()[0] == n,
+                "bias must be a contiguous CUDA vector of ", n, " elements");
+    TORCH_CHECK(bias->scalar_type() == D.scalar_type(), "bias must have the output's dtype");
+    check_status(nvfp_scaled_fp4_mm_bias(D.data_ptr(), A.data_ptr(), B.data_ptr(), A_sf.data_ptr(), B_sf.data_ptr(),
+                                         alpha_ptr, bias->data_ptr(), m, n, k, dt, mx ? 1 : 0, current_stream(A)));
+    return;
+  }
   auto fn = mx ? nvfp_mxfp4_mm : nvfp_scaled_fp4_mm;
   check_status(fn(D.data_ptr(), A.data_ptr(), B.data_ptr(), A_sf.data_ptr(), B_sf.data_ptr(), alpha_ptr,
                   m, n, k, dt, current_stream(A)));
+}
+
+// D = alpha * (A*A_sf) @ (B*B_sf)^T + bias, one rounding; bias: [n] of D's dtype.
+void scaled_fp4_mm_bias(torch::Tensor& D, torch::Tensor const& A, torch::Tensor const& B, torch::Tensor const& A_sf,
+                        torch::Tensor const& B_sf, c10::optional<torch::Tensor> const& alpha,
+                        torch::Tensor const& bias, bool mx) {
+  scaled_mm_impl(D, A, B, A_sf, B_sf, alpha, mx, bias);
 }
 
 void cutlass_scaled_fp4_mm(torch::Tensor& D, torch::Tensor const& A, torch::Tensor const& B,
@@ -268,6 +284,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reciprocal_approximate_ftz_tensor", &reciprocal_approximate_ftz_tensor);
   m.def("scaled_mxfp4_quant", &scaled_mxfp4_quant);
   m.def("mxfp4_scaled_mm", &mxfp4_scaled_mm);
+  m.def("scaled_fp4_mm_bias", &scaled_fp4_mm_bias);
   m.def("scaled_fp4_mm_multi", &scaled_fp4_mm_multi);
   m.def("scaled_fp4_mm_scatter_add", &scaled_fp4_mm_scatter_add);
   m.def("global_scale", &global_scale);

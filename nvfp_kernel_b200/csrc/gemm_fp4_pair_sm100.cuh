@@ -246,6 +246,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     constexpr int kEarlySteps = 64 / kCols;                  // steps that cover the 48 shared columns
     const int q = warp & 3;
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+    const OutT* bias = static_cast<const OutT*>(p.bias);
     const uint32_t acc_empty_leader = map_to_cta(bar(kAccEmpty), 0);
     const uint32_t staging = smem_base + C::kStages * C::kStageBytes + (uint32_t)(warp - 2) * 2 * C::kStoreBufBytes;
     uint32_t store_count = 0;
@@ -283,18 +284,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {     // eight 16-byte pieces of this thread's 128-byte row
-          uint4 o;
-          if constexpr (sizeof(OutT) == 4) {
-            o.x = __float_as_uint(__uint_as_float(r[4 * j + 0]) * alpha);
-            o.y = __float_as_uint(__uint_as_float(r[4 * j + 1]) * alpha);
-            o.z = __float_as_uint(__uint_as_float(r[4 * j + 2]) * alpha);
-            o.w = __float_as_uint(__uint_as_float(r[4 * j + 3]) * alpha);
-          } else {
-            o.x = pack2<OutT>(__uint_as_float(r[8 * j + 0]) * alpha, __uint_as_float(r[8 * j + 1]) * alpha);
-            o.y = pack2<OutT>(__uint_as_float(r[8 * j + 2]) * alpha, __uint_as_float(r[8 * j + 3]) * alpha);
-            o.z = pack2<OutT>(__uint_as_float(r[8 * j + 4]) * alpha, __uint_as_float(r[8 * j + 5]) * alpha);
-            o.w = pack2<OutT>(__uint_as_float(r[8 * j + 6]) * alpha, __uint_as_float(r[8 * j + 7]) * alpha);
-          }
+          constexpr int kPer = 16 / (int)sizeof(OutT);
+          const int colj = tn * kPairBN + c * kCols + j * kPer;
+          const uint4 o = scale_bias_pack<OutT>(&r[kPer * j], alpha, (bias && colj < p.n) ? bias + colj : nullptr);
           st_shared_v4(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4), o);
         }
         fence_proxy_async_smem();

@@ -234,7 +234,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const int wrow = q * 32 + lane;                 // weight row within the tile = accumulator lane
   const uint32_t ld = skinny_reduce_ld(sp.nt);
   bool have_acc = false;
-  float alpha = 1.0f;
+  float alpha = 1.0f, bias = 0.0f;
   if (epi) {
     // Rows of this tile beyond the ring's first fill, one 128-byte line per instruction; thread = weight row.
     const int row = n_tile * 128 + wrow;
@@ -245,6 +245,11 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       for (int off = byte_begin; off < byte_end; off += 128) prefetch_l2(w_row + off);
     }
     if (rank == 0 && p.alpha) alpha = __ldg(p.alpha);
+    if (rank == 0 && p.bias && row < p.n) {
+      if constexpr (sizeof(OutT) == 4) bias = __ldg(static_cast<const float*>(p.bias) + row);
+      else if constexpr (std::is_same<OutT, __half>::value) bias = __half2float(static_cast<const __half*>(p.bias)[row]);
+      else bias = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row]);
+    }
   }
   if (epi && my_stages > 0) {
     have_acc = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull), 0, abort_flag));
@@ -329,7 +334,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       if (c != 0) named_barrier_sync(1, 128);            // the previous chunk has left the staging tile
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
-        const float v = part[t] * alpha;
+        const float v = fmaf(part[t], alpha, bias);
         if constexpr (sizeof(OutT) == 4) out_tile[t * 128 + wrow] = v;
         else if constexpr (std::is_same<OutT, __half>::value) out_tile[t * 128 + wrow] = __float2half_rn(v);
         else out_tile[t * 128 + wrow] = __float2bfloat16_rn(v);

@@ -70,6 +70,7 @@ struct GemmParams {
   const uint8_t* sfa;
   const uint8_t* sfb;
   const float* alpha;
+  const void* bias;     // n values of the output type added after alpha, or null
   void* d;
   int m, n, k;
   int tiles_m, tiles_n;
@@ -88,31 +89,45 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// 32 consecutive fp32 accumulators of one row * alpha -> 32 outputs, 16-byte stores.
+// Accumulators of 16 bytes' worth of consecutive output columns (8 values of a 16-bit type, 4 of fp32)
+// -> alpha * acc (+ bias) -> packed output.  `bias16` points at the bias of the first of those columns or is null.
 template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t (&r)[32], float alpha) {
-  uint4* dst = reinterpret_cast<uint4*>(dst_elems);
+__device__ __forceinline__ uint4 scale_bias_pack(const uint32_t* r, float alpha, const void* bias16) {
+  uint4 o;
   if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-    for (int v = 0; v < 8; ++v) {
-      uint4 o;
-      o.x = __float_as_uint(__uint_as_float(r[4 * v + 0]) * alpha);
-      o.y = __float_as_uint(__uint_as_float(r[4 * v + 1]) * alpha);
-      o.z = __float_as_uint(__uint_as_float(r[4 * v + 2]) * alpha);
-      o.w = __float_as_uint(__uint_as_float(r[4 * v + 3]) * alpha);
-      dst[v] = o;
-    }
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias16) b = __ldg(static_cast<const float4*>(bias16));
+    o.x = __float_as_uint(fmaf(__uint_as_float(r[0]), alpha, b.x));
+    o.y = __float_as_uint(fmaf(__uint_as_float(r[1]), alpha, b.y));
+    o.z = __float_as_uint(fmaf(__uint_as_float(r[2]), alpha, b.z));
+    o.w = __float_as_uint(fmaf(__uint_as_float(r[3]), alpha, b.w));
   } else {
+    float2 b[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+    if (bias16) {
+      const uint4 raw = __ldg(static_cast<const uint4*>(bias16));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      uint4 o;
-      o.x = pack2<OutT>(__uint_as_float(r[8 * v + 0]) * alpha, __uint_as_float(r[8 * v + 1]) * alpha);
-      o.y = pack2<OutT>(__uint_as_float(r[8 * v + 2]) * alpha, __uint_as_float(r[8 * v + 3]) * alpha);
-      o.z = pack2<OutT>(__uint_as_float(r[8 * v + 4]) * alpha, __uint_as_float(r[8 * v + 5]) * alpha);
-      o.w = pack2<OutT>(__uint_as_float(r[8 * v + 6]) * alpha, __uint_as_float(r[8 * v + 7]) * alpha);
-      dst[v] = o;
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (std::is_same<OutT, __half>::value) b[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        else b[i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      }
     }
+    o.x = pack2<OutT>(fmaf(__uint_as_float(r[0]), alpha, b[0].x), fmaf(__uint_as_float(r[1]), alpha, b[0].y));
+    o.y = pack2<OutT>(fmaf(__uint_as_float(r[2]), alpha, b[1].x), fmaf(__uint_as_float(r[3]), alpha, b[1].y));
+    o.z = pack2<OutT>(fmaf(__uint_as_float(r[4]), alpha, b[2].x), fmaf(__uint_as_float(r[5]), alpha, b[2].y));
+    o.w = pack2<OutT>(fmaf(__uint_as_float(r[6]), alpha, b[3].x), fmaf(__uint_as_float(r[7]), alpha, b[3].y));
   }
+  return o;
+}
+
+// 32 consecutive fp32 accumulators of one row -> 32 outputs, 16-byte stores.  `bias` points at the bias of the
+// first column or is null.
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t (&r)[32], float alpha, const OutT* bias) {
+  uint4* dst = reinterpret_cast<uint4*>(dst_elems);
+  constexpr int kPer = 16 / (int)sizeof(OutT);
+#pragma unroll
+  for (int v = 0; v < 32 / kPer; ++v) dst[v] = scale_bias_pack<OutT>(&r[kPer * v], alpha, bias ? bias + kPer * v : nullptr);
 }
 
 template <int BN, bool MX, typename OutT>
@@ -284,6 +299,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
     OutT* d = static_cast<OutT*>(p.d);
+    const OutT* bias = static_cast<const OutT*>(p.bias);
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
@@ -304,7 +320,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tmem_ld_32x32b_x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col = tn * BN + c * 32;
-        if (row < p.m && col < p.n) store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha);
+        if (row < p.m && col < p.n)
+          store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha, bias ? bias + col : nullptr);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -380,7 +397,9 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
 // column-parallel gather, where the extra ones are peer GPUs' buffers.
 template <bool MX>
 int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
-              const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream) {
+              const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream,
+              const void* bias = nullptr) {
+  NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
   NVFP_REQUIRE(outputs != nullptr && n_out >= 1 && n_out <= kMaxOutputs,
                "between 1 and %d output matrices are supported, got %d", kMaxOutputs, n_out);
   for (int o = 0; o < n_out; ++o)
@@ -413,6 +432,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.sfa = static_cast<const uint8_t*>(sfa);
   p.sfb = static_cast<const uint8_t*>(sfb);
   p.alpha = alpha;
+  p.bias = bias;
   p.d = d;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.sf_k_chunks = (int)ceil_div(k / kBlock, 4);
@@ -471,6 +491,14 @@ extern "C" int nvfp_mxfp4_mm(void* d, const void* a, const void* b, const void* 
                              void* stream) {
   clear_error();
   return scaled_mm<true>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvfp_scaled_fp4_mm_bias(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+                                       const float* alpha, const void* bias, int64_t m, int64_t n, int64_t k,
+                                       int out_dtype, int mxfp4, void* stream) {
+  clear_error();
+  return mxfp4 ? scaled_mm<true>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream), bias)
+               : scaled_mm<false>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream), bias);
 }
 
 extern "C" int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void* a, const void* b,

@@ -154,15 +154,22 @@ class QuantLinear(nn.Module):
             return self._forward_fused_gather(x2, lead)
         if self.fused_reduce_scatter and self.world > 1 and x2.shape[0] % (32 * self.world) == 0:
             return self._forward_fused_reduce_scatter(x2)
+        # the bias rides in the GEMM epilogue (added before the single rounding) wherever the local product is
+        # already the final value of its columns; row-parallel partial sums get it after the reduction
+        fused_bias = None
+        if self.bias is not None and acc_dtype != torch.float32:
+            fused_bias = self._bias_shard() if self.parallel == "column" and self.world > 1 else self.bias
+            fused_bias = fused_bias.detach()
         if self.format == "nvfp4":
             a_fp4, a_sf, alpha = self._quantize_activation(x2)
-            y = ops.cutlass_scaled_fp4_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha, acc_dtype) \
+            y = ops.cutlass_scaled_fp4_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha, acc_dtype,
+                                          bias=fused_bias) \
                 if acc_dtype != torch.float32 else self._mm_f32(a_fp4, a_sf, alpha)
         else:
             a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
-            y = ops.mxfp4_scaled_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), acc_dtype)
+            y = ops.mxfp4_scaled_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), acc_dtype, bias=fused_bias)
         y = self._combine(y)
-        if self.bias is not None:
+        if self.bias is not None and fused_bias is None:
             y = y + (self.bias if y.shape[-1] == self.out_features else self._bias_shard())
         return y.reshape(*lead, y.shape[-1]) if y.shape[0] == x2.shape[0] else y
 

@@ -22,8 +22,9 @@ def scaled_fp4_quant(input: torch.Tensor, input_global_scale: torch.Tensor) -> t
     return _impl.scaled_fp4_quant(input, input_global_scale)
 
 
-def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype) -> torch.Tensor:
-    return _impl.cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype)
+def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype, bias=None) -> torch.Tensor:
+    """The reference's signature plus an optional `bias` ([n], out_dtype) added in the GEMM epilogue."""
+    return _impl.cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype, bias)
 
 
 def reciprocal_approximate_ftz_tensor(x: torch.Tensor):

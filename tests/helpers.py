@@ -45,15 +45,22 @@ def capi_mx_quant(x: torch.Tensor, rounding: str = "rceil", fill: int = 0xAA):
     return out, sf
 
 
-def capi_mm(a, b, sfa, sfb, alpha, out_dtype=torch.bfloat16, mx: bool = False):
+def capi_mm(a, b, sfa, sfb, alpha, out_dtype=torch.bfloat16, mx: bool = False, bias=None):
     lib = _capi.load()
     m, n, k = a.shape[0], b.shape[0], a.shape[1] * 2
     # canary-padded output: the kernel must not write outside [m, n]
     buf = torch.full((m * n + 256,), float("nan"), dtype=out_dtype, device=a.device)
     d = buf[128:128 + m * n].view(m, n)
-    fn = lib.nvfp_mxfp4_mm if mx else lib.nvfp_scaled_fp4_mm
-    _capi.check(fn(d.data_ptr(), a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
-                   alpha.data_ptr() if alpha is not None else None, m, n, k, _dt(out_dtype), _stream()))
+    alpha_ptr = alpha.data_ptr() if alpha is not None else None
+    if bias is not None:
+        assert bias.dtype == out_dtype and bias.numel() == n
+        _capi.check(lib.nvfp_scaled_fp4_mm_bias(d.data_ptr(), a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                                                alpha_ptr, bias.data_ptr(), m, n, k, _dt(out_dtype), 1 if mx else 0,
+                                                _stream()))
+    else:
+        fn = lib.nvfp_mxfp4_mm if mx else lib.nvfp_scaled_fp4_mm
+        _capi.check(fn(d.data_ptr(), a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), alpha_ptr, m, n, k,
+                       _dt(out_dtype), _stream()))
     assert _capi.device_status() == 0, "a kernel gave up on a bounded wait"
     assert torch.isnan(buf[:128]).all() and torch.isnan(buf[128 + m * n:]).all(), "out-of-bounds write"
     return d

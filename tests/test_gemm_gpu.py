@@ -120,6 +120,33 @@ def test_split_k_cluster_path_for_few_rows_and_long_k(m, n, k, mx):
         check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha, block=32 if mx else 16, ue8m0=mx))
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 4096, 4096), (48, 160, 9216), (100, 384, 1024), (128, 96, 512),
+                                   (512, 4096, 1024), (300, 4128, 2048)])
+@pytest.mark.parametrize("mx", [False, True])
+def test_bias_added_in_the_epilogue(m, n, k, mx):
+    """nvfp_scaled_fp4_mm_bias on shapes that reach each of the three kernels (few rows, 128-row tiles, CTA pairs):
+    alpha * acc + bias[n] with ONE rounding.  Checked against the fp32 output of the plain entry point plus the
+    bias in fp32: fp32 output to a few ulps, 16-bit outputs to half an ulp of the 16-bit type plus that."""
+    a, w = gemm_inputs(m, n, k, seed=m + n, w_std=0.05)
+    if mx:
+        a_fp4, a_sf = capi_mx_quant(a.cuda())
+        w_fp4, w_sf = capi_mx_quant(w.cuda())
+        alpha = None
+    else:
+        a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    plain = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.float32, mx=mx)
+    g = torch.Generator().manual_seed(n)
+    bias32 = (torch.randn(n, generator=g) * plain.abs().mean().item() * 2).cuda()
+    for dt, eps in ((torch.float32, 2.0 ** -22), (torch.bfloat16, 2.0 ** -8), (torch.float16, 2.0 ** -11)):
+        bias = bias32.to(dt)
+        out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, dt, mx=mx, bias=bias)
+        want = plain + bias.float()
+        # error budget: rounding of the result to dt, and the rounding of `plain` itself to fp32
+        tol = eps * want.abs() + 2.0 ** -22 * (plain.abs() + bias.float().abs()) + 1e-30
+        bad = (out.float() - want).abs() > tol
+        assert not bad.any(), (dt, int(bad.sum()), float((out.float() - want).abs().max()))
+
+
 def test_config1_vs_reference_pseudo_quant_path():
     """BASELINE config 1 (1024^3, seed 0): real path vs the port of the reference's torch
     pseudo-quant path on CPU (oracle/pseudo_path.py, itself pinned to the reference's output)."""

@@ -31,8 +31,15 @@ def test_quant_linear_equals_reference_flow(m, n, k):
     lin.weight.data.copy_(w)
     q = QuantLinear.from_linear(lin)
     y = q(a)
-    want = _reference_flow(a, w) + lin.bias
-    assert torch.equal(y, want)
+    # without the bias: exactly the reference's flow
+    product = _reference_flow(a, w)
+    q_nobias = QuantLinear(k, n, device="cuda").load_weight(w)
+    assert torch.equal(q_nobias(a), product)
+    # the bias is added in the GEMM epilogue before the one rounding to bf16, so the result is at least as close
+    # to product + bias as adding it to the rounded product would be
+    want = product.float() + lin.bias.float()
+    # (half a bf16 ulp, 2^-8 relative, for the rounding of `product` plus the same for the rounding of y)
+    assert ((y.float() - want).abs() <= 2.0 ** -7 * (product.float().abs() + lin.bias.float().abs()) + 1e-6).all()
     dense = lin(a)
     assert (y.float() - dense.float()).abs().max() < 0.3 * dense.float().abs().max()
     # leading dims are preserved
