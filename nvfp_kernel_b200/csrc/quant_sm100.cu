@@ -332,6 +332,7 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
   if (toggle) scratch += 2u * (*reinterpret_cast<volatile uint32_t*>(toggle) & 1u);
   const int64_t vec_per_row = n / VEC;
   const int64_t total = m * vec_per_row;
+  const bool dense = in_stride == n;            // rows back to back: vector j sits at in + j * VEC, no division
   typename Vec2<T>::type mx2 = zero2<T>();
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += 4 * step) {
@@ -342,8 +343,7 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
       v[u].raw[0] = make_uint4(0u, 0u, 0u, 0u);
       v[u].raw[1] = make_uint4(0u, 0u, 0u, 0u);
       if (j < total) {
-        const int64_t row = j / vec_per_row, c = j % vec_per_row;
-        const T* src = in + row * in_stride + c * VEC;
+        const T* src = dense ? in + j * VEC : in + (j / vec_per_row) * in_stride + (j % vec_per_row) * VEC;
         if (VEC == 16) load16<T>(v[u], src, true);
         else v[u].raw[0] = __ldg(reinterpret_cast<const uint4*>(src));
       }
@@ -400,7 +400,11 @@ int launch_amax(float* gs_out, uint32_t* scratch, const void* in, int64_t m, int
   if (!self_cleaning) NVFP_CUDA(cudaMemsetAsync(scratch, 0, 2 * sizeof(uint32_t), stream));
   const bool wide = n % 16 == 0 && stride % 16 == 0 && reinterpret_cast<uintptr_t>(in) % 32 == 0;
   const int64_t want = ceil_div(m * (n / (wide ? 16 : 8)), 256 * 4);
-  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 5));
+  // Three CTAs per SM: every CTA ends with two atomics on the same words, so the grid stays small, and the sweep
+  // is bound by DRAM reads either way (measured at 8192 x 8192, back to back: 26.5-28 us with 2 to 5 CTAs per SM and
+  // 2, 4 or 8 loads in flight per thread, about 5 TB/s, which is also the rate at which the quantizer reads;
+  // 33-47 us with one CTA per SM; 53 us with one iteration per thread and 16 K CTAs).
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 3));
   if (wide)
     amax_kernel<T, 16><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out, toggle,
                                                  gs_other, alpha_out);
