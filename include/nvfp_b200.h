@@ -215,6 +215,14 @@ int nvfp_alpha_from_scales(float* alpha_out, const float* gs_a, const float* gs_
  */
 int nvfp_device_status(uint32_t* status_out);
 
+/*
+ * Exercises that path without any failure: one thread of a one-CTA kernel waits on an mbarrier nobody arrives
+ * at, gives up after limit_ns (1 ns .. 100 ms), records bit 16 in the status word and the kernel returns
+ * normally.  nvfp_device_status then reports NVFP_ERR_DEVICE_TIMEOUT with that bit and clears the word.  For tests of
+ * the error plumbing; the context stays usable.
+ */
+int nvfp_selftest_wait_timeout(uint64_t limit_ns, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

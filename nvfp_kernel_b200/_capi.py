@@ -43,6 +43,7 @@ PROTOTYPES = {
     "nvfp_global_scale_noalloc": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_alpha_from_scales": (_int, [_vp, _vp, _vp, _vp]),
     "nvfp_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32)]),
+    "nvfp_selftest_wait_timeout": (_int, [ctypes.c_uint64, _vp]),
 }
 
 _lib = None

@@ -474,10 +474,35 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   }
 }
 
+// One thread waits on an mbarrier that nobody ever arrives at, with the same bounded wait the GEMM roles
+// use, and reports the expiry like they do.  Nothing faults and the kernel returns normally.
+constexpr uint32_t kErrSelfTest = 1u << 16;
+__global__ void selftest_wait_kernel(uint32_t* status, uint64_t limit_ns) {
+  __shared__ uint64_t never_completes;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&never_completes), 1);
+    fence_mbar_init();
+    if (!mbar_wait_bounded(smem_u32(&never_completes), 0, &abort_flag, limit_ns)) atomicOr(status, kErrSelfTest);
+  }
+}
+
 }  // namespace
 }  // namespace nvfp
 
 using namespace nvfp;
+
+extern "C" int nvfp_selftest_wait_timeout(uint64_t limit_ns, void* stream) {
+  clear_error();
+  NVFP_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ull, "limit must be between 1 ns and 100 ms, got %llu ns",
+               (unsigned long long)limit_ns);
+  uint32_t* status = device_status_word();
+  NVFP_REQUIRE(status != nullptr, "cannot locate the device status word");
+  selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_ns);
+  NVFP_CUDA(cudaGetLastError());
+  return NVFP_OK;
+}
 
 extern "C" int nvfp_scaled_fp4_mm(void* d, const void* a, const void* b, const void* sfa,
                                   const void* sfb, const float* alpha, int64_t m, int64_t n,

@@ -251,3 +251,25 @@ def test_python_api_and_error_behaviour():
     with pytest.raises(AssertionError, match="fp16 or bf16"):
         nv.cutlass_scaled_fp4_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.float32)
     assert nv.device_status() == 0
+
+
+def test_expired_wait_is_reported_and_the_context_stays_usable():
+    """The failure path of every device-side wait, made to run without a failure: a one-thread kernel waits one
+    millisecond on an mbarrier nobody arrives at (the GEMM's own bounded wait), records its code and returns.
+    The host sees NVFP_ERR_DEVICE_TIMEOUT once, the word is cleared, and the next GEMM is correct."""
+    import ctypes
+    from nvfp_kernel_b200 import _capi
+    lib = _capi.load()
+    assert _capi.device_status() == 0
+    _capi.check(lib.nvfp_selftest_wait_timeout(1_000_000, torch.cuda.current_stream().cuda_stream))
+    word = ctypes.c_uint32(0)
+    rc = lib.nvfp_device_status(ctypes.byref(word))
+    assert rc == _capi.NVFP_ERR_DEVICE_TIMEOUT and word.value == 1 << 16
+    assert b"bounded wait" in lib.nvfp_last_error()
+    assert _capi.device_status() == 0                       # cleared by the read
+    assert lib.nvfp_selftest_wait_timeout(0, None) == _capi.NVFP_ERR_INVALID_ARGUMENT
+    assert lib.nvfp_selftest_wait_timeout(10**9, None) == _capi.NVFP_ERR_INVALID_ARGUMENT
+    a, w = gemm_inputs(64, 128, 256, seed=3)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha))
