@@ -112,6 +112,27 @@ int nvfp_scaled_fp4_mm_bias(void* d, const void* a, const void* b, const void* s
                             int out_dtype, int mxfp4, void* stream);
 
 /*
+ * One call for the forward of an NVFP4 linear layer with online activation quantization, the reference's
+ * FP4GemmWithOnlineActivation.forward (speed_test.py:43-50): d = (1 / (gs_x * gs_w)) * quant(x) @ w^T (+ bias) with
+ * gs_x = rcp(max|x|) * 2688.  Same bytes as nvfp_dynamic_fp4_quant followed by nvfp_scaled_fp4_mm_bias.  For few
+ * rows (the shapes that take the one-pass quantizer and the few-rows GEMM) the GEMM is launched with programmatic
+ * stream serialization: it streams its weights while the quantizer still runs and touches the activation operand
+ * only after the quantizer has finished.
+ *   x          device, [m, k] fp16 / bf16, row stride x_row_stride elements, 16-byte aligned
+ *   w_fp4/w_sf the weight as nvfp_scaled_fp4_quant produced it ([n, k/2] and its swizzled scales); must be complete
+ *              before this call's stream position is reached (it is read before the quantizer finishes)
+ *   w_global_scale  device fp32, the weight's global scale
+ *   bias       n values of the output type or NULL
+ *   workspace  device, nvfp_linear_workspace_bytes(m, k) bytes, 256-byte aligned: quantized activation, its scales,
+ *              gs_x and alpha; contents are dead after the call's kernels have run
+ *   scratch    eight uint32 zeroed once, as for nvfp_activation_scales
+ */
+int64_t nvfp_linear_workspace_bytes(int64_t m, int64_t k);
+int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k, int64_t x_row_stride, int x_dtype,
+                        const void* w_fp4, const void* w_sf, const float* w_global_scale, int64_t n,
+                        const void* bias, void* workspace, uint32_t* scratch, int out_dtype, void* stream);
+
+/*
  * The same GEMM with the [m, n] result written to n_dst (1..8) destinations instead of one, each a
  * row-major matrix with leading dimension dst_ld elements (>= n, multiple of 8), so that a slab can land
  * directly in its columns of a wider gathered matrix: dst[0] is

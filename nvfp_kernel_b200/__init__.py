@@ -8,6 +8,7 @@ from .ops import (
     dynamic_scaled_fp4_quant,
     get_active_backend,
     global_scale,
+    linear_forward,
     mxfp4_scaled_mm,
     reciprocal_approximate_ftz_tensor,
     scaled_fp4_quant,
@@ -28,6 +29,7 @@ __all__ = [
     "activation_scales",
     "device_status",
     "dynamic_scaled_fp4_quant",
+    "linear_forward",
     "QuantLinear",
     "HostPipeline",
 ]

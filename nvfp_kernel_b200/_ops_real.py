@@ -182,6 +182,28 @@ def dynamic_scaled_fp4_quant(input: torch.Tensor, scratch: torch.Tensor, gs_weig
     return output, output_scale.view(torch.float8_e4m3fn), gs, (alpha if gs_weight is not None else None)
 
 
+def linear_forward(input: torch.Tensor, weight_fp4: torch.Tensor, weight_sf: torch.Tensor,
+                   weight_global_scale: torch.Tensor, scratch: torch.Tensor, out_dtype: torch.dtype,
+                   bias: torch.Tensor | None = None) -> torch.Tensor:
+    """out[m, n] of an NVFP4 layer with online activation quantization (the reference's
+    FP4GemmWithOnlineActivation.forward, speed_test.py:43-50) in ONE extension call: global scale, alpha, quantize,
+    GEMM (+ bias).  input: [m, k] fp16/bf16; the weight as scaled_fp4_quant produced it."""
+    assert input.is_cuda and input.ndim == 2, "input must be a CUDA matrix"
+    assert input.dtype in (torch.float16, torch.bfloat16), f"input.dtype needs to be fp16 or bf16 but got {input.dtype}."
+    m, k = input.shape
+    assert k % 32 == 0, f"last dim has to be multiple of 32, but got {k}."
+    if input.stride(-1) != 1 or (m > 1 and input.stride(0) % 8 != 0) or input.data_ptr() % 16 != 0:
+        input = input.contiguous()
+    n = weight_fp4.shape[0]
+    ext = _load_scaled_fp4_ops(("linear_forward", "linear_workspace_bytes"))
+    out = torch.empty((m, n), dtype=out_dtype, device=input.device)
+    workspace = torch.empty(ext.linear_workspace_bytes(m, k), dtype=torch.uint8, device=input.device)
+    if bias is not None:
+        bias = _check_bias(bias, n, out_dtype)
+    ext.linear_forward(out, input, weight_fp4, weight_sf, weight_global_scale, bias, workspace, scratch)
+    return out
+
+
 def alpha_from_scales(gs_a: torch.Tensor, gs_b: torch.Tensor) -> torch.Tensor:
     out = torch.empty(1, dtype=torch.float32, device=gs_a.device)
     ext = _load_scaled_fp4_ops(("alpha_from_scales",))

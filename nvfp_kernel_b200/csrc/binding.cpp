@@ -259,6 +259,46 @@ void dynamic_scaled_fp4_quant(torch::Tensor& output, torch::Tensor& output_sf, t
                                       input.data_ptr(), m, n, m > 1 ? input.stride(0) : n, dt, gsw, current_stream(input)));
 }
 
+// Whole forward of an NVFP4 layer in one call: D = quant(X) @ W^T / (gs_x * gs_w) (+ bias).  `workspace`: uint8,
+// at least linear_workspace_bytes(m, k) bytes, 256-byte aligned.
+int64_t linear_workspace_bytes(int64_t m, int64_t k) { return nvfp_linear_workspace_bytes(m, k); }
+
+void linear_forward(torch::Tensor& D, torch::Tensor const& X, torch::Tensor const& W, torch::Tensor const& W_sf,
+                    torch::Tensor const& gs_w, std::optional<torch::Tensor> const& bias, torch::Tensor& workspace,
+                    torch::Tensor& scratch) {
+  TORCH_CHECK(X.dim() == 2 && X.stride(1) == 1, "input must be a matrix with dense rows");
+  CHECK_OPERAND(W, at::ScalarType::Byte, "weight");
+  TORCH_CHECK(W_sf.is_cuda() && W_sf.is_contiguous(), "weight scales must be a contiguous CUDA tensor");
+  TORCH_CHECK(D.is_cuda() && D.is_contiguous() && X.is_cuda() && gs_w.is_cuda() && workspace.is_cuda() && scratch.is_cuda(),
+              "all tensors must be CUDA tensors");
+  TORCH_CHECK(gs_w.scalar_type() == at::ScalarType::Float, "weight global scale must be fp32");
+  const int64_t m = X.size(0), k = X.size(1), n = W.size(0);
+  TORCH_CHECK(W.dim() == 2 && W.size(1) * 2 == k, "a and b shapes cannot be multiplied (", m, "x", k, " and ", n, "x",
+              W.size(1) * 2, ")");
+  TORCH_CHECK(n % 32 == 0, "Expected n to be divisible by 32, but got b shape: (", W.sizes()[0], "x", W.sizes()[1], ").");
+  TORCH_CHECK(W_sf.element_size() * W_sf.numel() == nvfp_sf_rows_padded(n) * nvfp_sf_cols_padded(k, 16),
+              "scale_b must be padded and swizzled to a shape (", nvfp_sf_rows_padded(n), "x", nvfp_sf_cols_padded(k, 16), ")");
+  TORCH_CHECK(D.dim() == 2 && D.size(0) == m && D.size(1) == n, "out must have shape (", m, "x", n, ")");
+  TORCH_CHECK(workspace.element_size() * workspace.numel() >= nvfp_linear_workspace_bytes(m, k), "workspace too small");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 32, "scratch must hold 32 bytes");
+  int dt;
+  if (D.scalar_type() == at::ScalarType::BFloat16) dt = NVFP_DTYPE_BF16;
+  else if (D.scalar_type() == at::ScalarType::Half) dt = NVFP_DTYPE_F16;
+  else if (D.scalar_type() == at::ScalarType::Float) dt = NVFP_DTYPE_F32;
+  else TORCH_CHECK(false, "Unsupported output data type of nvfp4 mm (", D.scalar_type(), ")");
+  const void* bias_ptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->dim() == 1 && bias->size(0) == n &&
+                    bias->scalar_type() == D.scalar_type(), "bias must be a contiguous CUDA vector of ", n, " elements of the output's dtype");
+    bias_ptr = bias->data_ptr();
+  }
+  const int xdt = dtype_code(X, "Unsupported input data type for quantize_to_fp4.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(X));
+  check_status(nvfp_linear_forward(D.data_ptr(), X.data_ptr(), m, k, m > 1 ? X.stride(0) : k, xdt, W.data_ptr(),
+                                   W_sf.data_ptr(), static_cast<const float*>(gs_w.data_ptr()), n, bias_ptr,
+                                   workspace.data_ptr(), static_cast<uint32_t*>(scratch.data_ptr()), dt, current_stream(X)));
+}
+
 void alpha_from_scales(torch::Tensor& alpha_out, torch::Tensor const& gs_a, torch::Tensor const& gs_b) {
   TORCH_CHECK(alpha_out.is_cuda() && gs_a.is_cuda() && gs_b.is_cuda(), "all tensors must be CUDA tensors");
   TORCH_CHECK(alpha_out.scalar_type() == at::ScalarType::Float && gs_a.scalar_type() == at::ScalarType::Float &&
@@ -290,6 +330,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("global_scale", &global_scale);
   m.def("activation_scales", &activation_scales);
   m.def("dynamic_scaled_fp4_quant", &dynamic_scaled_fp4_quant);
+  m.def("linear_workspace_bytes", &linear_workspace_bytes);
+  m.def("linear_forward", &linear_forward);
   m.def("alpha_from_scales", &alpha_from_scales);
   m.def("device_status", &device_status);
 }

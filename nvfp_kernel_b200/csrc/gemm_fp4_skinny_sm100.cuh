@@ -53,6 +53,9 @@ struct SkinnyParams {
   int num_stages;       // pipeline depth
   uint32_t stage_bytes;
   const void* w;           // weights [n, k/2], for the L2 prefetch
+  int after_producer;      // launched with programmatic stream serialization behind the kernel that writes the
+                           // activation operand, its scales and alpha: weights may be fetched before that kernel
+                           // has finished, everything it writes only after griddepcontrol.wait
   uint32_t reduce_offset;  // leader's buffer for the peers' partial sums: 0 = it reuses the drained stage area
 };
 
@@ -108,8 +111,10 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const uint8_t* sfw_tile = p.sfb + (int64_t)n_tile * p.sf_k_chunks * 512;
 
   // Loads of local stage i (K range [ks * 1024, ks * 1024 + 1024)) into ring slot s; the boxes of one group
-  // report to one barrier.
-  auto load_stage = [&](int i) {
+  // report to one barrier.  `what` selects the weight side (armed with the bytes of both sides), the activation
+  // side, or both.
+  constexpr int kWeights = 1, kActivations = 2;
+  auto load_stage = [&](int i, int what) {
     const int ks = ks_begin + i;
     const uint32_t s = (uint32_t)i % sp.num_stages;
     const uint32_t st = stage_base + s * sp.stage_bytes;
@@ -119,14 +124,17 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       const int chunk0 = ks * C::kChunksPerStage + g * C::kChunksPerGroup;
       const uint32_t sf_bytes = (uint32_t)min(C::kChunksPerGroup, p.sf_k_chunks - chunk0) * 512u;
       const uint32_t full = bar(kFull + (int)s * kSkinnyGroups + g);
-      mbar_arrive_expect_tx(full, (uint32_t)nb * (C::kWBoxBytes + x_box_bytes) + 2 * sf_bytes);
-      for (int b = b0; b < b0 + nb; ++b) {
-        const int kbyte = (ks * kSkinnyBoxes + b) * kStageKBytes;
-        tma_load_2d(st + b * C::kWBoxBytes, &tmap_w, full, kbyte, n_tile * 128);
-        tma_load_2d(st + off_x + b * x_box_bytes, &tmap_x, full, kbyte, 0);
+      if (what & kWeights) {
+        mbar_arrive_expect_tx(full, (uint32_t)nb * (C::kWBoxBytes + x_box_bytes) + 2 * sf_bytes);
+        for (int b = b0; b < b0 + nb; ++b)
+          tma_load_2d(st + b * C::kWBoxBytes, &tmap_w, full, (ks * kSkinnyBoxes + b) * kStageKBytes, n_tile * 128);
+        bulk_load(st + off_sfw + g * C::kSfGroupBytes, sfw_tile + (int64_t)chunk0 * 512, sf_bytes, full);
       }
-      bulk_load(st + off_sfw + g * C::kSfGroupBytes, sfw_tile + (int64_t)chunk0 * 512, sf_bytes, full);
-      bulk_load(st + off_sfx + g * C::kSfGroupBytes, p.sfa + (int64_t)chunk0 * 512, sf_bytes, full);
+      if (what & kActivations) {
+        for (int b = b0; b < b0 + nb; ++b)
+          tma_load_2d(st + off_x + b * x_box_bytes, &tmap_x, full, (ks * kSkinnyBoxes + b) * kStageKBytes, 0);
+        bulk_load(st + off_sfx + g * C::kSfGroupBytes, p.sfa + (int64_t)chunk0 * 512, sf_bytes, full);
+      }
     }
   };
   if (warp == 0) {
@@ -144,7 +152,14 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       prefetch_tensormap(&tmap_w);
       prefetch_tensormap(&tmap_x);
       const int first = min(my_stages, sp.num_stages);
-      for (int i = 0; i < first; ++i) load_stage(i);
+      if (sp.after_producer) {
+        // the weights do not depend on the kernel before this one: fetch them while it still runs
+        for (int i = 0; i < first; ++i) load_stage(i, kWeights);
+        griddep_wait();
+        for (int i = 0; i < first; ++i) load_stage(i, kActivations);
+      } else {
+        for (int i = 0; i < first; ++i) load_stage(i, kWeights | kActivations);
+      }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -168,7 +183,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
           atomicOr(p.status, kErrProducer);
           break;
         }
-        load_stage(i);
+        load_stage(i, kWeights | kActivations);
       }
     }
     __syncwarp();
@@ -244,7 +259,8 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       const int byte_end = min(ks_end * (kSkinnyStageK / 2), p.k / 2);
       for (int off = byte_begin; off < byte_end; off += 128) prefetch_l2(w_row + off);
     }
-    if (rank == 0 && p.alpha) alpha = __ldg(p.alpha);
+    if (sp.after_producer) griddep_wait();         // alpha comes from the kernel before this one
+    if (rank == 0 && p.alpha) alpha = *reinterpret_cast<const volatile float*>(p.alpha);
     if (rank == 0 && p.bias && row < p.n) {
       if constexpr (sizeof(OutT) == 4) bias = __ldg(static_cast<const float*>(p.bias) + row);
       else if constexpr (std::is_same<OutT, __half>::value) bias = __half2float(static_cast<const __half*>(p.bias)[row]);
@@ -379,11 +395,13 @@ inline bool skinny_preferred(int64_t m, int64_t n, int sm_count) {
 }
 
 template <bool MX, typename OutT>
-int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream) {
+int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
+                  bool after_producer = false) {
   using C = SkinnyCfg<MX>;
   SkinnyParams sp{};
   sp.g = base;
   sp.w = b;
+  sp.after_producer = after_producer ? 1 : 0;
   const int m = base.m, n = base.n, k = base.k;
   sp.nt = (int)round_up(m, 16);
   const int n_tiles = (int)ceil_div(n, 128);
@@ -419,13 +437,22 @@ int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_c
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)sp.split;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int num_attrs = 0;
+  if (sp.split > 1) {
+    attr[num_attrs].id = cudaLaunchAttributeClusterDimension;
+    attr[num_attrs].val.clusterDim.x = (unsigned)sp.split;
+    attr[num_attrs].val.clusterDim.y = 1;
+    attr[num_attrs].val.clusterDim.z = 1;
+    ++num_attrs;
+  }
+  if (after_producer) {
+    attr[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++num_attrs;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = sp.split > 1 ? 1 : 0;
+  cfg.numAttrs = num_attrs;
   NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, sp));
   return NVFP_OK;
 }

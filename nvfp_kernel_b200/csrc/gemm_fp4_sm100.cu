@@ -398,7 +398,7 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
 template <bool MX>
 int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream,
-              const void* bias = nullptr) {
+              const void* bias = nullptr, bool after_producer = false) {
   NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
   NVFP_REQUIRE(outputs != nullptr && n_out >= 1 && n_out <= kMaxOutputs,
                "between 1 and %d output matrices are supported, got %d", kMaxOutputs, n_out);
@@ -442,9 +442,9 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   // Few activation rows (decode): weights are streamed once; swap the operands and split K over a cluster.
   if (n_out == 1 && ld == n && skinny_preferred(m, n, info.sm_count)) {
     switch (out_dtype) {
-      case NVFP_DTYPE_BF16: return launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream);
-      case NVFP_DTYPE_F16: return launch_skinny<MX, __half>(p, a, b, info.sm_count, stream);
-      default: return launch_skinny<MX, float>(p, a, b, info.sm_count, stream);
+      case NVFP_DTYPE_BF16: return launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream, after_producer);
+      case NVFP_DTYPE_F16: return launch_skinny<MX, __half>(p, a, b, info.sm_count, stream, after_producer);
+      default: return launch_skinny<MX, float>(p, a, b, info.sm_count, stream, after_producer);
     }
   }
   // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
@@ -524,6 +524,43 @@ extern "C" int nvfp_scaled_fp4_mm_bias(void* d, const void* a, const void* b, co
   clear_error();
   return mxfp4 ? scaled_mm<true>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream), bias)
                : scaled_mm<false>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream), bias);
+}
+
+extern "C" int64_t nvfp_linear_workspace_bytes(int64_t m, int64_t k) {
+  if (m < 0 || k < 0) return -1;
+  return round_up(m * (k / 2), 256) + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256) + 256;
+}
+
+extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k, int64_t x_row_stride, int x_dtype,
+                                   const void* w_fp4, const void* w_sf, const float* w_global_scale, int64_t n,
+                                   const void* bias, void* workspace, uint32_t* scratch, int out_dtype, void* stream_) {
+  clear_error();
+  NVFP_REQUIRE(m >= 0 && n >= 0 && k >= 0, "negative shape");
+  NVFP_REQUIRE(k % 32 == 0, "Expected k to be divisible by 32, but got k: %lld.", (long long)k);
+  NVFP_REQUIRE(x != nullptr && workspace != nullptr && scratch != nullptr && w_global_scale != nullptr, "null pointer");
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  NVFP_REQUIRE(x_dtype == NVFP_DTYPE_F16 || x_dtype == NVFP_DTYPE_BF16,
+               "Unsupported input data type for quantize_to_fp4 (dtype code %d).", x_dtype);
+  NVFP_REQUIRE(x_row_stride >= k && x_row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0,
+               "activation must be 16-byte aligned with a row stride that is >= k and a multiple of 8 elements");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* a_fp4 = ws;
+  uint8_t* a_sf = a_fp4 + round_up(m * (k / 2), 256);
+  float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
+  float* alpha = gs + 1;
+  if (m == 0 || n == 0) return NVFP_OK;
+  // The GEMM may start under the quantizer only if the quantizer is the single cooperative launch and the GEMM
+  // is the kernel that knows to fetch nothing but weights before griddepcontrol.wait.
+  DeviceInfo info;
+  if (int rc = current_device_info(&info)) return rc;
+  const bool overlap = dynamic_fp4_quant_is_one_pass(m, k, x_dtype) && skinny_preferred(m, n, info.sm_count);
+  bool one_pass = false;
+  if (int rc = dynamic_fp4_quant_launch(a_fp4, a_sf, gs, alpha, scratch, x, m, k, x_row_stride, x_dtype, w_global_scale,
+                                        overlap, &one_pass, stream))
+    return rc;
+  return scaled_mm<false>(&d, 1, n, a_fp4, w_fp4, a_sf, w_sf, alpha, m, n, k, out_dtype, stream, bias,
+                          overlap && one_pass);
 }
 
 extern "C" int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void* a, const void* b,

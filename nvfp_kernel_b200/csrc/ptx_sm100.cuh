@@ -83,6 +83,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// ------------------------------------------------ programmatic dependent launch ---
+// In a kernel launched with the programmatic-stream-serialization attribute: blocks until the kernels before
+// it in the stream have completed and their writes are visible.  A no-op otherwise.
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel in the stream, if it was launched with that attribute, start while this grid still runs.
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // --------------------------------------------------------------------- TMA ---
 // 2-D tiled load global -> shared, completion reported to an mbarrier of this CTA.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar,

@@ -159,6 +159,7 @@ struct DynamicScale {
   const float* gs_other;  // the other operand's global scale, or null
   float* alpha_out;       // 1 / (gs_out * gs_other), written when gs_other is given
   uint32_t* status;       // device status word
+  int release_next;       // let a programmatically dependent next kernel start while this one runs
 };
 constexpr uint32_t kErrQuantBarrier = 1u << 8;
 
@@ -168,6 +169,9 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
                  uint8_t* __restrict__ out, uint8_t* __restrict__ sf_out, int m, int n,
                  int num_col_tiles, int num_k_chunks, int mx_rounding, int aligned32, const DynamicScale dyn) {
   static_assert(!DYNAMIC || BLOCK == 16, "only NVFP4 has a global scale");
+  if constexpr (DYNAMIC) {
+    if (dyn.release_next) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
   constexpr int kThreadsPerRow = kTileCols / 16;                    // 8
   constexpr int kRowsPerPass = kThreads / kThreadsPerRow;           // 32
   constexpr int kPasses = kTileRows / kRowsPerPass;                 // 4: all in flight at once
@@ -404,7 +408,9 @@ int launch_amax(float* gs_out, uint32_t* scratch, const void* in, int64_t m, int
   // is bound by DRAM reads either way (measured at 8192 x 8192, back to back: 26.5-28 us with 2 to 5 CTAs per SM and
   // 2, 4 or 8 loads in flight per thread, about 5 TB/s, which is also the rate at which the quantizer reads;
   // 33-47 us with one CTA per SM; 53 us with one iteration per thread and 16 K CTAs).
-  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)info.sm_count * 3));
+  // Tensors that one wave of five CTAs per SM covers get one iteration per thread (latency matters there).
+  const int64_t ctas = want <= (int64_t)info.sm_count * 5 ? want : (int64_t)info.sm_count * 3;
+  const unsigned grid = (unsigned)std::max<int64_t>(1, ctas);
   if (wide)
     amax_kernel<T, 16><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out, toggle,
                                                  gs_other, alpha_out);
@@ -478,22 +484,30 @@ int dynamic_quant_capacity(int device, int sm_count) {
 }
 
 template <typename T>
-int launch_dynamic_quant(void* out_fp4, void* out_sf, float* gs_out, float* alpha_out, uint32_t* scratch, const void* in,
-                         int64_t m, int64_t n, int64_t stride, const float* gs_other, cudaStream_t stream) {
+bool dynamic_quant_fits(int64_t m, int64_t n) {
   DeviceInfo info;
-  if (int rc = current_device_info(&info)) return rc;
+  int device = 0;
+  if (current_device_info(&info) != NVFP_OK || cudaGetDevice(&device) != cudaSuccess) return false;
+  const int64_t tiles = ceil_div(m, kTileRows) * ceil_div(n, kTileCols);
+  return tiles > 0 && tiles <= dynamic_quant_capacity<T>(device, info.sm_count);
+}
+
+template <typename T>
+int launch_dynamic_quant(void* out_fp4, void* out_sf, float* gs_out, float* alpha_out, uint32_t* scratch, const void* in,
+                         int64_t m, int64_t n, int64_t stride, const float* gs_other, cudaStream_t stream,
+                         bool release_next = false, bool* one_pass = nullptr) {
   const int64_t m_tiles = ceil_div(m, kTileRows), col_tiles = ceil_div(n, kTileCols);
   const int64_t tiles = m_tiles * col_tiles;
-  int device = 0;
-  NVFP_CUDA(cudaGetDevice(&device));
-  if (tiles == 0 || tiles > dynamic_quant_capacity<T>(device, info.sm_count)) {
+  const bool fits = dynamic_quant_fits<T>(m, n);
+  if (one_pass) *one_pass = fits;
+  if (!fits) {
     // too large to keep in registers across the grid: global-scale pass, then quantize pass
     if (int rc = launch_amax<T>(gs_out, scratch, in, m, n, stride, stream, true, gs_other, gs_other ? alpha_out : nullptr))
       return rc;
     return launch_quant<16>(out_fp4, out_sf, in, gs_out, m, n, stride,
                             std::is_same<T, __half>::value ? NVFP_DTYPE_F16 : NVFP_DTYPE_BF16, 0, stream);
   }
-  DynamicScale dyn{scratch, gs_out, gs_other, alpha_out, device_status_word()};
+  DynamicScale dyn{scratch, gs_out, gs_other, alpha_out, device_status_word(), release_next ? 1 : 0};
   NVFP_REQUIRE(dyn.status != nullptr, "cannot locate the device status word");
   const int aligned32 = (reinterpret_cast<uintptr_t>(in) % 32 == 0 && stride % 16 == 0) ? 1 : 0;
   cudaLaunchConfig_t cfg = {};
@@ -513,6 +527,21 @@ int launch_dynamic_quant(void* out_fp4, void* out_sf, float* gs_out, float* alph
 }
 
 }  // namespace
+
+int dynamic_fp4_quant_launch(void* out_fp4, void* out_sf, float* gs_out, float* alpha_out, uint32_t* scratch,
+                             const void* in, int64_t m, int64_t n, int64_t stride, int in_dtype,
+                             const float* gs_weight, bool release_next, bool* one_pass, cudaStream_t stream) {
+  return in_dtype == NVFP_DTYPE_F16
+             ? launch_dynamic_quant<__half>(out_fp4, out_sf, gs_out, alpha_out, scratch, in, m, n, stride, gs_weight,
+                                            stream, release_next, one_pass)
+             : launch_dynamic_quant<__nv_bfloat16>(out_fp4, out_sf, gs_out, alpha_out, scratch, in, m, n, stride,
+                                                   gs_weight, stream, release_next, one_pass);
+}
+
+bool dynamic_fp4_quant_is_one_pass(int64_t m, int64_t n, int in_dtype) {
+  return in_dtype == NVFP_DTYPE_F16 ? dynamic_quant_fits<__half>(m, n) : dynamic_quant_fits<__nv_bfloat16>(m, n);
+}
+
 }  // namespace nvfp
 
 using namespace nvfp;

@@ -160,7 +160,11 @@ class QuantLinear(nn.Module):
         if self.bias is not None and acc_dtype != torch.float32:
             fused_bias = self._bias_shard() if self.parallel == "column" and self.world > 1 else self.bias
             fused_bias = fused_bias.detach()
-        if self.format == "nvfp4":
+        if self.format == "nvfp4" and acc_dtype != torch.float32:
+            # one extension call: global scale, alpha, quantize and GEMM (+ bias)
+            y = ops.linear_forward(x2, self.weight_fp4, self.weight_sf, self.weight_global_scale, self._scale_scratch,
+                                   acc_dtype, bias=fused_bias)
+        elif self.format == "nvfp4":
             a_fp4, a_sf, alpha = self._quantize_activation(x2)
             y = ops.cutlass_scaled_fp4_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha, acc_dtype,
                                           bias=fused_bias) \

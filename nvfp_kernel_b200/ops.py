@@ -42,6 +42,7 @@ global_scale = _impl.global_scale
 alpha_from_scales = _impl.alpha_from_scales
 activation_scales = _impl.activation_scales
 dynamic_scaled_fp4_quant = _impl.dynamic_scaled_fp4_quant
+linear_forward = _impl.linear_forward
 
 
 def device_status() -> int:

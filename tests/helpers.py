@@ -91,6 +91,23 @@ def capi_dynamic_quant(x: torch.Tensor, scratch: torch.Tensor, gs_weight: torch.
     return out, sf, scal[:1], scal[1:]
 
 
+def capi_linear_forward(x, w_fp4, w_sf, w_gs, scratch, out_dtype=torch.bfloat16, bias=None):
+    """Whole layer forward through nvfp_linear_forward."""
+    lib = _capi.load()
+    m, k = x.shape
+    n = w_fp4.shape[0]
+    buf = torch.full((m * n + 256,), float("nan"), dtype=out_dtype, device=x.device)
+    d = buf[128:128 + m * n].view(m, n)
+    ws = torch.empty(lib.nvfp_linear_workspace_bytes(m, k), dtype=torch.uint8, device=x.device)
+    _capi.check(lib.nvfp_linear_forward(d.data_ptr(), x.data_ptr(), m, k, x.stride(0) if m > 1 else k, _dt(x.dtype),
+                                        w_fp4.data_ptr(), w_sf.data_ptr(), w_gs.data_ptr(), n,
+                                        bias.data_ptr() if bias is not None else None, ws.data_ptr(),
+                                        scratch.data_ptr(), _dt(out_dtype), _stream()))
+    assert _capi.device_status() == 0, "a kernel gave up on a bounded wait"
+    assert torch.isnan(buf[:128]).all() and torch.isnan(buf[128 + m * n:]).all(), "out-of-bounds write"
+    return d
+
+
 def capi_rcp(x: torch.Tensor) -> torch.Tensor:
     lib = _capi.load()
     y = torch.empty_like(x)

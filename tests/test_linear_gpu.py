@@ -126,3 +126,25 @@ def test_host_pipeline_matches_direct_calls():
     for x, o in zip(xs[:3], outs2):
         assert torch.equal(o, layer(x.cuda()).cpu())
     assert nv.device_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 6144, 4096), (8, 4096, 14336), (48, 256, 1024), (128, 512, 2048),
+                                   (300, 384, 1024), (2048, 4096, 4096)])
+def test_one_call_forward_equals_the_separate_calls(m, n, k):
+    """nvfp_linear_forward (quantizer and GEMM issued by one call; for few rows the GEMM is launched under the
+    quantizer and streams its weights meanwhile) gives the bytes of nvfp_dynamic_fp4_quant + nvfp_scaled_fp4_mm(_bias),
+    call after call with changing inputs, with and without a bias."""
+    from helpers import capi_dynamic_quant, capi_global_scale, capi_linear_forward, capi_mm, capi_quant
+    a, w = gemm_inputs(m, n, k, seed=m + n + k, w_std=0.05)
+    a, w = a.cuda(), w.cuda()
+    w_gs = capi_global_scale(w)
+    w_fp4, w_sf = capi_quant(w, w_gs)
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    bias = (torch.randn(n) * 0.1).to(torch.bfloat16).cuda()
+    for i in range(4):
+        x = (a * (1.0 + 0.5 * i)).to(torch.bfloat16)
+        b = bias if i % 2 else None
+        got = capi_linear_forward(x, w_fp4, w_sf, w_gs, scratch, torch.bfloat16, b)
+        a_fp4, a_sf, _, alpha = capi_dynamic_quant(x, scratch, w_gs)
+        want = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16, bias=b)
+        assert torch.equal(got, want), (i, m, n, k)
