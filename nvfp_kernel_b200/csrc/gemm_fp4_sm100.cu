@@ -77,6 +77,8 @@ struct GemmParams {
   int sf_k_chunks;      // 512-byte chunks per 128-row scale tile along K
   int sfb_row_tiles;    // 128-row scale tiles of B
   uint32_t* status;
+  int after_producer;   // launched with programmatic stream serialization behind the kernel that writes A, its
+                        // scales and alpha: B and its scales may be fetched before that kernel has finished
 };
 
 template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -184,33 +186,51 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------ producer ---
     if (elect_one()) {
-      uint32_t kc = 0;   // stage fills issued so far
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      // Fill kc of this CTA: K stage kc % k_stages of its (kc / k_stages)-th tile, into ring slot kc % kStages.
+      // `what`: the B side (which also arms the barrier with the bytes of both sides), the A side, or both.
+      constexpr int kSideB = 1, kSideA = 2;
+      auto fill = [&](uint32_t kc, int what) {
+        const int tile = (int)blockIdx.x + (int)(kc / (uint32_t)k_stages) * (int)gridDim.x, ks = (int)(kc % (uint32_t)k_stages);
         const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
         const int halves = min(C::kHalves, p.sfb_row_tiles - tn * C::kHalves);
-        for (int ks = 0; ks < k_stages; ++ks, ++kc) {
-          const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
-          if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
-            *abort_flag = 1;
-            atomicOr(p.status, kErrProducer);
-            ok = false;
-            break;
-          }
-          const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
-          const uint32_t sf_bytes = (uint32_t)chunks * 512u;
-          const uint32_t st = smem_base + s * C::kStageBytes;
+        const uint32_t s = kc % C::kStages;
+        const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - ks * C::kChunksPerStage);
+        const uint32_t sf_bytes = (uint32_t)chunks * 512u;
+        const uint32_t st = smem_base + s * C::kStageBytes;
+        const int64_t chunk0 = (int64_t)ks * C::kChunksPerStage;
+        if (what & kSideB) {
           mbar_arrive_expect_tx(bar(kFull + s), C::kABytes + C::kBBytes + sf_bytes * (1 + halves));
-          tma_load_2d(st, &tmap_a, bar(kFull + s), ks * kStageKBytes, tm * kBM);
           tma_load_2d(st + C::kABytes, &tmap_b, bar(kFull + s), ks * kStageKBytes, tn * BN);
-          const int64_t chunk0 = (int64_t)ks * C::kChunksPerStage;
-          bulk_load(st + C::kABytes + C::kBBytes,
-                    p.sfa + ((int64_t)tm * p.sf_k_chunks + chunk0) * 512, sf_bytes, bar(kFull + s));
           for (int h = 0; h < halves; ++h)
             bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + h * C::kChunksPerStage * 512,
                       p.sfb + ((int64_t)(tn * C::kHalves + h) * p.sf_k_chunks + chunk0) * 512,
                       sf_bytes, bar(kFull + s));
         }
+        if (what & kSideA) {
+          tma_load_2d(st, &tmap_a, bar(kFull + s), ks * kStageKBytes, tm * kBM);
+          bulk_load(st + C::kABytes + C::kBBytes,
+                    p.sfa + ((int64_t)tm * p.sf_k_chunks + chunk0) * 512, sf_bytes, bar(kFull + s));
+        }
+      };
+      const int my_tiles = (int)blockIdx.x < num_tiles ? (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+      const uint32_t fills = (uint32_t)my_tiles * (uint32_t)k_stages;
+      uint32_t kc = 0;   // stage fills issued so far
+      if (p.after_producer) {
+        // B does not depend on the kernel before this one: fill the ring's B side while that kernel still runs
+        const uint32_t early = min(fills, (uint32_t)C::kStages);
+        for (uint32_t i = 0; i < early; ++i) fill(i, kSideB);
+        griddep_wait();
+        for (uint32_t i = 0; i < early; ++i) fill(i, kSideA);
+        kc = early;
+      }
+      for (; kc < fills; ++kc) {
+        const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
+        if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(p.status, kErrProducer);
+          break;
+        }
+        fill(kc, kSideB | kSideA);
       }
       if (*abort_flag) {
         // give the copies already issued a bounded chance to land before the CTA exits
@@ -297,7 +317,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   } else {
     // ------------------------------------------------------------ epilogue ---
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
-    const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+    if (p.after_producer) griddep_wait();   // alpha comes from the kernel before this one
+    const float alpha = p.alpha ? *reinterpret_cast<const volatile float*>(p.alpha) : 1.0f;
     OutT* d = static_cast<OutT*>(p.d);
     const OutT* bias = static_cast<const OutT*>(p.bias);
     int it = 0;
@@ -385,8 +406,17 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count);
-  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
-  NVFP_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.after_producer ? 1 : 0;
+  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p));
   return NVFP_OK;
 }
 
@@ -456,6 +486,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
       default: return launch_pair<MX, float>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
     }
   }
+  p.after_producer = after_producer ? 1 : 0;     // the tile kernel below knows to fetch only B before it waits
   // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a
   // single accumulator buffer; use them when there are enough tiles to fill the GPU.
   const int64_t tiles256 = ceil_div(m, kBM) * ceil_div(n, 256);
@@ -550,11 +581,10 @@ extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k,
   float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
   float* alpha = gs + 1;
   if (m == 0 || n == 0) return NVFP_OK;
-  // The GEMM may start under the quantizer only if the quantizer is the single cooperative launch and the GEMM
-  // is the kernel that knows to fetch nothing but weights before griddepcontrol.wait.
-  DeviceInfo info;
-  if (int rc = current_device_info(&info)) return rc;
-  const bool overlap = dynamic_fp4_quant_is_one_pass(m, k, x_dtype) && skinny_preferred(m, n, info.sm_count);
+  // The GEMM may start under the quantizer when the quantizer is the single cooperative launch; the few-rows and
+  // the 128-row-tile kernels then fetch nothing but weights before their griddepcontrol.wait (the CTA-pair kernel
+  // is launched the ordinary way).
+  const bool overlap = dynamic_fp4_quant_is_one_pass(m, k, x_dtype);
   bool one_pass = false;
   if (int rc = dynamic_fp4_quant_launch(a_fp4, a_sf, gs, alpha, scratch, x, m, k, x_row_stride, x_dtype, w_global_scale,
                                         overlap, &one_pass, stream))
