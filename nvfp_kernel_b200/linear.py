@@ -116,24 +116,35 @@ class QuantLinear(nn.Module):
             self._graphs = {}
         return self
 
-    def _graphed_forward(self, x: torch.Tensor) -> torch.Tensor:
-        key = (tuple(x.shape), x.dtype)
+    def graph_input(self, shape, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """The buffer the graph for this input shape reads.  A caller that writes its activation there and passes
+        this very tensor to forward() saves the copy forward() would otherwise make."""
+        return self._graph_entry(tuple(shape), dtype, None)[1]
+
+    def _graph_entry(self, shape, dtype, x):
+        key = (shape, dtype)
         entry = self._graphs.get(key)
         if entry is None:
-            static_in = torch.empty_like(x, memory_format=torch.contiguous_format)
-            static_in.copy_(x)
-            stream = torch.cuda.Stream(device=x.device)
-            stream.wait_stream(torch.cuda.current_stream(x.device))
+            device = self.weight_fp4.device
+            static_in = torch.zeros(shape, dtype=dtype, device=device)
+            if x is not None:
+                static_in.copy_(x)
+            stream = torch.cuda.Stream(device=device)
+            stream.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(stream):
                 for _ in range(2):                     # warm-up outside capture (lazy initialisation, allocator)
                     self._forward_impl(static_in)
-            torch.cuda.current_stream(x.device).wait_stream(stream)
+            torch.cuda.current_stream(device).wait_stream(stream)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 static_out = self._forward_impl(static_in)
             entry = self._graphs[key] = (graph, static_in, static_out)
-        graph, static_in, static_out = entry
-        static_in.copy_(x)
+        return entry
+
+    def _graphed_forward(self, x: torch.Tensor) -> torch.Tensor:
+        graph, static_in, static_out = self._graph_entry(tuple(x.shape), x.dtype, x)
+        if x.data_ptr() != static_in.data_ptr():
+            static_in.copy_(x)
         graph.replay()
         return static_out
 

@@ -72,6 +72,14 @@ def test_cuda_graph_replay_matches_eager_and_handles_several_shapes():
     b = (a[:4] * 2).contiguous()                        # a second shape gets its own graph
     assert torch.equal(graphed(b), eager(b))
     assert torch.equal(graphed(a), eager(a))
+    # writing into the graph's own input buffer and passing it saves the copy
+    buf = graphed.graph_input((16, 1024), torch.bfloat16)
+    buf.copy_(a * 0.5)
+    assert torch.equal(graphed(buf), eager(a * 0.5))
+    fresh = QuantLinear(1024, 512, device="cuda").load_weight(w).enable_cuda_graph()
+    buf2 = fresh.graph_input((16, 1024))                # captured before any forward, on an all-zero activation
+    buf2.copy_(a)
+    assert torch.equal(fresh(buf2), eager(a))
     import nvfp_kernel_b200 as nv
     assert nv.device_status() == 0
 
