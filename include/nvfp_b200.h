@@ -112,6 +112,19 @@ int nvfp_scaled_fp4_mm_bias(void* d, const void* a, const void* b, const void* s
                             int out_dtype, int mxfp4, void* stream);
 
 /*
+ * The product written as NVFP4: alpha * acc (+ bias) is rounded to value_dtype (fp16 or bf16) and quantized in the
+ * GEMM epilogue with the global scale out_global_scale[0], bit for bit what nvfp_scaled_fp4_mm(_bias) followed by
+ * nvfp_scaled_fp4_quant(out, out_global_scale) would produce, without the [m, n] tensor ever reaching memory.  For a
+ * next layer whose activation scale is known beforehand (calibrated); no counterpart in the reference.
+ *   d_fp4  device, [m, n/2] bytes, 16-byte aligned
+ *   d_sf   device, nvfp_sf_rows_padded(m) x nvfp_sf_cols_padded(n, 16) bytes in the swizzled layout; padding zero
+ *   bias   n values of value_dtype or NULL;  mxfp4 selects the INPUT operand format as in nvfp_scaled_fp4_mm_bias
+ */
+int nvfp_scaled_fp4_mm_fp4out(void* d_fp4, void* d_sf, const void* a, const void* b, const void* sfa, const void* sfb,
+                              const float* alpha, const void* bias, const float* out_global_scale, int64_t m,
+                              int64_t n, int64_t k, int value_dtype, int mxfp4, void* stream);
+
+/*
  * One call for the forward of an NVFP4 linear layer with online activation quantization, the reference's
  * FP4GemmWithOnlineActivation.forward (speed_test.py:43-50): d = (1 / (gs_x * gs_w)) * quant(x) @ w^T (+ bias) with
  * gs_x = rcp(max|x|) * 2688.  Same bytes as nvfp_dynamic_fp4_quant followed by nvfp_scaled_fp4_mm_bias.  For few

@@ -11,6 +11,7 @@ from .ops import (
     linear_forward,
     mxfp4_scaled_mm,
     reciprocal_approximate_ftz_tensor,
+    scaled_fp4_mm_fp4out,
     scaled_fp4_quant,
     scaled_mxfp4_quant,
 )
@@ -30,6 +31,7 @@ __all__ = [
     "device_status",
     "dynamic_scaled_fp4_quant",
     "linear_forward",
+    "scaled_fp4_mm_fp4out",
     "QuantLinear",
     "HostPipeline",
 ]

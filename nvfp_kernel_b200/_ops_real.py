@@ -125,6 +125,27 @@ def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype, 
     return out
 
 
+def scaled_fp4_mm_fp4out(a, b, block_scale_a, block_scale_b, alpha, out_global_scale, value_dtype=torch.bfloat16,
+                         bias=None) -> tuple[torch.Tensor, torch.Tensor]:
+    """scaled_fp4_quant(cutlass_scaled_fp4_mm(a, b, ..., value_dtype, bias), out_global_scale) in one kernel: the
+    GEMM epilogue quantizes its tile, the [m, n] tensor never reaches memory.  Returns (uint8 [m, n/2],
+    float8_e4m3fn [round_up(m,128), round_up(n/16,4)]), ready to be the `a` operand of the next layer."""
+    assert alpha is not None, "alpha must be a CUDA tensor"
+    assert value_dtype in (torch.float16, torch.bfloat16), f"value_dtype needs to be fp16 or bf16 but got {value_dtype}"
+    _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, value_dtype, torch.float8_e4m3fn)
+    assert out_global_scale.is_cuda and out_global_scale.dtype == torch.float, "out_global_scale must be a CUDA fp32 tensor"
+    m, n = a.shape[0], b.shape[0]
+    assert n % 32 == 0, f"n has to be multiple of 32, but got {n}."
+    out = torch.empty((m, n // 2), dtype=torch.uint8, device=a.device)
+    out_sf = torch.empty((_round_up(m, 128), _round_up(n // 16, 4) // 4), dtype=torch.int32, device=a.device)
+    if bias is not None:
+        bias = _check_bias(bias, n, value_dtype)
+    ext = _load_scaled_fp4_ops(("scaled_fp4_mm_fp4out",))
+    ext.scaled_fp4_mm_fp4out(out, out_sf, a, b, block_scale_a, block_scale_b, alpha, bias, out_global_scale,
+                             1 if value_dtype == torch.bfloat16 else 0, False)
+    return out, out_sf.view(torch.float8_e4m3fn)
+
+
 def mxfp4_scaled_mm(a, b, block_scale_a, block_scale_b, out_dtype, alpha=None, bias=None) -> torch.Tensor:
     _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, torch.float8_e8m0fnu)
     m, n = a.shape[0], b.shape[0]

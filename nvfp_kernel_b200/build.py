@@ -62,7 +62,7 @@ def build_lib(force: bool = False, verbose: bool = False) -> str:
     srcs = [os.path.join(CSRC, s) for s in CU_SOURCES]
     deps = srcs + [os.path.join(CSRC, "common.h"), os.path.join(CSRC, "ptx_sm100.cuh"),
                    os.path.join(CSRC, "gemm_fp4_pair_sm100.cuh"),
-                   os.path.join(CSRC, "gemm_fp4_skinny_sm100.cuh"),
+                   os.path.join(CSRC, "gemm_fp4_skinny_sm100.cuh"), os.path.join(CSRC, "quant_math.cuh"),
                    os.path.join(ROOT, "include", "nvfp_b200.h")]
     digest = _digest(deps, NVCC_FLAGS)
     if not force and _up_to_date(LIB_PATH, digest):

@@ -59,7 +59,9 @@ struct OutMaps {
 //   kOutScatterAdd  row-parallel (K-split) layers: destination r owns rows [r*rows_per_owner, ...) of the
 //                   result; each 32-row block of this rank's fp32 partial product is ADDED (TMA reduce)
 //                   into its owner's buffer -- the reduce-scatter fused into the epilogue
-constexpr int kOutStoreAll = 0, kOutScatterAdd = 1;
+//   kOutFp4         the product, rounded to OutT, is quantized to NVFP4 in the epilogue (global scale p.out_gs):
+//                   packed bytes to p.d, swizzled scales to p.out_sf; no output maps
+constexpr int kOutStoreAll = 0, kOutScatterAdd = 1, kOutFp4 = 2;
 
 template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -247,6 +249,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int q = warp & 3;
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
     const OutT* bias = static_cast<const OutT*>(p.bias);
+    const float out_gs = (OUT_MODE == kOutFp4 && p.out_gs) ? __ldg(p.out_gs) : 1.0f;
+    const float rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
     const uint32_t acc_empty_leader = map_to_cta(bar(kAccEmpty), 0);
     const uint32_t staging = smem_base + C::kStages * C::kStageBytes + (uint32_t)(warp - 2) * 2 * C::kStoreBufBytes;
     uint32_t store_count = 0;
@@ -277,6 +281,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        }
+        if constexpr (OUT_MODE == kOutFp4) {
+          quantize_row_chunk<OutT, 4>(p, r, alpha, bias, row0 + lane, tn * kPairBN + c * kCols, out_gs, rcp_out_gs, rcp6);
+          continue;
         }
         // the buffer used two steps ago must have been read out by its TMA store
         const uint32_t buf = staging + (store_count & 1u) * C::kStoreBufBytes;
@@ -369,8 +377,9 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   OutMaps out_maps;
   memset(&out_maps, 0, sizeof(out_maps));
   const int rows_per_owner = OUT_MODE == kOutScatterAdd ? p.m / n_out : p.m;
-  for (int o = 0; o < n_out; ++o)
-    if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], rows_per_owner, p.n, ld)) return rc;
+  if constexpr (OUT_MODE != kOutFp4)
+    for (int o = 0; o < n_out; ++o)
+      if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], rows_per_owner, p.n, ld)) return rc;
   auto kernel = fp4_gemm_pair_kernel<MX, OutT, OUT_MODE>;
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;

@@ -25,6 +25,7 @@
 #include <type_traits>
 
 #include "common.h"
+#include "quant_math.cuh"
 #include "ptx_sm100.cuh"
 
 namespace nvfp {
@@ -71,6 +72,10 @@ struct GemmParams {
   const uint8_t* sfb;
   const float* alpha;
   const void* bias;     // n values of the output type added after alpha, or null
+  // NVFP4 output: when out_gs is set, the product (rounded to the output type) is quantized in the epilogue with
+  // this global scale; d receives [m, n/2] packed bytes and out_sf the swizzled scales of an [m, n] tensor
+  const float* out_gs;
+  uint8_t* out_sf;
   void* d;
   int m, n, k;
   int tiles_m, tiles_n;
@@ -130,6 +135,50 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t 
   constexpr int kPer = 16 / (int)sizeof(OutT);
 #pragma unroll
   for (int v = 0; v < 32 / kPer; ++v) dst[v] = scale_bias_pack<OutT>(&r[kPer * v], alpha, bias ? bias + kPer * v : nullptr);
+}
+
+// NBLK consecutive 16-column blocks of one output row, starting at column col0 (a multiple of 16 * NBLK, NBLK = 2 or
+// 4): alpha * acc (+ bias) rounded to OutT, then quantized to NVFP4 exactly as the quantizer kernel would quantize
+// that OutT tensor.  Writes 8 bytes of nibbles per block and NBLK scale bytes, which are consecutive in the
+// swizzled [rowTile][kTile][32][4][4] layout.  Rows in [m, round_up(m, 128)) get zero scales, like the quantizer's.
+template <typename OutT, int NBLK>
+__device__ __forceinline__ void quantize_row_chunk(const GemmParams& p, const uint32_t* r, float alpha, const OutT* bias,
+                                                   int row, int col0, float gs, float rcp_gs, float rcp6) {
+  static_assert(sizeof(OutT) == 2, "the quantizer reads fp16 or bf16");
+  using V2 = typename Vec2<OutT>::type;
+  uint32_t sf_word = 0;
+  uint2 q[NBLK];
+#pragma unroll
+  for (int b = 0; b < NBLK; ++b) {
+    V2 h2[8];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int colj = col0 + 16 * b + 8 * half;
+      const uint4 o = scale_bias_pack<OutT>(&r[16 * b + 8 * half], alpha, (bias && colj < p.n) ? bias + colj : nullptr);
+      const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h2[4 * half + i] = *reinterpret_cast<const V2*>(&w[i]);
+    }
+    uint8_t sf;
+    q[b] = nvfp4_quantize_block<OutT>(h2, gs, rcp_gs, rcp6, sf);
+    sf_word |= (uint32_t)sf << (8 * b);
+  }
+  uint8_t* out = static_cast<uint8_t*>(p.d);
+  if (row < p.m) {
+#pragma unroll
+    for (int b = 0; b < NBLK; b += 2)
+      if (col0 + 16 * b < p.n)
+        *reinterpret_cast<uint4*>(out + (int64_t)row * (p.n / 2) + (col0 + 16 * b) / 2) = make_uint4(q[b].x, q[b].y, q[b + 1].x, q[b + 1].y);
+  } else {
+    sf_word = 0;
+  }
+  const int k_tiles = (p.n + 63) / 64, k_tile = col0 / 64;
+  if (row < (p.m + 127) / 128 * 128 && k_tile < k_tiles) {
+    uint8_t* dst = p.out_sf + ((int64_t)(row / 128) * k_tiles + k_tile) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 +
+                   (col0 % 64) / 16;
+    if constexpr (NBLK == 4) *reinterpret_cast<uint32_t*>(dst) = sf_word;
+    else *reinterpret_cast<uint16_t*>(dst) = (uint16_t)sf_word;
+  }
 }
 
 template <int BN, bool MX, typename OutT>
@@ -321,6 +370,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const float alpha = p.alpha ? *reinterpret_cast<const volatile float*>(p.alpha) : 1.0f;
     OutT* d = static_cast<OutT*>(p.d);
     const OutT* bias = static_cast<const OutT*>(p.bias);
+    const float out_gs = p.out_gs ? __ldg(p.out_gs) : 1.0f, rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
@@ -341,6 +391,12 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tmem_ld_32x32b_x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col = tn * BN + c * 32;
+        if constexpr (sizeof(OutT) == 2) {
+          if (p.out_gs) {
+            quantize_row_chunk<OutT, 2>(p, r, alpha, bias, row, col, out_gs, rcp_out_gs, rcp6);
+            continue;
+          }
+        }
         if (row < p.m && col < p.n)
           store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha, bias ? bias + col : nullptr);
       }
@@ -428,8 +484,16 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
 template <bool MX>
 int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream,
-              const void* bias = nullptr, bool after_producer = false) {
+              const void* bias = nullptr, bool after_producer = false, const float* out_gs = nullptr,
+              void* out_sf = nullptr) {
   NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
+  if (out_gs != nullptr) {
+    NVFP_REQUIRE(out_sf != nullptr && (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0,
+                 "scale output is null or not 16-byte aligned");
+    NVFP_REQUIRE(out_dtype == NVFP_DTYPE_F16 || out_dtype == NVFP_DTYPE_BF16,
+                 "the value quantized to NVFP4 must be fp16 or bf16 (dtype code %d)", out_dtype);
+    NVFP_REQUIRE(n_out == 1 && ld == n, "NVFP4 output goes to one dense destination");
+  }
   NVFP_REQUIRE(outputs != nullptr && n_out >= 1 && n_out <= kMaxOutputs,
                "between 1 and %d output matrices are supported, got %d", kMaxOutputs, n_out);
   for (int o = 0; o < n_out; ++o)
@@ -463,6 +527,8 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.sfb = static_cast<const uint8_t*>(sfb);
   p.alpha = alpha;
   p.bias = bias;
+  p.out_gs = out_gs;
+  p.out_sf = static_cast<uint8_t*>(out_sf);
   p.d = d;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.sf_k_chunks = (int)ceil_div(k / kBlock, 4);
@@ -470,7 +536,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.status = device_status_word();
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
   // Few activation rows (decode): weights are streamed once; swap the operands and split K over a cluster.
-  if (n_out == 1 && ld == n && skinny_preferred(m, n, info.sm_count)) {
+  if (n_out == 1 && ld == n && out_gs == nullptr && skinny_preferred(m, n, info.sm_count)) {
     switch (out_dtype) {
       case NVFP_DTYPE_BF16: return launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream, after_producer);
       case NVFP_DTYPE_F16: return launch_skinny<MX, __half>(p, a, b, info.sm_count, stream, after_producer);
@@ -480,6 +546,10 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
   const int64_t pair_tiles = ceil_div(m, kPairBM) * ceil_div(n, kPairBN);
   if (n_out > 1 || ld != n || (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2)) {
+    if (out_gs != nullptr)
+      return out_dtype == NVFP_DTYPE_BF16
+                 ? launch_pair<MX, __nv_bfloat16, kOutFp4>(p, a, b, outputs, n_out, ld, info.sm_count, stream)
+                 : launch_pair<MX, __half, kOutFp4>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
     switch (out_dtype) {
       case NVFP_DTYPE_BF16: return launch_pair<MX, __nv_bfloat16>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
       case NVFP_DTYPE_F16: return launch_pair<MX, __half>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
@@ -555,6 +625,18 @@ extern "C" int nvfp_scaled_fp4_mm_bias(void* d, const void* a, const void* b, co
   clear_error();
   return mxfp4 ? scaled_mm<true>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream), bias)
                : scaled_mm<false>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream), bias);
+}
+
+extern "C" int nvfp_scaled_fp4_mm_fp4out(void* d_fp4, void* d_sf, const void* a, const void* b, const void* sfa,
+                                         const void* sfb, const float* alpha, const void* bias,
+                                         const float* out_global_scale, int64_t m, int64_t n, int64_t k,
+                                         int value_dtype, int mxfp4, void* stream) {
+  clear_error();
+  NVFP_REQUIRE(out_global_scale != nullptr, "output global scale is null");
+  return mxfp4 ? scaled_mm<true>(&d_fp4, 1, n, a, b, sfa, sfb, alpha, m, n, k, value_dtype, static_cast<cudaStream_t>(stream),
+                                 bias, false, out_global_scale, d_sf)
+               : scaled_mm<false>(&d_fp4, 1, n, a, b, sfa, sfb, alpha, m, n, k, value_dtype, static_cast<cudaStream_t>(stream),
+                                  bias, false, out_global_scale, d_sf);
 }
 
 extern "C" int64_t nvfp_linear_workspace_bytes(int64_t m, int64_t k) {

@@ -22,65 +22,15 @@
 #include <type_traits>
 
 #include "common.h"
+#include "quant_math.cuh"
 
 namespace nvfp {
 namespace {
-
-__device__ __forceinline__ float rcp_approx_ftz(float a) {
-  float b;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(a));
-  return b;
-}
 
 __device__ __forceinline__ uint64_t global_timer_ns_q() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
-}
-
-__device__ __forceinline__ float mul_ftz(float a, float b) {
-  float c;
-  asm("mul.ftz.f32 %0, %1, %2;" : "=f"(c) : "f"(a), "f"(b));
-  return c;
-}
-
-// Eight fp32 -> eight e2m1 nibbles in one word; value i lands in bits [4i, 4i+4).
-// cvt.rn.satfinite.e2m1x2.f32 d, a, b puts a in the high and b in the low nibble.
-__device__ __forceinline__ uint32_t cvt_e2m1x8(float f0, float f1, float f2, float f3, float f4,
-                                               float f5, float f6, float f7) {
-  uint32_t r;
-  asm("{\n"
-      ".reg .b8 q0, q1, q2, q3;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 q0, %2, %1;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 q1, %4, %3;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 q2, %6, %5;\n"
-      "cvt.rn.satfinite.e2m1x2.f32 q3, %8, %7;\n"
-      "mov.b32 %0, {q0, q1, q2, q3};\n"
-      "}"
-      : "=r"(r)
-      : "f"(f0), "f"(f1), "f"(f2), "f"(f3), "f"(f4), "f"(f5), "f"(f6), "f"(f7));
-  return r;
-}
-
-template <typename T> struct Vec2;
-template <> struct Vec2<__half> { using type = __half2; };
-template <> struct Vec2<__nv_bfloat16> { using type = __nv_bfloat162; };
-
-template <typename T> __device__ __forceinline__ float2 to_float2(typename Vec2<T>::type v);
-template <> __device__ __forceinline__ float2 to_float2<__half>(__half2 v) { return __half22float2(v); }
-template <> __device__ __forceinline__ float2 to_float2<__nv_bfloat16>(__nv_bfloat162 v) {
-  return __bfloat1622float2(v);
-}
-template <typename T> __device__ __forceinline__ float to_float(T v);
-template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
-template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
-  return __bfloat162float(v);
-}
-
-template <typename T> __device__ __forceinline__ typename Vec2<T>::type zero2();
-template <> __device__ __forceinline__ __half2 zero2<__half>() { return __float2half2_rn(0.0f); }
-template <> __device__ __forceinline__ __nv_bfloat162 zero2<__nv_bfloat16>() {
-  return __float2bfloat162_rn(0.0f);
 }
 
 template <typename T>
@@ -267,22 +217,18 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
   for (int p = 0; p < kPasses; ++p) {
     const int row_in_tile = p * kRowsPerPass + row_in_pass;
     const int row = mt * kTileRows + row_in_tile;
-    auto mx2 = __habs2(v[p].h2[0]);
-#pragma unroll
-    for (int i = 1; i < 8; ++i) mx2 = __hmax2(mx2, __habs2(v[p].h2[i]));
-#pragma unroll
-    for (int s = 1; s < kThreadsPerBlock; s <<= 1)
-      mx2 = __hmax2(__shfl_xor_sync(0xffffffffu, mx2, s), mx2);
-    const float amax = to_float<T>(__hmax(mx2.x, mx2.y));
-
     uint8_t sf_byte;
-    float out_scale;
-    if (BLOCK == 16) {
-      const float sf_value = mul_ftz(gs, mul_ftz(amax, rcp6));
-      sf_byte = (uint8_t)__nv_cvt_float_to_fp8(sf_value, __NV_SATFINITE, __NV_E4M3);
-      const float sf_q = __half2float(__half(__nv_cvt_fp8_to_halfraw(sf_byte, __NV_E4M3)));
-      out_scale = sf_q != 0.0f ? rcp_approx_ftz(mul_ftz(sf_q, rcp_gs)) : 0.0f;
+    uint2 packed;
+    if constexpr (BLOCK == 16) {
+      packed = nvfp4_quantize_block<T>(v[p].h2, gs, rcp_gs, rcp6, sf_byte);
     } else {
+      auto mx2 = __habs2(v[p].h2[0]);
+#pragma unroll
+      for (int i = 1; i < 8; ++i) mx2 = __hmax2(mx2, __habs2(v[p].h2[i]));
+#pragma unroll
+      for (int s = 1; s < kThreadsPerBlock; s <<= 1)
+        mx2 = __hmax2(__shfl_xor_sync(0xffffffffu, mx2, s), mx2);
+      const float amax = to_float<T>(__hmax(mx2.x, mx2.y));
       const float sf_value = mul_ftz(amax, rcp6);
       const uint32_t bits = __float_as_uint(sf_value);
       uint32_t e = (bits >> 23) & 0xffu;
@@ -290,19 +236,17 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
       e = min(e, 254u);
       if (sf_value != sf_value) e = 255u;
       sf_byte = (uint8_t)e;
-      out_scale = (e > 0 && e < 254) ? __uint_as_float((254u - e) << 23) : 0.0f;
-    }
-
-    float2 f[8];
+      const float out_scale = (e > 0 && e < 254) ? __uint_as_float((254u - e) << 23) : 0.0f;
+      float2 f[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      f[i] = to_float2<T>(v[p].h2[i]);
-      f[i].x = mul_ftz(f[i].x, out_scale);
-      f[i].y = mul_ftz(f[i].y, out_scale);
+      for (int i = 0; i < 8; ++i) {
+        f[i] = to_float2<T>(v[p].h2[i]);
+        f[i].x = mul_ftz(f[i].x, out_scale);
+        f[i].y = mul_ftz(f[i].y, out_scale);
+      }
+      packed.x = cvt_e2m1x8(f[0].x, f[0].y, f[1].x, f[1].y, f[2].x, f[2].y, f[3].x, f[3].y);
+      packed.y = cvt_e2m1x8(f[4].x, f[4].y, f[5].x, f[5].y, f[6].x, f[6].y, f[7].x, f[7].y);
     }
-    uint2 packed;
-    packed.x = cvt_e2m1x8(f[0].x, f[0].y, f[1].x, f[1].y, f[2].x, f[2].y, f[3].x, f[3].y);
-    packed.y = cvt_e2m1x8(f[4].x, f[4].y, f[5].x, f[5].y, f[6].x, f[6].y, f[7].x, f[7].y);
     if (col_ok && row < m)
       *reinterpret_cast<uint2*>(out + (int64_t)row * (n / 2) + col / 2) = packed;
     if (seg % kThreadsPerBlock == 0)

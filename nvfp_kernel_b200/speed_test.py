@@ -3,6 +3,7 @@
     python -m nvfp_kernel_b200.speed_test                 # BF16 torch.mm vs FP4 (online activation quantize + GEMM)
     python -m nvfp_kernel_b200.speed_test --table decode  # Llama-3-8B decode shapes, M in {1, 16, 128}
     python -m nvfp_kernel_b200.speed_test --table quant   # quantizer alone, GB/s
+    python -m nvfp_kernel_b200.speed_test --table fp4out  # GEMM + quantizer of its output, separate and fused
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m nvfp_kernel_b200.speed_test --table tp
                                                           # Llama-3-70B prefill layers, tensor-parallel
 
@@ -99,6 +100,31 @@ def quant(repeats: int):
         print(f"{m:<7} {k:<7} {t_q:<15.1f} {m * k * 2.5625 / t_q / 1e3:<20.0f} {t_a:<10.1f}")
 
 
+def fp4out(repeats: int):
+    """A layer whose output feeds another NVFP4 layer: GEMM -> bf16 tensor -> global scale -> quantizer, against the
+    GEMM that quantizes in its epilogue (output scale known beforehand)."""
+    print(f"{'M':<6} {'K':<6} {'N':<6} {'GEMM (us)':<11} {'+ amax + quantize (us)':<24} {'GEMM with NVFP4 output (us)':<28}")
+    print("-" * 84)
+    for m, k, n in ((8192, 8192, 8192), (4096, 4096, 4096), (8192, 8192, 28672), (2048, 4096, 14336)):
+        a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
+        w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+        ga, gw = ops.global_scale(a), ops.global_scale(w)
+        a_fp4, a_sf = ops.scaled_fp4_quant(a, ga)
+        w_fp4, w_sf = ops.scaled_fp4_quant(w, gw)
+        del a, w
+        alpha = ops.alpha_from_scales(ga, gw)
+        out_gs = ops.global_scale(ops.cutlass_scaled_fp4_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16))
+
+        def separate():
+            y = ops.cutlass_scaled_fp4_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+            return ops.scaled_fp4_quant(y, ops.global_scale(y))
+
+        t_mm = time_us(lambda: ops.cutlass_scaled_fp4_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16), repeats)
+        t_sep = time_us(separate, repeats)
+        t_fused = time_us(lambda: ops.scaled_fp4_mm_fp4out(a_fp4, w_fp4, a_sf, w_sf, alpha, out_gs), repeats)
+        print(f"{m:<6} {k:<6} {n:<6} {t_mm:<11.1f} {t_sep:<24.1f} {t_fused:<28.1f}")
+
+
 def tensor_parallel(repeats: int):
     """Llama-3-70B prefill layers (M = 8192) sharded over the ranks of this launch (torchrun):
     gate_up [N = 57344, K = 8192] column-parallel, down [N = 8192, K = 28672] row-parallel, each with the
@@ -163,11 +189,11 @@ def main():
     ap = argparse.ArgumentParser(description="BF16 GEMM vs FP4 GEMM with online activation quantization")
     ap.add_argument("--batch_size", type=int, default=4096, help="M dimension of the sweep")
     ap.add_argument("--repeats", type=int, default=50)
-    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp"])
+    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp", "fp4out"])
     args = ap.parse_args()
     torch.cuda.empty_cache()
     {"sweep": lambda: sweep(args.batch_size, args.repeats), "decode": lambda: decode(args.repeats),
-     "quant": lambda: quant(args.repeats), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
+     "quant": lambda: quant(args.repeats), "fp4out": lambda: fp4out(min(args.repeats, 20)), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
 
 
 if __name__ == "__main__":

@@ -91,6 +91,20 @@ def capi_dynamic_quant(x: torch.Tensor, scratch: torch.Tensor, gs_weight: torch.
     return out, sf, scal[:1], scal[1:]
 
 
+def capi_mm_fp4out(a, b, sfa, sfb, alpha, out_gs, value_dtype=torch.bfloat16, mx: bool = False, bias=None, fill: int = 0xAA):
+    """GEMM whose result leaves as NVFP4 (nvfp_scaled_fp4_mm_fp4out): (packed [m, n/2], swizzled scales)."""
+    lib = _capi.load()
+    m, n, k = a.shape[0], b.shape[0], a.shape[1] * 2
+    out = torch.full((m, n // 2), fill, dtype=torch.uint8, device=a.device)
+    sf = torch.full(sf_shape(m, n, 16), fill, dtype=torch.uint8, device=a.device)
+    _capi.check(lib.nvfp_scaled_fp4_mm_fp4out(out.data_ptr(), sf.data_ptr(), a.data_ptr(), b.data_ptr(), sfa.data_ptr(),
+                                              sfb.data_ptr(), alpha.data_ptr() if alpha is not None else None,
+                                              bias.data_ptr() if bias is not None else None, out_gs.data_ptr(), m, n, k,
+                                              _dt(value_dtype), 1 if mx else 0, _stream()))
+    assert _capi.device_status() == 0, "a kernel gave up on a bounded wait"
+    return out, sf
+
+
 def capi_linear_forward(x, w_fp4, w_sf, w_gs, scratch, out_dtype=torch.bfloat16, bias=None):
     """Whole layer forward through nvfp_linear_forward."""
     lib = _capi.load()

@@ -147,6 +147,29 @@ def test_bias_added_in_the_epilogue(m, n, k, mx):
         assert not bad.any(), (dt, int(bad.sum()), float((out.float() - want).abs().max()))
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 256, 512), (128, 96, 512), (300, 4128, 1024), (1000, 512, 2048), (512, 4096, 1024),
+                                   (2048, 4096, 512), (1100, 4000, 256)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_result_written_as_nvfp4_equals_gemm_then_quantizer(m, n, k, dt):
+    """nvfp_scaled_fp4_mm_fp4out (the epilogue quantizes alpha*acc+bias, rounded to fp16/bf16, with a given global
+    scale) against the two separate calls: same packed bytes, same scale tensor including its zero padding.  Shapes
+    reach the 128-row-tile kernel and the CTA-pair kernel, with ragged rows, ragged 64-column scale tiles, a scale
+    that fits and one that saturates."""
+    from helpers import capi_mm_fp4out
+    a, w = gemm_inputs(m, n, k, seed=m + n, w_std=0.05)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    g = torch.Generator().manual_seed(k)
+    bias = (torch.randn(n, generator=g) * 0.5).to(dt).cuda()
+    for b in (None, bias):
+        plain = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, dt, bias=b)
+        fits = ((448.0 * 6.0) / plain.float().abs().max()).reshape(1)
+        for out_gs in (fits, fits * 37.0):
+            want_fp4, want_sf = capi_quant(plain.contiguous(), out_gs)
+            got_fp4, got_sf = capi_mm_fp4out(a_fp4, w_fp4, a_sf, w_sf, alpha, out_gs, dt, bias=b)
+            assert torch.equal(got_fp4, want_fp4), (m, n, k, b is not None)
+            assert torch.equal(got_sf, want_sf), (m, n, k, b is not None)
+
+
 def test_config1_vs_reference_pseudo_quant_path():
     """BASELINE config 1 (1024^3, seed 0): real path vs the port of the reference's torch
     pseudo-quant path on CPU (oracle/pseudo_path.py, itself pinned to the reference's output)."""

@@ -156,3 +156,32 @@ def test_one_call_forward_equals_the_separate_calls(m, n, k):
         a_fp4, a_sf, _, alpha = capi_dynamic_quant(x, scratch, w_gs)
         want = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16, bias=b)
         assert torch.equal(got, want), (i, m, n, k)
+
+
+def test_two_layers_chained_through_nvfp4_output():
+    """Layer 1 writes its result as NVFP4 straight from the GEMM epilogue (calibrated output scale), layer 2
+    consumes it: bit-identical to layer 1 -> bf16 tensor -> quantizer -> layer 2, with one kernel and one
+    [m, n] round trip through memory fewer."""
+    import nvfp_kernel_b200 as nv
+    torch.manual_seed(11)
+    m, k, n1, n2 = 512, 1024, 4096, 512
+    x = torch.randn(m, k).to(torch.bfloat16).cuda()
+    w1 = (torch.randn(n1, k) * 0.05).to(torch.bfloat16).cuda()
+    w2 = (torch.randn(n2, n1) * 0.02).to(torch.bfloat16).cuda()
+    gx, g1, g2 = nv.global_scale(x), nv.global_scale(w1), nv.global_scale(w2)
+    x_fp4, x_sf = nv.scaled_fp4_quant(x, gx)
+    w1_fp4, w1_sf = nv.scaled_fp4_quant(w1, g1)
+    w2_fp4, w2_sf = nv.scaled_fp4_quant(w2, g2)
+    alpha1 = nv.alpha_from_scales(gx, g1)
+    # unfused chain; its hidden tensor also provides the "calibrated" scale of the hidden activation
+    h = nv.cutlass_scaled_fp4_mm(x_fp4, w1_fp4, x_sf, w1_sf, alpha1, torch.bfloat16)
+    gh = nv.global_scale(h)
+    h_fp4, h_sf = nv.scaled_fp4_quant(h, gh)
+    alpha2 = nv.alpha_from_scales(gh, g2)
+    want = nv.cutlass_scaled_fp4_mm(h_fp4, w2_fp4, h_sf, w2_sf, alpha2, torch.bfloat16)
+    # fused: no hidden bf16 tensor
+    f_fp4, f_sf = nv.scaled_fp4_mm_fp4out(x_fp4, w1_fp4, x_sf, w1_sf, alpha1, gh, torch.bfloat16)
+    assert torch.equal(f_fp4, h_fp4) and torch.equal(f_sf.view(torch.uint8), h_sf.view(torch.uint8))
+    got = nv.cutlass_scaled_fp4_mm(f_fp4, w2_fp4, f_sf, w2_sf, alpha2, torch.bfloat16)
+    assert torch.equal(got, want)
+    assert nv.device_status() == 0
