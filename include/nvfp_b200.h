@@ -125,6 +125,22 @@ int nvfp_scaled_fp4_mm_fp4out(void* d_fp4, void* d_sf, const void* a, const void
                               int64_t n, int64_t k, int value_dtype, int mxfp4, void* stream);
 
 /*
+ * Gate/up projection of a gated MLP with the activation in the epilogue.  b holds the two projections' rows
+ * interleaved in groups of 16: rows [32g, 32g+16) are gate rows 16g.., rows [32g+16, 32g+32) the matching up rows
+ * (quantized as ONE tensor, after interleaving).  Per row and group the epilogue forms v = alpha * acc (+ bias)
+ * rounded to value_dtype, then out[16g + i] = value_dtype(value_dtype(silu(v_gate[i])) * v_up[i]), silu in fp32:
+ * what a framework computes with silu(gate) * up on fp16 / bf16 tensors.  The [m, n] product never reaches memory.
+ *   out_global_scale NULL: d receives [m, n/2] values of value_dtype; d_sf is ignored
+ *   out_global_scale set:  the [m, n/2] result is quantized to NVFP4 as by nvfp_scaled_fp4_quant(result,
+ *                          out_global_scale): d receives [m, n/4] packed bytes, d_sf the swizzled scales of an
+ *                          [m, n/2] tensor -- the down projection's activation operand
+ *   bias  n values of value_dtype in the interleaved order, or NULL.  No counterpart in the reference.
+ */
+int nvfp_scaled_fp4_mm_silu_mul(void* d, void* d_sf, const void* a, const void* b, const void* sfa, const void* sfb,
+                                const float* alpha, const void* bias, const float* out_global_scale, int64_t m,
+                                int64_t n, int64_t k, int value_dtype, int mxfp4, void* stream);
+
+/*
  * One call for the forward of an NVFP4 linear layer with online activation quantization, the reference's
  * FP4GemmWithOnlineActivation.forward (speed_test.py:43-50): d = (1 / (gs_x * gs_w)) * quant(x) @ w^T (+ bias) with
  * gs_x = rcp(max|x|) * 2688.  Same bytes as nvfp_dynamic_fp4_quant followed by nvfp_scaled_fp4_mm_bias.  For few

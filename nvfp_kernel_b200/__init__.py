@@ -11,7 +11,9 @@ from .ops import (
     linear_forward,
     mxfp4_scaled_mm,
     reciprocal_approximate_ftz_tensor,
+    interleave_gate_up,
     scaled_fp4_mm_fp4out,
+    scaled_fp4_mm_silu_mul,
     scaled_fp4_quant,
     scaled_mxfp4_quant,
 )
@@ -32,6 +34,8 @@ __all__ = [
     "dynamic_scaled_fp4_quant",
     "linear_forward",
     "scaled_fp4_mm_fp4out",
+    "scaled_fp4_mm_silu_mul",
+    "interleave_gate_up",
     "QuantLinear",
     "HostPipeline",
 ]

@@ -40,6 +40,7 @@ PROTOTYPES = {
     "nvfp_activation_scales": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "nvfp_scaled_fp4_mm_bias": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "nvfp_scaled_fp4_mm_fp4out": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "nvfp_scaled_fp4_mm_silu_mul": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "nvfp_linear_workspace_bytes": (_i64, [_i64, _i64]),
     "nvfp_linear_forward": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _vp]),
     "nvfp_dynamic_fp4_quant": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),

@@ -146,6 +146,40 @@ def scaled_fp4_mm_fp4out(a, b, block_scale_a, block_scale_b, alpha, out_global_s
     return out, out_sf.view(torch.float8_e4m3fn)
 
 
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up weights -> [2I, K] with rows interleaved in groups of 16 (16 gate rows, their 16 up rows, ...),
+    the order scaled_fp4_mm_silu_mul expects.  Quantize the result as one tensor."""
+    assert w_gate.shape == w_up.shape and w_gate.ndim == 2 and w_gate.shape[0] % 16 == 0, \
+        f"gate and up must be [I, K] with I a multiple of 16, got {tuple(w_gate.shape)} and {tuple(w_up.shape)}"
+    i, k = w_gate.shape
+    return torch.stack((w_gate.reshape(i // 16, 16, k), w_up.reshape(i // 16, 16, k)), dim=1).reshape(2 * i, k).contiguous()
+
+
+def scaled_fp4_mm_silu_mul(a, b, block_scale_a, block_scale_b, alpha, value_dtype=torch.bfloat16,
+                           out_global_scale=None, bias=None):
+    """Gate/up projection of a gated MLP with silu(gate) * up in the GEMM epilogue; `b` is the quantized
+    interleave_gate_up(w_gate, w_up).  Returns the [m, n/2] activation in value_dtype, or, with out_global_scale,
+    its NVFP4 quantization (uint8 [m, n/4], float8_e4m3fn scales) ready to be the down projection's `a` operand."""
+    assert alpha is not None, "alpha must be a CUDA tensor"
+    assert value_dtype in (torch.float16, torch.bfloat16), f"value_dtype needs to be fp16 or bf16 but got {value_dtype}"
+    _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, value_dtype, torch.float8_e4m3fn)
+    m, n = a.shape[0], b.shape[0]
+    assert n % 32 == 0, f"n has to be multiple of 32, but got {n}."
+    if bias is not None:
+        bias = _check_bias(bias, n, value_dtype)
+    code = 1 if value_dtype == torch.bfloat16 else 0
+    ext = _load_scaled_fp4_ops(("scaled_fp4_mm_silu_mul",))
+    if out_global_scale is None:
+        out = torch.empty((m, n // 2), dtype=value_dtype, device=a.device)
+        ext.scaled_fp4_mm_silu_mul(out, None, a, b, block_scale_a, block_scale_b, alpha, bias, None, code, False)
+        return out
+    assert out_global_scale.is_cuda and out_global_scale.dtype == torch.float, "out_global_scale must be a CUDA fp32 tensor"
+    out = torch.empty((m, n // 4), dtype=torch.uint8, device=a.device)
+    out_sf = torch.empty((_round_up(m, 128), _round_up(n // 32, 4) // 4), dtype=torch.int32, device=a.device)
+    ext.scaled_fp4_mm_silu_mul(out, out_sf, a, b, block_scale_a, block_scale_b, alpha, bias, out_global_scale, code, False)
+    return out, out_sf.view(torch.float8_e4m3fn)
+
+
 def mxfp4_scaled_mm(a, b, block_scale_a, block_scale_b, out_dtype, alpha=None, bias=None) -> torch.Tensor:
     _mm_asserts(a, b, block_scale_a, block_scale_b, alpha, out_dtype, torch.float8_e8m0fnu)
     m, n = a.shape[0], b.shape[0]

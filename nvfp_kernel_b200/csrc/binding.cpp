@@ -184,6 +184,56 @@ void scaled_fp4_mm_fp4out(torch::Tensor& D_fp4, torch::Tensor& D_sf, torch::Tens
                                          m, n, k, (int)value_dtype_code, mx ? 1 : 0, current_stream(A)));
 }
 
+// Gate/up projection with silu(gate) * up in the epilogue (B's rows interleaved in groups of 16).  D: [m, n/2] of the
+// value dtype when out_gs is absent; uint8 [m, n/4] plus D_sf (swizzled scales of an [m, n/2] tensor) when it is given.
+void scaled_fp4_mm_silu_mul(torch::Tensor& D, c10::optional<torch::Tensor> D_sf, torch::Tensor const& A,
+                            torch::Tensor const& B, torch::Tensor const& A_sf, torch::Tensor const& B_sf,
+                            c10::optional<torch::Tensor> const& alpha, c10::optional<torch::Tensor> const& bias,
+                            c10::optional<torch::Tensor> const& out_gs, int64_t value_dtype_code, bool mx) {
+  CHECK_OPERAND(A, at::ScalarType::Byte, "a");
+  CHECK_OPERAND(B, at::ScalarType::Byte, "b");
+  TORCH_CHECK(A_sf.is_cuda() && A_sf.is_contiguous() && B_sf.is_cuda() && B_sf.is_contiguous(),
+              "scales must be contiguous CUDA tensors");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.sizes()[1] == B.sizes()[1], "a and b shapes cannot be multiplied");
+  TORCH_CHECK(mx || alpha.has_value(), "alpha is required");
+  const int64_t m = A.sizes()[0], n = B.sizes()[0], k = A.sizes()[1] * 2;
+  TORCH_CHECK(n % 32 == 0, "Expected n to be divisible by 32, but got b shape: (", B.sizes()[0], "x", B.sizes()[1], ").");
+  TORCH_CHECK(A_sf.element_size() * A_sf.numel() == nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, mx ? 32 : 16) &&
+                  B_sf.element_size() * B_sf.numel() == nvfp_sf_rows_padded(n) * nvfp_sf_cols_padded(k, mx ? 32 : 16),
+              "operand scales must be padded and swizzled");
+  TORCH_CHECK(D.is_cuda() && D.is_contiguous(), "output must be a contiguous CUDA tensor");
+  const bool quantized = out_gs.has_value() && out_gs->defined();
+  void* sf_ptr = nullptr;
+  if (quantized) {
+    TORCH_CHECK(out_gs->is_cuda() && out_gs->scalar_type() == at::ScalarType::Float, "output global scale must be CUDA fp32");
+    TORCH_CHECK(D.scalar_type() == at::ScalarType::Byte && D.numel() == m * (n / 4), "output must be uint8 [m, n/4]");
+    TORCH_CHECK(D_sf.has_value() && D_sf->is_cuda() && D_sf->is_contiguous() &&
+                    D_sf->element_size() * D_sf->numel() >= nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(n / 2, 16),
+                "output scales missing or too small for the padded layout");
+    sf_ptr = D_sf->data_ptr();
+  } else {
+    TORCH_CHECK(D.numel() == m * (n / 2) &&
+                    ((value_dtype_code == NVFP_DTYPE_BF16 && D.scalar_type() == at::ScalarType::BFloat16) ||
+                     (value_dtype_code == NVFP_DTYPE_F16 && D.scalar_type() == at::ScalarType::Half)),
+                "output must be [m, n/2] of the value dtype");
+  }
+  const void* bias_ptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->dim() == 1 && bias->sizes()[0] == n,
+                "bias must be a contiguous CUDA vector of ", n, " elements");
+    TORCH_CHECK((value_dtype_code == NVFP_DTYPE_BF16 && bias->scalar_type() == at::ScalarType::BFloat16) ||
+                    (value_dtype_code == NVFP_DTYPE_F16 && bias->scalar_type() == at::ScalarType::Half),
+                "bias must have the value dtype");
+    bias_ptr = bias->data_ptr();
+  }
+  const at::cuda::OptionalCUDAGuard guard(device_of(A));
+  const float* alpha_ptr = alpha.has_value() ? static_cast<const float*>(alpha->data_ptr()) : nullptr;
+  check_status(nvfp_scaled_fp4_mm_silu_mul(D.data_ptr(), sf_ptr, A.data_ptr(), B.data_ptr(), A_sf.data_ptr(), B_sf.data_ptr(),
+                                           alpha_ptr, bias_ptr,
+                                           quantized ? static_cast<const float*>(out_gs->data_ptr()) : nullptr, m, n, k,
+                                           (int)value_dtype_code, mx ? 1 : 0, current_stream(A)));
+}
+
 // GEMM whose [m, n] result goes to several destinations given as raw device addresses (the local
 // output first, then peer GPUs' buffers): the column-parallel gather fused into the epilogue.
 void scaled_fp4_mm_multi(std::vector<int64_t> const& dst_ptrs, int64_t dst_ld, int64_t out_dtype_code, torch::Tensor const& A,
@@ -364,6 +414,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mxfp4_scaled_mm", &mxfp4_scaled_mm);
   m.def("scaled_fp4_mm_bias", &scaled_fp4_mm_bias);
   m.def("scaled_fp4_mm_fp4out", &scaled_fp4_mm_fp4out);
+  m.def("scaled_fp4_mm_silu_mul", &scaled_fp4_mm_silu_mul);
   m.def("scaled_fp4_mm_multi", &scaled_fp4_mm_multi);
   m.def("scaled_fp4_mm_scatter_add", &scaled_fp4_mm_scatter_add);
   m.def("global_scale", &global_scale);

@@ -59,9 +59,9 @@ struct OutMaps {
 //   kOutScatterAdd  row-parallel (K-split) layers: destination r owns rows [r*rows_per_owner, ...) of the
 //                   result; each 32-row block of this rank's fp32 partial product is ADDED (TMA reduce)
 //                   into its owner's buffer -- the reduce-scatter fused into the epilogue
-//   kOutFp4         the product, rounded to OutT, is quantized to NVFP4 in the epilogue (global scale p.out_gs):
-//                   packed bytes to p.d, swizzled scales to p.out_sf; no output maps
-constexpr int kOutStoreAll = 0, kOutScatterAdd = 1, kOutFp4 = 2;
+//   kOutFused       the epilogue applies the gated activation (p.act) and / or quantizes to NVFP4 (p.out_gs) and
+//                   stores from registers (finish_row_chunk); no output maps
+constexpr int kOutStoreAll = 0, kOutScatterAdd = 1, kOutFused = 2;
 
 template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -249,7 +249,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int q = warp & 3;
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
     const OutT* bias = static_cast<const OutT*>(p.bias);
-    const float out_gs = (OUT_MODE == kOutFp4 && p.out_gs) ? __ldg(p.out_gs) : 1.0f;
+    const float out_gs = (OUT_MODE == kOutFused && p.out_gs) ? __ldg(p.out_gs) : 1.0f;
     const float rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
     const uint32_t acc_empty_leader = map_to_cta(bar(kAccEmpty), 0);
     const uint32_t staging = smem_base + C::kStages * C::kStageBytes + (uint32_t)(warp - 2) * 2 * C::kStoreBufBytes;
@@ -282,8 +282,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         }
-        if constexpr (OUT_MODE == kOutFp4) {
-          quantize_row_chunk<OutT, 4>(p, r, alpha, bias, row0 + lane, tn * kPairBN + c * kCols, out_gs, rcp_out_gs, rcp6);
+        if constexpr (OUT_MODE == kOutFused) {
+          if (p.act) finish_row_chunk<OutT, 64, true>(p, r, alpha, bias, row0 + lane, tn * kPairBN + c * kCols, out_gs, rcp_out_gs, rcp6);
+          else finish_row_chunk<OutT, 64, false>(p, r, alpha, bias, row0 + lane, tn * kPairBN + c * kCols, out_gs, rcp_out_gs, rcp6);
           continue;
         }
         // the buffer used two steps ago must have been read out by its TMA store
@@ -377,7 +378,7 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   OutMaps out_maps;
   memset(&out_maps, 0, sizeof(out_maps));
   const int rows_per_owner = OUT_MODE == kOutScatterAdd ? p.m / n_out : p.m;
-  if constexpr (OUT_MODE != kOutFp4)
+  if constexpr (OUT_MODE != kOutFused)
     for (int o = 0; o < n_out; ++o)
       if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], rows_per_owner, p.n, ld)) return rc;
   auto kernel = fp4_gemm_pair_kernel<MX, OutT, OUT_MODE>;

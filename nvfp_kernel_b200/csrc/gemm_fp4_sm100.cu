@@ -76,6 +76,7 @@ struct GemmParams {
   // this global scale; d receives [m, n/2] packed bytes and out_sf the swizzled scales of an [m, n] tensor
   const float* out_gs;
   uint8_t* out_sf;
+  int act;              // 1: silu(gate) * up on groups of 16 + 16 interleaved columns (output [m, n / 2]), 0: none
   void* d;
   int m, n, k;
   int tiles_m, tiles_n;
@@ -137,49 +138,95 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t 
   for (int v = 0; v < 32 / kPer; ++v) dst[v] = scale_bias_pack<OutT>(&r[kPer * v], alpha, bias ? bias + kPer * v : nullptr);
 }
 
-// NBLK consecutive 16-column blocks of one output row, starting at column col0 (a multiple of 16 * NBLK, NBLK = 2 or
-// 4): alpha * acc (+ bias) rounded to OutT, then quantized to NVFP4 exactly as the quantizer kernel would quantize
-// that OutT tensor.  Writes 8 bytes of nibbles per block and NBLK scale bytes, which are consecutive in the
-// swizzled [rowTile][kTile][32][4][4] layout.  Rows in [m, round_up(m, 128)) get zero scales, like the quantizer's.
-template <typename OutT, int NBLK>
-__device__ __forceinline__ void quantize_row_chunk(const GemmParams& p, const uint32_t* r, float alpha, const OutT* bias,
-                                                   int row, int col0, float gs, float rcp_gs, float rcp6) {
-  static_assert(sizeof(OutT) == 2, "the quantizer reads fp16 or bf16");
+// silu(g) * u the way a framework evaluates it on 16-bit tensors: silu in fp32, rounded to T, times u in fp32,
+// rounded to T.
+template <typename T>
+__device__ __forceinline__ float silu_mul_16bit(float g, float u) {
+  const float s = g / (1.0f + expf(-g));
+  if constexpr (std::is_same<T, __half>::value) return __half2float(__float2half_rn(s)) * u;
+  else return __bfloat162float(__float2bfloat16_rn(s)) * u;
+}
+
+// Everything the epilogue can do to NCOLS (64 or 32) consecutive columns of one row beyond a plain store.
+//   values   alpha * acc (+ bias), rounded to OutT (fp16 / bf16)
+//   ACT      gated activation: the columns come in groups of 32, 16 "gate" columns followed by their 16 "up" columns
+//            (the weight's rows were interleaved that way); each group yields 16 outputs silu(gate) * up, so the
+//            output tensor is [m, n / 2]
+//   p.out_gs set: the outputs are quantized to NVFP4 exactly as the quantizer kernel would quantize that OutT
+//            tensor (8 bytes of nibbles per 16 outputs to p.d, scale bytes, adjacent in the swizzled
+//            [rowTile][kTile][32][4][4] layout, to p.out_sf; rows in [m, round_up(m, 128)) get zero scales)
+//   else     the outputs are stored to p.d as OutT
+template <typename OutT, int NCOLS, bool ACT>
+__device__ __forceinline__ void finish_row_chunk(const GemmParams& p, const uint32_t* r, float alpha, const OutT* bias,
+                                                 int row, int col0, float gs, float rcp_gs, float rcp6) {
+  static_assert(sizeof(OutT) == 2, "16-bit values only");
   using V2 = typename Vec2<OutT>::type;
+  constexpr int NOUT = ACT ? NCOLS / 2 : NCOLS;          // outputs of this chunk
+  uint32_t w[NCOLS / 2];                                 // the values as packed pairs
+#pragma unroll
+  for (int piece = 0; piece < NCOLS / 8; ++piece) {
+    const int colj = col0 + 8 * piece;
+    const uint4 o = scale_bias_pack<OutT>(&r[8 * piece], alpha, (bias && colj < p.n) ? bias + colj : nullptr);
+    w[4 * piece + 0] = o.x; w[4 * piece + 1] = o.y; w[4 * piece + 2] = o.z; w[4 * piece + 3] = o.w;
+  }
+  uint32_t out_pairs[NOUT / 2];
+  if constexpr (ACT) {
+#pragma unroll
+    for (int g = 0; g < NCOLS / 32; ++g)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 gate = to_float2<OutT>(*reinterpret_cast<const V2*>(&w[16 * g + i]));
+        const float2 up = to_float2<OutT>(*reinterpret_cast<const V2*>(&w[16 * g + 8 + i]));
+        out_pairs[8 * g + i] = pack2<OutT>(silu_mul_16bit<OutT>(gate.x, up.x), silu_mul_16bit<OutT>(gate.y, up.y));
+      }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NOUT / 2; ++i) out_pairs[i] = w[i];
+  }
+  const int out_cols = ACT ? p.n / 2 : p.n, ocol0 = ACT ? col0 / 2 : col0;
+  if (p.out_gs == nullptr) {
+    if (row < p.m) {
+      OutT* dst = static_cast<OutT*>(p.d) + (int64_t)row * out_cols + ocol0;
+#pragma unroll
+      for (int v = 0; v < NOUT / 8; ++v)
+        if (ocol0 + 8 * v < out_cols)
+          reinterpret_cast<uint4*>(dst)[v] = make_uint4(out_pairs[4 * v], out_pairs[4 * v + 1], out_pairs[4 * v + 2], out_pairs[4 * v + 3]);
+    }
+    return;
+  }
+  constexpr int NBLK = NOUT / 16;
   uint32_t sf_word = 0;
   uint2 q[NBLK];
 #pragma unroll
   for (int b = 0; b < NBLK; ++b) {
     V2 h2[8];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int colj = col0 + 16 * b + 8 * half;
-      const uint4 o = scale_bias_pack<OutT>(&r[16 * b + 8 * half], alpha, (bias && colj < p.n) ? bias + colj : nullptr);
-      const uint32_t w[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) h2[4 * half + i] = *reinterpret_cast<const V2*>(&w[i]);
-    }
+    for (int i = 0; i < 8; ++i) h2[i] = *reinterpret_cast<const V2*>(&out_pairs[8 * b + i]);
     uint8_t sf;
     q[b] = nvfp4_quantize_block<OutT>(h2, gs, rcp_gs, rcp6, sf);
     sf_word |= (uint32_t)sf << (8 * b);
   }
   uint8_t* out = static_cast<uint8_t*>(p.d);
   if (row < p.m) {
+    uint8_t* dst = out + (int64_t)row * (out_cols / 2) + ocol0 / 2;
 #pragma unroll
-    for (int b = 0; b < NBLK; b += 2)
-      if (col0 + 16 * b < p.n)
-        *reinterpret_cast<uint4*>(out + (int64_t)row * (p.n / 2) + (col0 + 16 * b) / 2) = make_uint4(q[b].x, q[b].y, q[b + 1].x, q[b + 1].y);
+    for (int b = 0; b < NBLK; ++b)
+      if (ocol0 + 16 * b < out_cols) *reinterpret_cast<uint2*>(dst + 8 * b) = q[b];
   } else {
     sf_word = 0;
   }
-  const int k_tiles = (p.n + 63) / 64, k_tile = col0 / 64;
+  const int k_tiles = (out_cols + 63) / 64, k_tile = ocol0 / 64;
   if (row < (p.m + 127) / 128 * 128 && k_tile < k_tiles) {
     uint8_t* dst = p.out_sf + ((int64_t)(row / 128) * k_tiles + k_tile) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 +
-                   (col0 % 64) / 16;
+                   (ocol0 % 64) / 16;
     if constexpr (NBLK == 4) *reinterpret_cast<uint32_t*>(dst) = sf_word;
-    else *reinterpret_cast<uint16_t*>(dst) = (uint16_t)sf_word;
+    else if constexpr (NBLK == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)sf_word;
+    else *dst = (uint8_t)sf_word;
   }
 }
+
+// True when the epilogue has more to do than scale, add the bias and store.
+__device__ __forceinline__ bool has_fused_output(const GemmParams& p) { return p.out_gs != nullptr || p.act != 0; }
 
 template <int BN, bool MX, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -392,8 +439,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tmem_ld_wait();
         const int col = tn * BN + c * 32;
         if constexpr (sizeof(OutT) == 2) {
-          if (p.out_gs) {
-            quantize_row_chunk<OutT, 2>(p, r, alpha, bias, row, col, out_gs, rcp_out_gs, rcp6);
+          if (has_fused_output(p)) {
+            if (p.act) finish_row_chunk<OutT, 32, true>(p, r, alpha, bias, row, col, out_gs, rcp_out_gs, rcp6);
+            else finish_row_chunk<OutT, 32, false>(p, r, alpha, bias, row, col, out_gs, rcp_out_gs, rcp6);
             continue;
           }
         }
@@ -485,14 +533,16 @@ template <bool MX>
 int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream,
               const void* bias = nullptr, bool after_producer = false, const float* out_gs = nullptr,
-              void* out_sf = nullptr) {
+              void* out_sf = nullptr, int act = 0) {
   NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
-  if (out_gs != nullptr) {
-    NVFP_REQUIRE(out_sf != nullptr && (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0,
+  const bool fused = out_gs != nullptr || act != 0;
+  if (fused) {
+    NVFP_REQUIRE(act == 0 || act == 1, "unknown activation code %d", act);
+    NVFP_REQUIRE(out_gs == nullptr || (out_sf != nullptr && (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0),
                  "scale output is null or not 16-byte aligned");
     NVFP_REQUIRE(out_dtype == NVFP_DTYPE_F16 || out_dtype == NVFP_DTYPE_BF16,
-                 "the value quantized to NVFP4 must be fp16 or bf16 (dtype code %d)", out_dtype);
-    NVFP_REQUIRE(n_out == 1 && ld == n, "NVFP4 output goes to one dense destination");
+                 "the epilogue's activation and quantization work on fp16 or bf16 values (dtype code %d)", out_dtype);
+    NVFP_REQUIRE(n_out == 1 && ld == n, "a fused epilogue writes one dense destination");
   }
   NVFP_REQUIRE(outputs != nullptr && n_out >= 1 && n_out <= kMaxOutputs,
                "between 1 and %d output matrices are supported, got %d", kMaxOutputs, n_out);
@@ -529,6 +579,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.bias = bias;
   p.out_gs = out_gs;
   p.out_sf = static_cast<uint8_t*>(out_sf);
+  p.act = act;
   p.d = d;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.sf_k_chunks = (int)ceil_div(k / kBlock, 4);
@@ -536,7 +587,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.status = device_status_word();
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
   // Few activation rows (decode): weights are streamed once; swap the operands and split K over a cluster.
-  if (n_out == 1 && ld == n && out_gs == nullptr && skinny_preferred(m, n, info.sm_count)) {
+  if (n_out == 1 && ld == n && !fused && skinny_preferred(m, n, info.sm_count)) {
     switch (out_dtype) {
       case NVFP_DTYPE_BF16: return launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream, after_producer);
       case NVFP_DTYPE_F16: return launch_skinny<MX, __half>(p, a, b, info.sm_count, stream, after_producer);
@@ -546,10 +597,10 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
   const int64_t pair_tiles = ceil_div(m, kPairBM) * ceil_div(n, kPairBN);
   if (n_out > 1 || ld != n || (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2)) {
-    if (out_gs != nullptr)
+    if (fused)
       return out_dtype == NVFP_DTYPE_BF16
-                 ? launch_pair<MX, __nv_bfloat16, kOutFp4>(p, a, b, outputs, n_out, ld, info.sm_count, stream)
-                 : launch_pair<MX, __half, kOutFp4>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
+                 ? launch_pair<MX, __nv_bfloat16, kOutFused>(p, a, b, outputs, n_out, ld, info.sm_count, stream)
+                 : launch_pair<MX, __half, kOutFused>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
     switch (out_dtype) {
       case NVFP_DTYPE_BF16: return launch_pair<MX, __nv_bfloat16>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
       case NVFP_DTYPE_F16: return launch_pair<MX, __half>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
@@ -637,6 +688,17 @@ extern "C" int nvfp_scaled_fp4_mm_fp4out(void* d_fp4, void* d_sf, const void* a,
                                  bias, false, out_global_scale, d_sf)
                : scaled_mm<false>(&d_fp4, 1, n, a, b, sfa, sfb, alpha, m, n, k, value_dtype, static_cast<cudaStream_t>(stream),
                                   bias, false, out_global_scale, d_sf);
+}
+
+extern "C" int nvfp_scaled_fp4_mm_silu_mul(void* d, void* d_sf, const void* a, const void* b, const void* sfa,
+                                           const void* sfb, const float* alpha, const void* bias,
+                                           const float* out_global_scale, int64_t m, int64_t n, int64_t k,
+                                           int value_dtype, int mxfp4, void* stream) {
+  clear_error();
+  return mxfp4 ? scaled_mm<true>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, value_dtype, static_cast<cudaStream_t>(stream),
+                                 bias, false, out_global_scale, d_sf, 1)
+               : scaled_mm<false>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, value_dtype, static_cast<cudaStream_t>(stream),
+                                  bias, false, out_global_scale, d_sf, 1);
 }
 
 extern "C" int64_t nvfp_linear_workspace_bytes(int64_t m, int64_t k) {

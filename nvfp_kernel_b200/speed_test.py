@@ -4,6 +4,7 @@
     python -m nvfp_kernel_b200.speed_test --table decode  # Llama-3-8B decode shapes, M in {1, 16, 128}
     python -m nvfp_kernel_b200.speed_test --table quant   # quantizer alone, GB/s
     python -m nvfp_kernel_b200.speed_test --table fp4out  # GEMM + quantizer of its output, separate and fused
+    python -m nvfp_kernel_b200.speed_test --table mlp     # gated MLP: separate kernels vs activation + quantizer in the epilogue
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m nvfp_kernel_b200.speed_test --table tp
                                                           # Llama-3-70B prefill layers, tensor-parallel
 
@@ -125,6 +126,47 @@ def fp4out(repeats: int):
         print(f"{m:<6} {k:<6} {n:<6} {t_mm:<11.1f} {t_sep:<24.1f} {t_fused:<28.1f}")
 
 
+def mlp(repeats: int):
+    """Gated MLP (Llama shapes) from a bf16 activation to a bf16 result: every step a separate kernel, against the
+    gate/up GEMM that applies silu(gate) * up and quantizes for the down projection in its epilogue."""
+    import torch.nn.functional as F
+    print(f"{'model':<12} {'M':<6} {'hidden':<7} {'inter':<7} {'separate (us)':<15} {'fused epilogue (us)':<21} {'TFLOP/s fused':<14}")
+    print("-" * 86)
+    for name, m, hidden, inter in (("llama-3-8b", 8192, 4096, 14336), ("llama-3-70b", 8192, 8192, 28672),
+                                   ("llama-3-8b", 512, 4096, 14336)):
+        x = torch.randn(m, hidden, dtype=torch.bfloat16, device="cuda")
+        w_gu = (torch.randn(2 * inter, hidden, device="cuda") * 0.02).to(torch.bfloat16)   # already interleaved
+        w_d = (torch.randn(hidden, inter, device="cuda") * 0.02).to(torch.bfloat16)
+        ggu, gd = ops.global_scale(w_gu), ops.global_scale(w_d)
+        gu_fp4, gu_sf = ops.scaled_fp4_quant(w_gu, ggu)
+        d_fp4, d_sf = ops.scaled_fp4_quant(w_d, gd)
+        del w_gu, w_d
+        scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+
+        def separate():
+            x_fp4, x_sf, _, alpha1 = ops.dynamic_scaled_fp4_quant(x, scratch, ggu)
+            y = ops.cutlass_scaled_fp4_mm(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, torch.bfloat16).view(m, inter // 16, 2, 16)
+            h = F.silu(y[:, :, 0]) * y[:, :, 1]
+            h_fp4, h_sf, _, alpha2 = ops.dynamic_scaled_fp4_quant(h.view(m, inter), scratch, gd)
+            return ops.cutlass_scaled_fp4_mm(h_fp4, d_fp4, h_sf, d_sf, alpha2, torch.bfloat16)
+
+        separate()
+        gh = ops.global_scale((F.silu(torch.randn(m, 64, device="cuda")) * torch.randn(m, 64, device="cuda")).to(torch.bfloat16))
+        alpha2 = ops.alpha_from_scales(gh, gd)                 # calibrated scale of the hidden activation
+
+        def fused():
+            x_fp4, x_sf, _, alpha1 = ops.dynamic_scaled_fp4_quant(x, scratch, ggu)
+            h_fp4, h_sf = ops.scaled_fp4_mm_silu_mul(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, torch.bfloat16, out_global_scale=gh)
+            return ops.cutlass_scaled_fp4_mm(h_fp4, d_fp4, h_sf, d_sf, alpha2, torch.bfloat16)
+
+        t_sep = time_us(separate, repeats)
+        t_fused = time_us(fused, repeats)
+        flops = 2.0 * m * hidden * inter * 3
+        print(f"{name:<12} {m:<6} {hidden:<7} {inter:<7} {t_sep:<15.1f} {t_fused:<21.1f} {flops / t_fused / 1e6:<14.0f}")
+        del gu_fp4, gu_sf, d_fp4, d_sf, x
+        torch.cuda.empty_cache()
+
+
 def tensor_parallel(repeats: int):
     """Llama-3-70B prefill layers (M = 8192) sharded over the ranks of this launch (torchrun):
     gate_up [N = 57344, K = 8192] column-parallel, down [N = 8192, K = 28672] row-parallel, each with the
@@ -189,11 +231,11 @@ def main():
     ap = argparse.ArgumentParser(description="BF16 GEMM vs FP4 GEMM with online activation quantization")
     ap.add_argument("--batch_size", type=int, default=4096, help="M dimension of the sweep")
     ap.add_argument("--repeats", type=int, default=50)
-    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp", "fp4out"])
+    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp", "fp4out", "mlp"])
     args = ap.parse_args()
     torch.cuda.empty_cache()
     {"sweep": lambda: sweep(args.batch_size, args.repeats), "decode": lambda: decode(args.repeats),
-     "quant": lambda: quant(args.repeats), "fp4out": lambda: fp4out(min(args.repeats, 20)), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
+     "quant": lambda: quant(args.repeats), "fp4out": lambda: fp4out(min(args.repeats, 20)), "mlp": lambda: mlp(min(args.repeats, 10)), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
 
 
 if __name__ == "__main__":

@@ -185,3 +185,43 @@ def test_two_layers_chained_through_nvfp4_output():
     got = nv.cutlass_scaled_fp4_mm(f_fp4, w2_fp4, f_sf, w2_sf, alpha2, torch.bfloat16)
     assert torch.equal(got, want)
     assert nv.device_status() == 0
+
+
+@pytest.mark.parametrize("m,k,inter,hidden", [(300, 1024, 1440, 512), (2048, 1024, 2048, 1024), (40, 512, 256, 256)])
+def test_gated_mlp_with_activation_and_quantizer_in_the_epilogue(m, k, inter, hidden):
+    """x -> gate/up GEMM with silu(gate)*up (and the NVFP4 quantization of the result) in its epilogue -> down GEMM,
+    against the same chain with the bf16 gate/up product, torch's silu * mul and the quantizer kernel in between."""
+    import torch.nn.functional as F
+    import nvfp_kernel_b200 as nv
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, k).to(torch.bfloat16).cuda()
+    w_gate = (torch.randn(inter, k) * 0.05).to(torch.bfloat16).cuda()
+    w_up = (torch.randn(inter, k) * 0.05).to(torch.bfloat16).cuda()
+    w_down = (torch.randn(hidden, inter) * 0.03).to(torch.bfloat16).cuda()
+    w_gu = nv.interleave_gate_up(w_gate, w_up)
+    assert torch.equal(w_gu.view(inter // 16, 2, 16, k)[:, 0].reshape(inter, k), w_gate)
+    gx, ggu, gd = nv.global_scale(x), nv.global_scale(w_gu), nv.global_scale(w_down)
+    x_fp4, x_sf = nv.scaled_fp4_quant(x, gx)
+    gu_fp4, gu_sf = nv.scaled_fp4_quant(w_gu, ggu)
+    d_fp4, d_sf = nv.scaled_fp4_quant(w_down, gd)
+    alpha1 = nv.alpha_from_scales(gx, ggu)
+    # separate kernels
+    y = nv.cutlass_scaled_fp4_mm(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, torch.bfloat16).view(m, inter // 16, 2, 16)
+    h = F.silu(y[:, :, 0].reshape(m, inter)) * y[:, :, 1].reshape(m, inter)
+    # activation in the epilogue, bf16 out: torch's result up to the last bit of its exp
+    h_f = nv.scaled_fp4_mm_silu_mul(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, torch.bfloat16)
+    assert h_f.shape == (m, inter)
+    diff = (h_f.float() - h.float()).abs()
+    assert (diff <= 2.0 ** -7 * h.float().abs() + 1e-30).all()
+    assert (h_f == h).float().mean() > 0.999
+    # activation and quantizer in the epilogue: exactly the quantizer's bytes for that activation
+    gh = nv.global_scale(h_f)
+    want_fp4, want_sf = nv.scaled_fp4_quant(h_f, gh)
+    got_fp4, got_sf = nv.scaled_fp4_mm_silu_mul(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, torch.bfloat16, out_global_scale=gh)
+    assert torch.equal(got_fp4, want_fp4) and torch.equal(got_sf.view(torch.uint8), want_sf.view(torch.uint8))
+    alpha2 = nv.alpha_from_scales(gh, gd)
+    out = nv.cutlass_scaled_fp4_mm(got_fp4, d_fp4, got_sf, d_sf, alpha2, torch.bfloat16)
+    assert torch.equal(out, nv.cutlass_scaled_fp4_mm(want_fp4, d_fp4, want_sf, d_sf, alpha2, torch.bfloat16))
+    dense = F.linear(F.silu(F.linear(x, w_gate)) * F.linear(x, w_up), w_down)
+    assert (out.float() - dense.float()).abs().max() < 0.35 * dense.float().abs().max()
+    assert nv.device_status() == 0
