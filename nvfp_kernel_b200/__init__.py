@@ -19,6 +19,7 @@ from .ops import (
 )
 from .linear import QuantLinear
 from .host_pipeline import HostPipeline
+from .mlp import QuantGatedMLP
 
 __all__ = [
     "scaled_fp4_quant",
@@ -38,4 +39,5 @@ __all__ = [
     "interleave_gate_up",
     "QuantLinear",
     "HostPipeline",
+    "QuantGatedMLP",
 ]

@@ -219,6 +219,30 @@ def tensor_parallel(repeats: int):
             continue
         t = timed(make("row" if world > 1 else None, 8192, 28672, **kw), x)
         rows.append(("down row-parallel", name if world > 1 else "single GPU", t, flops / t / 1e9))
+    # the whole gated MLP, intermediate dimension split: quantize, gate/up GEMM (silu * up and NVFP4 quantization in the
+    # epilogue), down GEMM with its partial sums reduce-scattered; every rank builds only its own shards
+    from . import QuantGatedMLP
+    x = torch.randn((m, 8192), generator=g, device="cuda").to(torch.bfloat16)
+    flops = 2.0 * m * 8192 * 28672 * 3
+    for name, kw in (("NCCL reduce-scatter", {}), ("fused reduce-scatter", {"fused_reduce_scatter": True})):
+        if world == 1 and kw:
+            continue
+        mlp_layer = QuantGatedMLP(8192, 28672, parallel="tensor" if world > 1 else None, device="cuda", **kw)
+        il = mlp_layer.inter_local
+        for w_name, sf_name, gs_name, shape in (("gate_up_fp4", "gate_up_sf", "gate_up_global_scale", (2 * il, 8192)),
+                                                ("down_fp4", "down_sf", "down_global_scale", (8192, il))):
+            shard = (torch.randn(shape, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+            gs = ops.global_scale(shard)
+            w_fp4, w_sf = ops.scaled_fp4_quant(shard, gs)
+            setattr(mlp_layer, w_name, w_fp4)
+            setattr(mlp_layer, sf_name, w_sf.view(torch.uint8))
+            getattr(mlp_layer, gs_name).copy_(gs)
+            del shard
+        mlp_layer.set_activation_scale(torch.tensor([2688.0 / 4.0], device="cuda"))
+        t = timed(mlp_layer, x)
+        rows.append(("gated MLP tensor-parallel", name if world > 1 else "single GPU", t, flops / t / 1e9))
+        del mlp_layer
+        torch.cuda.empty_cache()
     if rank == 0:
         print(f"Llama-3-70B prefill layers, M = {m}, {world} GPU(s); time = max over ranks, includes activation quantize")
         print(f"{'layer':<26} {'collective':<22} {'ms':<9} {'TFLOP/s (all ranks)':<20}")

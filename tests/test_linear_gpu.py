@@ -225,3 +225,32 @@ def test_gated_mlp_with_activation_and_quantizer_in_the_epilogue(m, k, inter, hi
     dense = F.linear(F.silu(F.linear(x, w_gate)) * F.linear(x, w_up), w_down)
     assert (out.float() - dense.float()).abs().max() < 0.35 * dense.float().abs().max()
     assert nv.device_status() == 0
+
+
+def test_quant_gated_mlp_module():
+    """QuantGatedMLP (three launches, calibrated hidden scale) against its own separate-kernel path (dynamic hidden
+    scale): with the scale calibrated on the very input both quantize the hidden activation with the same scale, so
+    the outputs are identical; on other inputs they stay close; state round trip; result near the dense MLP."""
+    from nvfp_kernel_b200 import QuantGatedMLP
+    from nvfp_kernel_b200.mlp import dense_gated_mlp
+    torch.manual_seed(2)
+    hidden, inter, m = 512, 1408, 192
+    x = torch.randn(m, hidden).to(torch.bfloat16).cuda()
+    wg = (torch.randn(inter, hidden) * 0.05).to(torch.bfloat16).cuda()
+    wu = (torch.randn(inter, hidden) * 0.05).to(torch.bfloat16).cuda()
+    wd = (torch.randn(hidden, inter) * 0.03).to(torch.bfloat16).cuda()
+    mlp = QuantGatedMLP(hidden, inter, device="cuda").load_weights(wg, wu, wd).calibrate(x)
+    y = mlp(x)
+    assert y.shape == (m, hidden) and y.dtype == torch.bfloat16
+    assert torch.equal(y, mlp.reference_forward(x))
+    x2 = (x * 0.7).to(torch.bfloat16)
+    y2, ref2 = mlp(x2.reshape(2, m // 2, hidden)), mlp.reference_forward(x2)
+    assert y2.shape == (2, m // 2, hidden)
+    assert (y2.reshape(m, hidden).float() - ref2.float()).abs().max() <= 0.08 * ref2.float().abs().max()
+    dense = dense_gated_mlp(x, wg, wu, wd)
+    assert (y.float() - dense.float()).abs().max() < 0.35 * dense.float().abs().max()
+    clone = QuantGatedMLP(hidden, inter, device="cuda")
+    clone.load_state_dict(mlp.state_dict())
+    assert torch.equal(clone(x), y)
+    import nvfp_kernel_b200 as nv
+    assert nv.device_status() == 0

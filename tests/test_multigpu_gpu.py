@@ -1,6 +1,7 @@
 """Tensor-parallel QuantLinear on 2 GPUs of one box (skipped with fewer): column-parallel with the
 NCCL all-gather and with the gather fused into the GEMM epilogue (peer stores) must both equal the
-1-GPU result bit for bit; row-parallel (K-split, reduce-scatter) stays within the GEMM tolerance."""
+1-GPU result bit for bit; row-parallel (K-split, reduce-scatter) stays within the GEMM tolerance; the
+tensor-parallel gated MLP (fused activation and quantization, NCCL or fused reduce-scatter) matches the 1-GPU one."""
 import os
 import socket
 
@@ -47,9 +48,28 @@ def _worker(rank, world, port, ret):
             y_rf = row_fused(a * scale)
             ref = QuantLinear(k, n, device="cuda").load_weight(w)(a * scale)
             check_gemm(y_rf, ref[lo:hi].double(), rel=2e-2)
+        # tensor-parallel gated MLP: intermediate dimension split, hidden activation quantized in the gate/up epilogue
+        # with one calibrated scale on every rank, partial sums of the down projection reduce-scattered over the rows
+        from nvfp_kernel_b200 import QuantGatedMLP
+        hidden, inter = 512, 1024
+        g = torch.Generator().manual_seed(3)
+        wg = (torch.randn(inter, hidden, generator=g) * 0.05).to(torch.bfloat16).cuda()
+        wu = (torch.randn(inter, hidden, generator=g) * 0.05).to(torch.bfloat16).cuda()
+        wd = (torch.randn(hidden, inter, generator=g) * 0.03).to(torch.bfloat16).cuda()
+        xm = torch.randn(m, hidden, generator=g).to(torch.bfloat16).cuda()
+        one = QuantGatedMLP(hidden, inter, device="cuda").load_weights(wg, wu, wd).calibrate(xm)
+        y_one = one(xm)
+        mlp_ok = []
+        for fused_rs in (False, True):
+            tp = QuantGatedMLP(hidden, inter, parallel="tensor", fused_reduce_scatter=fused_rs, device="cuda")
+            tp.load_weights(wg, wu, wd).calibrate(xm)
+            mlp_ok.append(bool(torch.equal(tp.act_global_scale, one.act_global_scale)))
+            for scale in (1.0, 0.5):
+                y_tp = tp(xm * scale)
+                check_gemm(y_tp, one(xm * scale)[lo:hi].double(), rel=2e-2)
         torch.cuda.synchronize()
         ret[rank] = (bool(torch.equal(y_nccl, single)), bool(torch.equal(y_fused, single)),
-                     bool(torch.equal(y_fused2, single2)), tuple(y_row.shape))
+                     bool(torch.equal(y_fused2, single2)), tuple(y_row.shape), tuple(mlp_ok), tuple(y_one.shape))
     finally:
         dist.destroy_process_group()
 
@@ -60,4 +80,4 @@ def test_column_and_row_parallel_two_gpus():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     for rank in range(world):
-        assert ret[rank] == (True, True, True, (256, 1024)), (rank, ret[rank])
+        assert ret[rank] == (True, True, True, (256, 1024), (True, True), (512, 512)), (rank, ret[rank])
