@@ -120,3 +120,26 @@ def test_two_rank_gloo_column_and_row_parallel():
     assert len(ret) == world
     for rank in range(world):
         assert ret[rank] == (True, True, True), (rank, ret[rank])
+
+
+def test_gate_up_interleave_layout_and_mlp_shard_granules():
+    """Rows of the fused gate/up weight come in groups of 16 gate rows followed by their 16 up rows, so that output
+    columns [32g, 32g+16) and [32g+16, 32g+32) of the GEMM are gate and up of the same 16 hidden units; a rank's
+    shard of the interleaved tensor is the interleave of its shards."""
+    from nvfp_kernel_b200._ops_real import interleave_gate_up
+    inter, k = 256, 64
+    gate = torch.arange(inter * k, dtype=torch.float32).reshape(inter, k)
+    up = -gate
+    gu = interleave_gate_up(gate, up)
+    assert gu.shape == (2 * inter, k)
+    for g in range(inter // 16):
+        assert torch.equal(gu[32 * g:32 * g + 16], gate[16 * g:16 * g + 16])
+        assert torch.equal(gu[32 * g + 16:32 * g + 32], up[16 * g:16 * g + 16])
+    world = 2
+    for rank in range(world):
+        lo, hi = shard_range(inter, rank, world, 64, "intermediate_size")
+        assert torch.equal(gu[2 * lo:2 * hi], interleave_gate_up(gate[lo:hi], up[lo:hi]))
+    with pytest.raises(AssertionError):
+        interleave_gate_up(gate[:24], up[:24])
+    with pytest.raises(ValueError):
+        shard_range(192, 0, 2, 64, "intermediate_size")      # 96 per rank is not a multiple of 64
