@@ -4,6 +4,7 @@
     python -m nvfp_kernel_b200.speed_test --table decode  # Llama-3-8B decode shapes, M in {1, 16, 128}
     python -m nvfp_kernel_b200.speed_test --table quant   # quantizer alone, GB/s
     python -m nvfp_kernel_b200.speed_test --table fp4out  # GEMM + quantizer of its output, separate and fused
+    python -m nvfp_kernel_b200.speed_test --table mxfp4   # MXFP4 at M = 4096, K = N = 8192, beside NVFP4
     python -m nvfp_kernel_b200.speed_test --table mlp     # gated MLP: separate kernels vs activation + quantizer in the epilogue
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m nvfp_kernel_b200.speed_test --table tp
                                                           # Llama-3-70B prefill layers, tensor-parallel
@@ -99,6 +100,38 @@ def quant(repeats: int):
         t_q = time_us(lambda: ops.scaled_fp4_quant(a, gs), repeats)
         t_a = time_us(lambda: ops.global_scale(a), repeats)
         print(f"{m:<7} {k:<7} {t_q:<15.1f} {m * k * 2.5625 / t_q / 1e3:<20.0f} {t_a:<10.1f}")
+
+
+def mxfp4(repeats: int):
+    """MXFP4 (32-element blocks, ue8m0 scales, no global scale) at M = 4096, K = N = 8192: Student-t (df = 3)
+    activations, N(0, 0.02) weights; the NVFP4 numbers of the same shape beside them."""
+    m, k, n = 4096, 8192, 8192
+    g = torch.Generator(device="cuda").manual_seed(0)
+    z = torch.randn((m, k), generator=g, device="cuda")
+    chi = sum(torch.randn((m, k), generator=g, device="cuda") ** 2 for _ in range(3)) / 3.0
+    a = (z / chi.sqrt()).to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    del z, chi
+    print(f"{'format':<8} {'quantize A (us)':<17} {'GB/s':<8} {'GEMM (us)':<11} {'TFLOP/s':<9} {'forward (us)':<13}")
+    print("-" * 70)
+    for fmt in ("mxfp4", "nvfp4"):
+        layer = QuantLinear(k, n, format=fmt, device="cuda").load_weight(w)
+        if fmt == "mxfp4":
+            a_fp4, a_sf = ops.scaled_mxfp4_quant(a)
+            w_sf = layer.weight_sf.view(torch.float8_e8m0fnu)
+            t_q = time_us(lambda: ops.scaled_mxfp4_quant(a), repeats)
+            t_mm = time_us(lambda: ops.mxfp4_scaled_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, torch.bfloat16), repeats)
+            bytes_per = 2.0 + 0.5 + 1.0 / 32
+        else:
+            gs = ops.global_scale(a)
+            a_fp4, a_sf = ops.scaled_fp4_quant(a, gs)
+            alpha = ops.alpha_from_scales(gs, layer.weight_global_scale)
+            w_sf = layer.weight_sf.view(torch.float8_e4m3fn)
+            t_q = time_us(lambda: ops.scaled_fp4_quant(a, gs), repeats)
+            t_mm = time_us(lambda: ops.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, alpha, torch.bfloat16), repeats)
+            bytes_per = 2.5625
+        t_fwd = time_us(lambda: layer(a), repeats)
+        print(f"{fmt:<8} {t_q:<17.1f} {m * k * bytes_per / t_q / 1e3:<8.0f} {t_mm:<11.1f} {2.0 * m * n * k / t_mm / 1e6:<9.0f} {t_fwd:<13.1f}")
 
 
 def fp4out(repeats: int):
@@ -255,11 +288,11 @@ def main():
     ap = argparse.ArgumentParser(description="BF16 GEMM vs FP4 GEMM with online activation quantization")
     ap.add_argument("--batch_size", type=int, default=4096, help="M dimension of the sweep")
     ap.add_argument("--repeats", type=int, default=50)
-    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp", "fp4out", "mlp"])
+    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp", "fp4out", "mlp", "mxfp4"])
     args = ap.parse_args()
     torch.cuda.empty_cache()
     {"sweep": lambda: sweep(args.batch_size, args.repeats), "decode": lambda: decode(args.repeats),
-     "quant": lambda: quant(args.repeats), "fp4out": lambda: fp4out(min(args.repeats, 20)), "mlp": lambda: mlp(min(args.repeats, 10)), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
+     "quant": lambda: quant(args.repeats), "fp4out": lambda: fp4out(min(args.repeats, 20)), "mlp": lambda: mlp(min(args.repeats, 10)), "mxfp4": lambda: mxfp4(min(args.repeats, 20)), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
 
 
 if __name__ == "__main__":
