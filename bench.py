@@ -276,13 +276,23 @@ def main_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- region 3: end to end through the public API with host buffers -----------------
     a_host = a.cpu().pin_memory()
-    out_host = torch.empty((world * M * N_PER_GPU,), dtype=torch.bfloat16).pin_memory()   # the gathered result
+    # Every rank ends a step holding the whole gathered [M, n_total] result; the host needs it once, so each rank
+    # copies out its own [M, N_PER_GPU] column slab (all ranks together: the whole result, every step).
+    out_host = torch.empty((M * N_PER_GPU,), dtype=torch.bfloat16).pin_memory()
     a_dev = torch.empty_like(a)
     e2e_steps = max(3, min(args.steps, 20))
 
+    def step_for_host(x):
+        y = step(x)
+        if world == 1:
+            return y
+        if args.gather == "nccl":
+            return y.view(world, M, N_PER_GPU)[rank]            # all_gather_into_tensor's layout: [world, M, N/world]
+        return y[:, rank * N_PER_GPU:(rank + 1) * N_PER_GPU]     # this rank's columns of the gathered matrix
+
     def e2e_step():
         a_dev.copy_(a_host, non_blocking=True)
-        y = step(a_dev)
+        y = step_for_host(a_dev)
         out_host.copy_(y.reshape(-1), non_blocking=True)
 
     for _ in range(2):
@@ -298,7 +308,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
 
     # the same calls through HostPipeline: the copy-in of step i+1, the kernels of step i and the copy-out of step
     # i-1 run at the same time (PCIe is full duplex); every step still copies its own input in and its result out
-    pipe = nv.HostPipeline(step, depth=2, device=dev, reuses_output=world > 1)
+    pipe = nv.HostPipeline(step_for_host, depth=2, device=dev, reuses_output=world > 1)
     out_hosts = [out_host, torch.empty_like(out_host).pin_memory()]
     for i in range(3):
         pipe.submit(a_host, out_hosts[i % 2])
@@ -347,7 +357,9 @@ def main_ours(args, rank: int, world: int, local_rank: int):
                      "frac_of_nominal_9pflops": gemm_tflops / NOMINAL_FP4_TFLOPS,
                      "algorithmic_flops_per_launch": 2.0 * M * N_PER_GPU * K},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                "h2d_bytes_per_step": world * a_host.numel() * 2, "d2h_bytes_per_step": world * out_host.numel() * 2,
+                "bytes_note": "totals over all ranks: every rank copies the (replicated) activation in and its own "
+                              "column slab of the result out",
                 "how": "nvfp_kernel_b200.HostPipeline(depth=2): pinned host input copied in, layer, result copied out to "
                        "pinned host memory, every step; consecutive steps overlap on three streams",
                 "serial_ms_per_step": ms_e2e_serial,
