@@ -547,7 +547,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   NVFP_REQUIRE(outputs != nullptr && n_out >= 1 && n_out <= kMaxOutputs,
                "between 1 and %d output matrices are supported, got %d", kMaxOutputs, n_out);
   for (int o = 0; o < n_out; ++o)
-    NVFP_REQUIRE(outputs[o] != nullptr && (reinterpret_cast<uintptr_t>(outputs[o]) & 15) == 0,
+    NVFP_REQUIRE((outputs[o] != nullptr || m == 0 || n == 0) && (reinterpret_cast<uintptr_t>(outputs[o]) & 15) == 0,
                  "output %d is null or not 16-byte aligned", o);
   NVFP_REQUIRE(ld >= n && ld % 8 == 0, "leading dimension %lld must be >= n and a multiple of 8", (long long)ld);
   void* d = outputs[0];
@@ -712,6 +712,7 @@ extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k,
   clear_error();
   NVFP_REQUIRE(m >= 0 && n >= 0 && k >= 0, "negative shape");
   NVFP_REQUIRE(k % 32 == 0, "Expected k to be divisible by 32, but got k: %lld.", (long long)k);
+  if (m == 0 || n == 0) return NVFP_OK;
   NVFP_REQUIRE(x != nullptr && workspace != nullptr && scratch != nullptr && w_global_scale != nullptr, "null pointer");
   NVFP_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
   NVFP_REQUIRE(x_dtype == NVFP_DTYPE_F16 || x_dtype == NVFP_DTYPE_BF16,
@@ -724,7 +725,6 @@ extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k,
   uint8_t* a_sf = a_fp4 + round_up(m * (k / 2), 256);
   float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
   float* alpha = gs + 1;
-  if (m == 0 || n == 0) return NVFP_OK;
   // The GEMM may start under the quantizer when the quantizer is the single cooperative launch; the few-rows and
   // the 128-row-tile kernels then fetch nothing but weights before their griddepcontrol.wait (the CTA-pair kernel
   // is launched the ordinary way).

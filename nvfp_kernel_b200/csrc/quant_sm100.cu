@@ -370,8 +370,8 @@ __global__ void alpha_kernel(float* alpha_out, const float* gs_a, const float* g
 }
 
 int check_16bit_input(const void* in, int64_t m, int64_t n, int64_t stride, int dtype, int block) {
-  NVFP_REQUIRE(in != nullptr, "input pointer is null");
   NVFP_REQUIRE(m >= 0 && n >= 0, "negative shape (%lld x %lld)", (long long)m, (long long)n);
+  NVFP_REQUIRE(in != nullptr || m == 0 || n == 0, "input pointer is null");      // an empty tensor has no storage
   NVFP_REQUIRE(n % block == 0, "The N dimension must be multiple of %d (got %lld).", block, (long long)n);
   NVFP_REQUIRE(dtype == NVFP_DTYPE_F16 || dtype == NVFP_DTYPE_BF16,
                "Unsupported input data type for quantize_to_fp4 (dtype code %d).", dtype);
@@ -386,11 +386,11 @@ template <int BLOCK>
 int launch_quant(void* out_fp4, void* out_sf, const void* in, const float* gs, int64_t m, int64_t n,
                  int64_t stride, int dtype, int rounding, cudaStream_t stream) {
   if (int rc = check_16bit_input(in, m, n, stride, dtype, BLOCK)) return rc;
+  if (m == 0 || n == 0) return NVFP_OK;
   NVFP_REQUIRE(out_fp4 != nullptr && out_sf != nullptr, "output pointer is null");
   NVFP_REQUIRE((reinterpret_cast<uintptr_t>(out_fp4) & 7) == 0 &&
                    (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0,
                "outputs must be aligned (fp4: 8 bytes, scales: 16 bytes)");
-  if (m == 0 || n == 0) return NVFP_OK;
   const int64_t m_tiles = ceil_div(m, kTileRows);
   const int64_t col_tiles = ceil_div(n, kTileCols);
   const int64_t k_chunks = ceil_div(n / BLOCK, 4);
@@ -548,7 +548,8 @@ extern "C" int nvfp_dynamic_fp4_quant(void* out_fp4, void* out_sf, float* gs_out
                                       const float* gs_weight, void* stream_) {
   clear_error();
   if (int rc = check_16bit_input(in, m, n, in_row_stride, in_dtype, 16)) return rc;
-  NVFP_REQUIRE(out_fp4 != nullptr && out_sf != nullptr && gs_out != nullptr && scratch != nullptr, "null pointer");
+  NVFP_REQUIRE(((out_fp4 != nullptr && out_sf != nullptr) || m == 0 || n == 0) && gs_out != nullptr && scratch != nullptr,
+               "null pointer");
   NVFP_REQUIRE(gs_weight == nullptr || alpha_out != nullptr, "alpha output is null although a weight scale is given");
   NVFP_REQUIRE((reinterpret_cast<uintptr_t>(out_fp4) & 7) == 0 && (reinterpret_cast<uintptr_t>(out_sf) & 15) == 0,
                "outputs must be aligned (fp4: 8 bytes, scales: 16 bytes)");

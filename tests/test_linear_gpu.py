@@ -254,3 +254,31 @@ def test_quant_gated_mlp_module():
     assert torch.equal(clone(x), y)
     import nvfp_kernel_b200 as nv
     assert nv.device_status() == 0
+
+
+def test_empty_batches():
+    """Zero rows (an empty batch) and zero output columns go through every entry point without a launch that
+    touches memory: empty results of the right shape, 2688 as the global scale of an empty activation."""
+    import nvfp_kernel_b200 as nv
+    from nvfp_kernel_b200 import QuantLinear
+    from helpers import capi_dynamic_quant, capi_linear_forward, capi_mm, capi_quant
+    w = (torch.randn(256, 512) * 0.05).to(torch.bfloat16).cuda()
+    layer = QuantLinear(512, 256, bias=True, device="cuda").load_weight(w)
+    x0 = torch.empty((0, 512), dtype=torch.bfloat16, device="cuda")
+    y0 = layer(x0)
+    assert y0.shape == (0, 256) and y0.dtype == torch.bfloat16
+    assert layer(x0.reshape(0, 4, 512)).shape == (0, 4, 256)
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    fp4, sf, gs, _ = capi_dynamic_quant(x0, scratch, None)
+    assert fp4.shape == (0, 256) and sf.shape == (0, 32) and gs.item() == 2688.0
+    fp4, sf = capi_quant(x0, gs)
+    assert fp4.numel() == 0 and sf.numel() == 0
+    out = capi_mm(fp4, layer.weight_fp4, sf, layer.weight_sf, torch.ones(1, device="cuda"), torch.bfloat16)
+    assert out.shape == (0, 256)
+    out = capi_linear_forward(x0, layer.weight_fp4, layer.weight_sf, layer.weight_global_scale, scratch)
+    assert out.shape == (0, 256)
+    # the layer still works afterwards (scratch state intact)
+    x = torch.randn(8, 512).to(torch.bfloat16).cuda()
+    ref = QuantLinear(512, 256, bias=True, device="cuda").load_weight(w)
+    assert torch.equal(layer(x), ref(x))
+    assert nv.device_status() == 0
