@@ -1,4 +1,4 @@
-// Block-scaled FP4 GEMM for few activation rows (decode, M <= 64).  Included by
+// Block-scaled FP4 GEMM for few activation rows (decode, M <= 128).  Included by
 // gemm_fp4_sm100.cu inside namespace nvfp::<anonymous>.
 //
 // With a handful of tokens the product is bound by streaming the weights once, and the
@@ -6,40 +6,36 @@
 // (kernel/nvfp4_scaled_mm_sm120_kernels.cu:190-220) -- leaves most SMs idle.  Here:
 //   * operands are swapped: the 128 rows of the MMA are WEIGHT rows, the MMA's N is the token count
 //     (rounded up to 16), so shared memory holds weights, not padding;
-//   * a pipeline stage covers 1024 elements of K (four 128-byte-swizzled boxes per operand), so every
-//     weight row contributes 512 contiguous bytes per stage: DRAM pages are read in long bursts instead
-//     of 128-byte slivers, and the issuer pays one barrier round trip per 16 MMAs;
+//   * a pipeline stage covers 1024 elements of K (512 above 64 tokens): four (two) 128-byte-swizzled boxes per
+//     operand, so every weight row contributes 512 (256) contiguous bytes per stage, and the issuer pays one
+//     barrier round trip per 16 (8) MMAs; all scale copies of a stage are queued before its MMAs (a barrier
+//     per box measured 60 % slower per stage);
 //   * the epilogue warps, idle during the main loop, prefetch this CTA's whole slab of weights into L2
-//     with plain prefetch instructions (the ring only keeps two stages in flight, too few to cover DRAM
-//     latency), and each box has its own barrier, so the first MMAs start when 1/4 of a stage has landed;
-//   * K is split over a cluster of CTAs; each computes a partial [128 weight rows x NT tokens]
-//     in tensor memory, the non-leaders stage theirs in their own shared memory and send it to the
-//     leader with one bulk copy per warp (shared memory to shared memory inside the cluster, completion
-//     on an mbarrier of the leader), the leader adds, scales by alpha and stores.  No global scratch, no
-//     second kernel, no atomics.
+//     with plain prefetch instructions (the ring only keeps two or three stages in flight, too few to cover DRAM
+//     latency; a prefetch through the TMA unit halved the load rate);
+//   * K is split over a cluster of CTAs; each computes a partial [128 weight rows x NT tokens] in tensor
+//     memory.  The tokens are divided among "owners" -- the leader alone, or every rank when each can get a
+//     multiple of 16 tokens -- and every rank sends each owner that owner's tokens of its partial: staged in its
+//     own (drained) shared memory, then one bulk copy per warp and owner, shared memory to shared memory inside
+//     the cluster, completion on an mbarrier of the owner.  An owner adds what it receives to its own partial,
+//     scales by alpha, adds the bias and stores its tokens.  No global scratch, no second kernel, no atomics.
 #pragma once
 
-constexpr int kSkinnyMaxTokens = 64;
+constexpr int kSkinnyMaxTokens = 128;
 constexpr int kSkinnyMaxSplit = 8;
-constexpr int kSkinnyBoxes = 4;                                   // 256-element K boxes per stage
-constexpr int kSkinnyStageK = kSkinnyBoxes * kStageK;             // 1024
-// "Full" barriers per stage.  One per box (4) lets the first MMAs start earlier but measured 60 % slower per
-// stage than one barrier (all scale copies of a stage queued before its MMAs), so the whole stage reports to one.
-constexpr int kSkinnyGroups = 1;
-constexpr int kSkinnyGroupBoxes = kSkinnyBoxes / kSkinnyGroups;   // boxes reported to one barrier
 constexpr uint32_t kSkinnyTmemCols = 256;
 constexpr uint32_t kSkinnyOutTileBytes = 16 * 128 * 4;            // output staging: 16 tokens x 128 columns fp32
-constexpr uint32_t kSkinnyAccCols = 64;                           // accumulator: columns [0, NT)
+constexpr uint32_t kSkinnyAccCols = 128;                          // accumulator: columns [0, NT)
 
-template <bool MX>
+// BOXES: 256-element K boxes per stage.
+template <bool MX, int BOXES>
 struct SkinnyCfg {
+  static constexpr int kStageElems = BOXES * kStageK;             // elements of K per stage
   static constexpr int kChunksPerBox = MX ? 2 : 4;                // 512-byte scale chunks per 256 elements of K
-  static constexpr int kChunksPerStage = kSkinnyBoxes * kChunksPerBox;
+  static constexpr int kChunksPerStage = BOXES * kChunksPerBox;
   static constexpr int kMmasPerChunk = MX ? 2 : 1;
   static constexpr uint32_t kWBoxBytes = 128 * kStageKBytes;      // 16 KB
   static constexpr uint32_t kSfBytes = kChunksPerStage * 512;     // per operand per stage
-  static constexpr int kChunksPerGroup = kSkinnyGroupBoxes * kChunksPerBox;
-  static constexpr uint32_t kSfGroupBytes = kChunksPerGroup * 512; // per operand per barrier group
   static constexpr uint32_t kSfwCol = kSkinnyAccCols;             // weight scales: 4 columns per chunk
   static constexpr uint32_t kSfxCol = kSfwCol + 4 * kChunksPerStage;
   static_assert(kSfxCol + 4 * kChunksPerStage <= kSkinnyTmemCols, "tensor memory budget");
@@ -47,24 +43,29 @@ struct SkinnyCfg {
 
 struct SkinnyParams {
   GemmParams g;
-  int nt;               // MMA N = tokens rounded up to 16
+  int nt;               // MMA N = tokens rounded up (to 16, or to 16 x owners)
   int split;            // cluster size = K splits
-  int stages_per_rank;  // stages (of 1024 elements of K) each rank of a cluster processes
+  int owners;           // ranks that reduce and store: 1 (the leader) or split (rank r owns tokens [r * tok, (r + 1) * tok))
+  int tok;              // tokens per owner = nt / owners, a multiple of 16
+  int stages_per_rank;  // stages each rank of a cluster processes
   int num_stages;       // pipeline depth
   uint32_t stage_bytes;
   const void* w;           // weights [n, k/2], for the L2 prefetch
   int after_producer;      // launched with programmatic stream serialization behind the kernel that writes the
                            // activation operand, its scales and alpha: weights may be fetched before that kernel
                            // has finished, everything it writes only after griddepcontrol.wait
-  uint32_t reduce_offset;  // leader's buffer for the peers' partial sums: 0 = it reuses the drained stage area
+  // Byte offsets from the start of shared memory.  After the main loop the stage area [0, ring) is dead and holds,
+  // from 0, the partial sums this rank stages for sending; behind them the output staging tile; the buffer this
+  // rank receives into lies behind the ring when there is room (recv_behind_ring), else behind those two.
+  uint32_t out_tile_offset;
+  uint32_t recv_offset;
+  int recv_behind_ring;
 };
 
-// Partial sums in the leader: [peer][weight row][NT + 4] fp32.  The 4 floats of padding make the row stride an
-// odd number of 16-byte units, so 32 lanes reading one float4 each from consecutive rows hit distinct banks.
-__host__ __device__ constexpr uint32_t skinny_reduce_ld(int nt) { return (uint32_t)nt + 4u; }
-__host__ __device__ constexpr uint32_t skinny_reduce_bytes(int nt, int split) {
-  return (uint32_t)(split - 1) * 128u * skinny_reduce_ld(nt) * 4u;
-}
+// Partial sums travel as [128 weight rows][tok + 4] fp32 per (sender, owner) pair.  The 4 floats of padding make the
+// row stride an odd number of 16-byte units, so 32 lanes reading one float4 each from consecutive rows hit distinct banks.
+__host__ __device__ constexpr uint32_t skinny_block_ld(int tok) { return (uint32_t)tok + 4u; }
+__host__ __device__ constexpr uint32_t skinny_block_bytes(int tok) { return 128u * skinny_block_ld(tok) * 4u; }
 
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -75,20 +76,22 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 
-template <bool MX, typename OutT>
+template <bool MX, typename OutT, int BOXES>
 __global__ void __launch_bounds__(kThreads)
 fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                        const SkinnyParams sp) {
-  using C = SkinnyCfg<MX>;
+  using C = SkinnyCfg<MX, BOXES>;
   const GemmParams& p = sp.g;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // [stages ...][leader's reduce buffer, unless it reuses the stage area][barriers]
-  const bool alias = sp.reduce_offset == 0;
-  const uint32_t reduce_bytes = skinny_reduce_bytes(sp.nt, sp.split);
-  float* reduce_buf = reinterpret_cast<float*>(smem + sp.reduce_offset);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + sp.num_stages * sp.stage_bytes + (alias ? 0u : reduce_bytes));
-  const int kFull = 0, kEmpty = kSkinnyGroups * sp.num_stages, kAccFull = kEmpty + sp.num_stages, kReduce = kAccFull + 1;
+  // [stages ...][receive buffer, when it is behind the ring][barriers]
+  const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
+  const uint32_t block_bytes = skinny_block_bytes(sp.tok);                  // one sender's tokens for one owner
+  const uint32_t recv_bytes = (uint32_t)(sp.split - 1) * block_bytes;
+  const uint32_t ld = skinny_block_ld(sp.tok);
+  float* recv_buf = reinterpret_cast<float*>(smem + sp.recv_offset);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes + (sp.recv_behind_ring ? recv_bytes : 0u));
+  const int kFull = 0, kEmpty = sp.num_stages, kAccFull = 2 * sp.num_stages, kReduce = kAccFull + 1;
   const int kNumBars = kReduce + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -97,58 +100,54 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const int lane = threadIdx.x & 31;
   const uint32_t rank = sp.split > 1 ? cluster_ctarank() : 0u;
   const int n_tile = sp.split > 1 ? (int)cluster_id_x() : (int)blockIdx.x;
+  const bool owner = (int)rank < sp.owners;
   const uint32_t stage_base = smem_u32(smem);
   auto bar = [&](int i) { return smem_u32(bars + i); };
   const uint32_t x_box_bytes = (uint32_t)sp.nt * kStageKBytes;
-  const uint32_t off_x = kSkinnyBoxes * C::kWBoxBytes;
-  const uint32_t off_sfw = off_x + kSkinnyBoxes * x_box_bytes, off_sfx = off_sfw + C::kSfBytes;
+  const uint32_t off_x = BOXES * C::kWBoxBytes;
+  const uint32_t off_sfw = off_x + BOXES * x_box_bytes, off_sfx = off_sfw + C::kSfBytes;
 
-  const int total_stages = (p.k + kSkinnyStageK - 1) / kSkinnyStageK;
+  const int total_stages = (p.k + C::kStageElems - 1) / C::kStageElems;
   const int ks_begin = min((int)rank * sp.stages_per_rank, total_stages);
   const int ks_end = min(ks_begin + sp.stages_per_rank, total_stages);
   const int my_stages = ks_end - ks_begin;
   const int k_boxes_total = (p.k + kStageK - 1) / kStageK;
   const uint8_t* sfw_tile = p.sfb + (int64_t)n_tile * p.sf_k_chunks * 512;
 
-  // Loads of local stage i (K range [ks * 1024, ks * 1024 + 1024)) into ring slot s; the boxes of one group
-  // report to one barrier.  `what` selects the weight side (armed with the bytes of both sides), the activation
-  // side, or both.
+  // Loads of local stage i into ring slot i % num_stages, all reported to the slot's one barrier.  `what` selects
+  // the weight side (which also arms the barrier with the bytes of both sides), the activation side, or both.
   constexpr int kWeights = 1, kActivations = 2;
   auto load_stage = [&](int i, int what) {
     const int ks = ks_begin + i;
     const uint32_t s = (uint32_t)i % sp.num_stages;
     const uint32_t st = stage_base + s * sp.stage_bytes;
-    const int boxes = min(kSkinnyBoxes, k_boxes_total - ks * kSkinnyBoxes);
-    for (int g = 0; g * kSkinnyGroupBoxes < boxes; ++g) {
-      const int b0 = g * kSkinnyGroupBoxes, nb = min(kSkinnyGroupBoxes, boxes - b0);
-      const int chunk0 = ks * C::kChunksPerStage + g * C::kChunksPerGroup;
-      const uint32_t sf_bytes = (uint32_t)min(C::kChunksPerGroup, p.sf_k_chunks - chunk0) * 512u;
-      const uint32_t full = bar(kFull + (int)s * kSkinnyGroups + g);
-      if (what & kWeights) {
-        mbar_arrive_expect_tx(full, (uint32_t)nb * (C::kWBoxBytes + x_box_bytes) + 2 * sf_bytes);
-        for (int b = b0; b < b0 + nb; ++b)
-          tma_load_2d(st + b * C::kWBoxBytes, &tmap_w, full, (ks * kSkinnyBoxes + b) * kStageKBytes, n_tile * 128);
-        bulk_load(st + off_sfw + g * C::kSfGroupBytes, sfw_tile + (int64_t)chunk0 * 512, sf_bytes, full);
-      }
-      if (what & kActivations) {
-        for (int b = b0; b < b0 + nb; ++b)
-          tma_load_2d(st + off_x + b * x_box_bytes, &tmap_x, full, (ks * kSkinnyBoxes + b) * kStageKBytes, 0);
-        bulk_load(st + off_sfx + g * C::kSfGroupBytes, p.sfa + (int64_t)chunk0 * 512, sf_bytes, full);
-      }
+    const int boxes = min(BOXES, k_boxes_total - ks * BOXES);
+    const int chunk0 = ks * C::kChunksPerStage;
+    const uint32_t sf_bytes = (uint32_t)min(C::kChunksPerStage, p.sf_k_chunks - chunk0) * 512u;
+    const uint32_t full = bar(kFull + (int)s);
+    if (what & kWeights) {
+      mbar_arrive_expect_tx(full, (uint32_t)boxes * (C::kWBoxBytes + x_box_bytes) + 2 * sf_bytes);
+      for (int b = 0; b < boxes; ++b)
+        tma_load_2d(st + b * C::kWBoxBytes, &tmap_w, full, (ks * BOXES + b) * kStageKBytes, n_tile * 128);
+      bulk_load(st + off_sfw, sfw_tile + (int64_t)chunk0 * 512, sf_bytes, full);
+    }
+    if (what & kActivations) {
+      for (int b = 0; b < boxes; ++b)
+        tma_load_2d(st + off_x + b * x_box_bytes, &tmap_x, full, (ks * BOXES + b) * kStageKBytes, 0);
+      bulk_load(st + off_sfx, p.sfa + (int64_t)chunk0 * 512, sf_bytes, full);
     }
   };
   if (warp == 0) {
     // The producer thread initialises the barriers itself and starts the first loads before the rest of
     // the CTA (tensor memory allocation, the other warps) is ready.
     if (elect_one()) {
-      for (int i = 0; i < kEmpty; ++i) mbar_init(bar(kFull + i), 1);
-      for (int i = 0; i < sp.num_stages; ++i) mbar_init(bar(kEmpty + i), 1);
+      for (int i = 0; i < kAccFull; ++i) mbar_init(bar(i), 1);
       mbar_init(bar(kAccFull), 1);
       mbar_init(bar(kReduce), 1);
       *abort_flag = 0;
       fence_mbar_init();
       fence_proxy_async_smem();
-      if (sp.split > 1 && rank == 0) mbar_arrive_expect_tx(bar(kReduce), reduce_bytes);
+      if (sp.split > 1 && owner) mbar_arrive_expect_tx(bar(kReduce), recv_bytes);
       prefetch_tensormap(&tmap_w);
       prefetch_tensormap(&tmap_x);
       const int first = min(my_stages, sp.num_stages);
@@ -170,8 +169,8 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  // With a buffer of its own the leader is ready for the peers' partial sums from here on.
-  if (sp.split > 1 && !alias) cluster_arrive();
+  // With receive buffers behind the rings every rank is ready for the others' partial sums from here on.
+  if (sp.split > 1 && sp.recv_behind_ring) cluster_arrive();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer ---
@@ -193,61 +192,54 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       const uint32_t sfw_tmem = tmem_base + C::kSfwCol, sfx_tmem = tmem_base + C::kSfxCol;
       const uint32_t idesc0 = make_idesc_fp4_block_scaled(128, sp.nt, MX, 0u, 0u);
       const uint32_t idesc1 = MX ? make_idesc_fp4_block_scaled(128, sp.nt, true, 2u, 2u) : idesc0;
-      bool ok = true;
-      for (int i = 0; i < my_stages && ok; ++i) {
+      for (int i = 0; i < my_stages; ++i) {
         const int ks = ks_begin + i;
         const uint32_t s = (uint32_t)i % sp.num_stages, ph = ((uint32_t)i / sp.num_stages) & 1u;
         const uint32_t st = stage_base + s * sp.stage_bytes;
-        const int boxes = min(kSkinnyBoxes, k_boxes_total - ks * kSkinnyBoxes);
-        for (int g = 0; g * kSkinnyGroupBoxes < boxes; ++g) {
-          if (!mbar_wait_bounded(bar(kFull + (int)s * kSkinnyGroups + g), ph, abort_flag)) {
-            *abort_flag = 1;
-            atomicOr(p.status, kErrIssuer);
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const int b0 = g * kSkinnyGroupBoxes, nb = min(kSkinnyGroupBoxes, boxes - b0);
-          const int chunk0 = ks * C::kChunksPerStage + g * C::kChunksPerGroup;
-          const int chunks = min(C::kChunksPerGroup, p.sf_k_chunks - chunk0);
-          // one set of scale columns per position in the stage: the tensor pipe runs one thread's copies and
-          // MMAs in issue order, so a later stage's copies cannot overtake this stage's MMAs
-          const uint32_t col = 4u * (uint32_t)(g * C::kChunksPerGroup);
-          const uint64_t sfw_desc = make_smem_desc(st + off_sfw + g * C::kSfGroupBytes, 0, 128, 0);
-          const uint64_t sfx_desc = make_smem_desc(st + off_sfx + g * C::kSfGroupBytes, 0, 128, 0);
-          for (int c = 0; c < chunks; ++c) {
-            tc_copy_sf_32x128b_warpx4(sfw_tmem + col + 4 * c, sfw_desc + (uint64_t)(c * 32));
-            tc_copy_sf_32x128b_warpx4(sfx_tmem + col + 4 * c, sfx_desc + (uint64_t)(c * 32));
-          }
-          for (int b = b0; b < b0 + nb; ++b) {
-            const int mmas = min(kStageK / kMmaK, (p.k - (ks * kSkinnyBoxes + b) * kStageK + kMmaK - 1) / kMmaK);
-            const uint64_t w_desc = make_smem_desc(st + b * C::kWBoxBytes, 16, 1024, 2);
-            const uint64_t x_desc = make_smem_desc(st + off_x + b * x_box_bytes, 16, 1024, 2);
-            const uint32_t bcol = 4u * (uint32_t)(b * C::kChunksPerBox);
-            for (int j = 0; j < mmas; ++j) {
-              const int c = j / C::kMmasPerChunk;
-              const uint32_t accumulate = (i | b | j) != 0 ? 1u : 0u;
-              if (MX)
-                tc_mma_mxf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), (j & 1) ? idesc1 : idesc0,
-                            sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
-              else
-                tc_mma_nvf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), idesc0,
-                            sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
-            }
+        const int boxes = min(BOXES, k_boxes_total - ks * BOXES);
+        if (!mbar_wait_bounded(bar(kFull + (int)s), ph, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(p.status, kErrIssuer);
+          break;
+        }
+        tc_fence_after_sync();
+        const int chunk0 = ks * C::kChunksPerStage;
+        const int chunks = min(C::kChunksPerStage, p.sf_k_chunks - chunk0);
+        // one set of scale columns per position in the stage: the tensor pipe runs one thread's copies and
+        // MMAs in issue order, so a later stage's copies cannot overtake this stage's MMAs
+        const uint64_t sfw_desc = make_smem_desc(st + off_sfw, 0, 128, 0);
+        const uint64_t sfx_desc = make_smem_desc(st + off_sfx, 0, 128, 0);
+        for (int c = 0; c < chunks; ++c) {
+          tc_copy_sf_32x128b_warpx4(sfw_tmem + 4 * c, sfw_desc + (uint64_t)(c * 32));
+          tc_copy_sf_32x128b_warpx4(sfx_tmem + 4 * c, sfx_desc + (uint64_t)(c * 32));
+        }
+        for (int b = 0; b < boxes; ++b) {
+          const int mmas = min(kStageK / kMmaK, (p.k - (ks * BOXES + b) * kStageK + kMmaK - 1) / kMmaK);
+          const uint64_t w_desc = make_smem_desc(st + b * C::kWBoxBytes, 16, 1024, 2);
+          const uint64_t x_desc = make_smem_desc(st + off_x + b * x_box_bytes, 16, 1024, 2);
+          const uint32_t bcol = 4u * (uint32_t)(b * C::kChunksPerBox);
+          for (int j = 0; j < mmas; ++j) {
+            const int c = j / C::kMmasPerChunk;
+            const uint32_t accumulate = (i | b | j) != 0 ? 1u : 0u;
+            if (MX)
+              tc_mma_mxf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), (j & 1) ? idesc1 : idesc0,
+                          sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
+            else
+              tc_mma_nvf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), idesc0,
+                          sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
           }
         }
-        if (ok) tc_commit(bar(kEmpty + s));
+        tc_commit(bar(kEmpty + s));
+        if (i == my_stages - 1) tc_commit(bar(kAccFull));
       }
-      if (ok) tc_commit(bar(kAccFull));
     }
     __syncwarp();
   }
 
-  // ------------------------------------------------- partial sums -> leader ---
+  // -------------------------------------- partial sums -> owners -> output ---
   const bool epi = warp >= 2;
   const int q = warp & 3;
   const int wrow = q * 32 + lane;                 // weight row within the tile = accumulator lane
-  const uint32_t ld = skinny_reduce_ld(sp.nt);
   bool have_acc = false;
   float alpha = 1.0f, bias = 0.0f;
   if (epi) {
@@ -255,13 +247,13 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
     const int row = n_tile * 128 + wrow;
     if (row < p.n) {
       const uint8_t* w_row = static_cast<const uint8_t*>(sp.w) + (int64_t)row * (p.k / 2);
-      const int byte_begin = (ks_begin + min(my_stages, sp.num_stages)) * (kSkinnyStageK / 2);
-      const int byte_end = min(ks_end * (kSkinnyStageK / 2), p.k / 2);
+      const int byte_begin = (ks_begin + min(my_stages, sp.num_stages)) * (C::kStageElems / 2);
+      const int byte_end = min(ks_end * (C::kStageElems / 2), p.k / 2);
       for (int off = byte_begin; off < byte_end; off += 128) prefetch_l2(w_row + off);
     }
     if (sp.after_producer) griddep_wait();         // alpha comes from the kernel before this one
-    if (rank == 0 && p.alpha) alpha = *reinterpret_cast<const volatile float*>(p.alpha);
-    if (rank == 0 && p.bias && row < p.n) {
+    if (owner && p.alpha) alpha = *reinterpret_cast<const volatile float*>(p.alpha);
+    if (owner && p.bias && row < p.n) {
       if constexpr (sizeof(OutT) == 4) bias = __ldg(static_cast<const float*>(p.bias) + row);
       else if constexpr (std::is_same<OutT, __half>::value) bias = __half2float(static_cast<const __half*>(p.bias)[row]);
       else bias = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row]);
@@ -278,55 +270,66 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
   bool have_peers = true;
   if (sp.split > 1) {
-    // A leader whose buffer reuses the stage area is ready only now: its epilogue warps arrive after its
+    // A rank whose receive buffer lies in its stage area is ready only now: its epilogue warps arrive after its
     // last MMA has completed (all TMA writes landed, all MMA reads done).
-    if (alias) cluster_arrive();
+    if (!sp.recv_behind_ring) cluster_arrive();
     cluster_wait();
-    if (epi && rank != 0) {
-      // own partial -> own (drained) stage area, laid out like the leader's buffer, then one bulk copy per warp
-      const uint32_t stage_row = stage_base + (uint32_t)wrow * ld * 4u;
-      for (int c = 0; c < sp.nt; c += 16) {
-        uint32_t r[16];
-        if (have_acc) {
-          tmem_ld_32x32b_x16(t_row + c, r);
-          tmem_ld_wait();
-        } else {
+    if (epi) {
+      // This rank's partial for every owner but itself -> its own (drained) stage area, one block
+      // [128 rows][tok + 4] per owner, then one bulk copy per warp and owner into that owner's receive buffer;
+      // slot of sender r at owner o: r for r < o, r - 1 above.
+      for (int o = 0; o < sp.owners; ++o) {
+        if (o == (int)rank) continue;
+        const uint32_t block = stage_base + (uint32_t)o * block_bytes;
+        const uint32_t stage_row = block + (uint32_t)wrow * ld * 4u;
+        for (int c = 0; c < sp.tok; c += 16) {
+          uint32_t r[16];
+          if (have_acc) {
+            tmem_ld_32x32b_x16(t_row + o * sp.tok + c, r);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int t = 0; t < 16; ++t) r[t] = 0u;
+            for (int t = 0; t < 16; ++t) r[t] = 0u;
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            st_shared_v4(stage_row + (uint32_t)(c + 4 * v) * 4u, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
         }
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          st_shared_v4(stage_row + (uint32_t)(c + 4 * v) * 4u, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         const uint32_t warp_bytes = 32u * ld * 4u, warp_off = (uint32_t)q * warp_bytes;
-        bulk_copy_to_cta(map_to_cta(smem_u32(reduce_buf), 0) + (rank - 1) * 128u * ld * 4u + warp_off, stage_base + warp_off,
-                         warp_bytes, map_to_cta(bar(kReduce), 0));
+        for (int o = 0; o < sp.owners; ++o) {
+          if (o == (int)rank) continue;
+          const uint32_t slot = (int)rank < o ? rank : rank - 1u;
+          bulk_copy_to_cta(map_to_cta(smem_u32(recv_buf), (uint32_t)o) + slot * block_bytes + warp_off,
+                           stage_base + (uint32_t)o * block_bytes + warp_off, warp_bytes, map_to_cta(bar(kReduce), (uint32_t)o));
+        }
       }
       __syncwarp();
     }
-    if (epi && rank == 0) {
+    if (epi && owner) {
       have_peers = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kReduce), 0, abort_flag));
       if (!have_peers) {
         *abort_flag = 1;
         if (lane == 0) atomicOr(p.status, kErrEpilogue);
       }
     }
-    // Second phase: a peer may leave only after the leader has received every copy (its source is the
-    // peer's shared memory); the leader arrives here and adds while the peers wait.  Nothing written before
-    // this arrival is read by another CTA afterwards, so it needs no release.
+    // Second phase: a rank may leave only after every owner has received every copy (the copies' source is the
+    // sender's shared memory); an owner arrives here once it has its data and adds while the others wait.  Nothing
+    // written before this arrival is read by another CTA afterwards, so it needs no release.
     cluster_arrive_relaxed();
   }
-  if (epi && rank == 0) {
+  if (epi && owner) {
     OutT* d = static_cast<OutT*>(p.d);
-    // staging tile [16 tokens][128 columns] in the drained stage area, behind the partial sums if they are there
-    OutT* out_tile = reinterpret_cast<OutT*>(smem + (alias ? reduce_bytes : 0u));
-    for (int c = 0; c < sp.nt; c += 16) {
+    // staging tile [16 tokens][128 columns] in the drained stage area, behind the blocks staged for sending
+    OutT* out_tile = reinterpret_cast<OutT*>(smem + sp.out_tile_offset);
+    const int tok0 = (int)rank * sp.tok;
+    for (int c = 0; c < sp.tok; c += 16) {
       uint32_t r[16];
       if (have_acc) {
-        tmem_ld_32x32b_x16(t_row + c, r);
+        tmem_ld_32x32b_x16(t_row + tok0 + c, r);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -337,7 +340,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       for (int t = 0; t < 16; ++t) part[t] = __uint_as_float(r[t]);
       if (have_peers) {
         for (int pr = 0; pr < sp.split - 1; ++pr) {
-          const float4* src = reinterpret_cast<const float4*>(reduce_buf + (pr * 128 + wrow) * ld + c);
+          const float4* src = reinterpret_cast<const float4*>(recv_buf + (pr * 128 + wrow) * ld + c);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const float4 f = src[v];
@@ -360,9 +363,9 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       constexpr int kSegElems = 16 / (int)sizeof(OutT);
       for (int sidx = (int)threadIdx.x - 64; sidx < 16 * kSegs; sidx += 128) {
         const int t = sidx / kSegs, seg = sidx % kSegs;
-        const int tok = c + t, col = n_tile * 128 + seg * kSegElems;
-        if (tok < p.m && col < p.n)
-          *reinterpret_cast<uint4*>(d + (int64_t)tok * p.n + col) = *reinterpret_cast<const uint4*>(out_tile + t * 128 + seg * kSegElems);
+        const int token = tok0 + c + t, col = n_tile * 128 + seg * kSegElems;
+        if (token < p.m && col < p.n)
+          *reinterpret_cast<uint4*>(d + (int64_t)token * p.n + col) = *reinterpret_cast<const uint4*>(out_tile + t * 128 + seg * kSegElems);
       }
     }
   }
@@ -373,64 +376,85 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   if (warp == 1) tmem_dealloc(tmem_base, kSkinnyTmemCols);
 }
 
-// Cluster size for n_tiles weight tiles and total_stages stages of K: double it while all CTAs still run in
-// one wave and every rank keeps enough stages to pay for the exchange of partial sums, whose cost grows with
-// the token count.  Measured on B200 (cold L2, 128 x 1024 stages): K = 14336, N = 4096 takes 20 / 15.5 / 12.6 us
-// with 1 / 2 / 4 ranks at 16 tokens and 21.4 / 16.5 / 17.2 us at 64 tokens; at K = 4096 splitting gains
-// nothing at 64 tokens and up to 0.5 us at 16.
-inline int skinny_split(int nt, int n_tiles, int total_stages, int sm_count) {
-  const int min_stages_per_rank = nt <= 32 ? 2 : 4;
+// K split for n_tiles weight tiles: double the cluster while all CTAs still run in one wave and every rank keeps
+// at least 2048 elements of K, about what the exchange of partial sums costs.  Measured on B200 (cold L2, events):
+// K = 14336, N = 4096: 16 tokens 20 / 15.5 / 12.6 us with 1 / 2 / 4 ranks; 128 tokens 29.6 / 23.6 / 21.5 us (the
+// 128-row tile kernel: 33.6 us); at K = 4096 a second rank gains about 1 us and more ranks nothing.
+inline int skinny_split(int n_tiles, int64_t k, int sm_count) {
   int split = 1;
-  while (split < kSkinnyMaxSplit && n_tiles * split * 2 <= sm_count &&
-         total_stages >= split * 2 * min_stages_per_rank)
-    split *= 2;
+  while (split < kSkinnyMaxSplit && n_tiles * split * 2 <= sm_count && k >= (int64_t)split * 2 * 2048) split *= 2;
   return split;
 }
 
-// Shapes this kernel is the better choice for: up to 64 tokens, unless the weight tiles alone need more than
-// one wave of CTAs and the tokens fill half of a 128-row tile anyway.
+// Shapes this kernel is the better choice for: up to 32 tokens always; up to 64 unless the weight tiles alone need
+// more than one wave of CTAs (the tokens then fill half of a 128-row tile anyway); up to 128 while the weight tiles
+// leave at least half of the SMs idle, so that splitting K can use them.
 inline bool skinny_preferred(int64_t m, int64_t n, int sm_count) {
   if (m > kSkinnyMaxTokens) return false;
-  return m <= 32 || ceil_div(n, 128) <= sm_count;
+  const int64_t n_tiles = ceil_div(n, 128);
+  if (m > 64) return n_tiles * 2 <= sm_count;
+  return m <= 32 || n_tiles <= sm_count;
 }
 
-template <bool MX, typename OutT>
-int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
-                  bool after_producer = false) {
-  using C = SkinnyCfg<MX>;
+template <bool MX, typename OutT, int BOXES>
+int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
+                        bool after_producer) {
+  using C = SkinnyCfg<MX, BOXES>;
+  constexpr int kMaxTokens = BOXES == 4 ? 64 : 128;
   SkinnyParams sp{};
   sp.g = base;
   sp.w = b;
   sp.after_producer = after_producer ? 1 : 0;
   const int m = base.m, n = base.n, k = base.k;
-  sp.nt = (int)round_up(m, 16);
   const int n_tiles = (int)ceil_div(n, 128);
-  const int total_stages = (int)ceil_div(k, kSkinnyStageK);
-  sp.stage_bytes =
-      (uint32_t)round_up(kSkinnyBoxes * (C::kWBoxBytes + (uint32_t)sp.nt * kStageKBytes) + 2 * C::kSfBytes, 1024);
+  const int total_stages = (int)ceil_div(k, C::kStageElems);
   const uint32_t budget = (uint32_t)kSmemLimit - 2048u;
-  const int max_stages = (int)(budget / sp.stage_bytes);
-  sp.split = skinny_split(sp.nt, n_tiles, total_stages, sm_count);
-  sp.stages_per_rank = (int)ceil_div(total_stages, sp.split);
-  sp.num_stages = std::max(1, std::min(sp.stages_per_rank, max_stages));
-  // The peers' partial sums get a buffer of their own behind the ring when it fits; otherwise they go into
-  // the leader's drained stage area (one more cluster barrier on the critical path).
-  const uint32_t reduce_bytes = sp.split > 1 ? skinny_reduce_bytes(sp.nt, sp.split) : 0u;
-  const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
-  uint32_t smem_bytes;
-  if (ring_bytes + reduce_bytes <= budget) {
-    sp.reduce_offset = sp.split > 1 ? ring_bytes : 1u;   // any non-zero value when there is nothing to reduce
-    smem_bytes = ring_bytes + reduce_bytes + 2048;
-  } else {
-    NVFP_REQUIRE(reduce_bytes + kSkinnyOutTileBytes <= ring_bytes,
-                 "internal: partial sums of %u bytes do not fit %u bytes of stages", reduce_bytes, ring_bytes);
-    sp.reduce_offset = 0;
-    smem_bytes = ring_bytes + 2048;
+  int split = skinny_split(n_tiles, k, sm_count);
+  uint32_t smem_bytes = 0;
+  for (;; split /= 2) {
+    // Every rank an owner when each can have a multiple of 16 tokens without padding the MMA beyond its limit and
+    // there is more than one chunk of tokens to share out; else the leader alone, which is only worth it for one
+    // chunk of tokens (32 and more tokens into one CTA cost more than the split saves).
+    int nt = (int)round_up(m, 16), owners = 1;
+    const int nt_scatter = (int)round_up(m, 16 * split);
+    const bool scatter = split > 1 && nt >= 32 && nt_scatter <= kMaxTokens;
+    if (split > 1 && nt >= 32 && !scatter) continue;
+    if (scatter) {
+      nt = nt_scatter;
+      owners = split;
+    }
+    sp.nt = nt;
+    sp.split = split;
+    sp.owners = owners;
+    sp.tok = nt / owners;
+    sp.stage_bytes = (uint32_t)round_up(BOXES * (C::kWBoxBytes + (uint32_t)nt * kStageKBytes) + 2 * C::kSfBytes, 1024);
+    const int max_stages = (int)(budget / sp.stage_bytes);
+    NVFP_REQUIRE(max_stages >= 1, "internal: a stage of %u bytes does not fit shared memory", sp.stage_bytes);
+    sp.stages_per_rank = (int)ceil_div(total_stages, split);
+    sp.num_stages = std::max(1, std::min(sp.stages_per_rank, max_stages));
+    const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
+    const uint32_t block_bytes = skinny_block_bytes(sp.tok);
+    const uint32_t staging_bytes = split > 1 ? (uint32_t)owners * block_bytes : 0u;
+    const uint32_t recv_bytes = (uint32_t)(split - 1) * block_bytes;
+    sp.out_tile_offset = staging_bytes;
+    if (ring_bytes + recv_bytes <= budget && staging_bytes + kSkinnyOutTileBytes <= ring_bytes) {
+      sp.recv_behind_ring = 1;
+      sp.recv_offset = ring_bytes;
+      smem_bytes = ring_bytes + recv_bytes + 2048;
+      break;
+    }
+    if (staging_bytes + kSkinnyOutTileBytes + recv_bytes <= ring_bytes) {
+      sp.recv_behind_ring = 0;
+      sp.recv_offset = staging_bytes + kSkinnyOutTileBytes;
+      smem_bytes = ring_bytes + 2048;
+      break;
+    }
+    NVFP_REQUIRE(split > 1, "internal: the epilogue's buffers do not fit %u bytes of stages", ring_bytes);
   }
   CUtensorMap map_w, map_x;
   if (int rc = make_operand_map(&map_w, b, n, k, 128)) return rc;
   if (int rc = make_operand_map(&map_x, a, m, k, sp.nt)) return rc;
-  auto kernel = fp4_gemm_skinny_kernel<MX, OutT>;
+  auto kernel = fp4_gemm_skinny_kernel<MX, OutT, BOXES>;
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(n_tiles * sp.split));
@@ -455,4 +479,13 @@ int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_c
   cfg.numAttrs = num_attrs;
   NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, sp));
   return NVFP_OK;
+}
+
+// Up to 64 tokens: stages of 1024 elements of K; above, the activation box is as large as the weight box and
+// stages of 512 keep three of them in shared memory.
+template <bool MX, typename OutT>
+int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
+                  bool after_producer = false) {
+  if (base.m <= 64) return launch_skinny_boxes<MX, OutT, 4>(base, a, b, sm_count, stream, after_producer);
+  return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer);
 }

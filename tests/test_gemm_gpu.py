@@ -102,12 +102,14 @@ def test_edge_shapes_vs_cpu_oracle(m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 96, 8192), (17, 128, 8448), (48, 4096, 14336), (64, 160, 9216),
-                                   (8, 1024, 32768), (33, 256, 4608), (64, 19072, 1024), (2, 32, 64)])
+                                   (8, 1024, 32768), (33, 256, 4608), (64, 19072, 1024), (2, 32, 64),
+                                   (128, 1024, 8192), (100, 4096, 14336), (65, 160, 4352), (96, 6144, 512)])
 @pytest.mark.parametrize("mx", [False, True])
 def test_split_k_cluster_path_for_few_rows_and_long_k(m, n, k, mx):
-    """Shapes the dispatcher sends to the swap-operands / cluster split-K kernel: clusters of 1, 2, 4 and 8,
-    partial sums in a buffer of their own and in the drained stage area, ragged last stages, more weight
-    tiles than SMs."""
+    """Shapes the dispatcher sends to the swap-operands / cluster split-K kernel: clusters of 1, 2, 4 and 8, the
+    leader reducing alone (one chunk of tokens) and every rank reducing its share of the tokens, receive buffers
+    behind the ring and in the drained stage area, ragged last stages, more weight tiles than SMs, 1024- and
+    512-element stages (up to 64 / 128 tokens)."""
     a, w = gemm_inputs(m, n, k, seed=m + k, w_std=0.05)
     if mx:
         a_fp4, a_sf = capi_mx_quant(a.cuda())
