@@ -398,7 +398,7 @@ inline bool skinny_preferred(int64_t m, int64_t n, int sm_count) {
 
 template <bool MX, typename OutT, int BOXES>
 int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
-                        bool after_producer) {
+                        bool after_producer, int max_ring_stages = 1 << 30) {
   using C = SkinnyCfg<MX, BOXES>;
   constexpr int kMaxTokens = BOXES == 4 ? 64 : 128;
   SkinnyParams sp{};
@@ -432,6 +432,7 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
     NVFP_REQUIRE(max_stages >= 1, "internal: a stage of %u bytes does not fit shared memory", sp.stage_bytes);
     sp.stages_per_rank = (int)ceil_div(total_stages, split);
     sp.num_stages = std::max(1, std::min(sp.stages_per_rank, max_stages));
+    sp.num_stages = std::min(sp.num_stages, max_ring_stages);
     const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
     const uint32_t block_bytes = skinny_block_bytes(sp.tok);
     const uint32_t staging_bytes = split > 1 ? (uint32_t)owners * block_bytes : 0u;
@@ -486,6 +487,12 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
 template <bool MX, typename OutT>
 int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
                   bool after_producer = false) {
+  // More weight tiles than SMs but at most two per SM, short K: with two 512-element stages a CTA needs under half
+  // of an SM's shared memory, so all CTAs are resident at once and share the DRAM bandwidth instead of running as one
+  // full wave and a partial one (N = 28672, K = 4096, up to 32 tokens: 24.5 against 26.7 us; at K = 8192 it loses).
+  const int64_t n_tiles = ceil_div(base.n, 128);
+  if (base.m <= 32 && n_tiles > sm_count && n_tiles <= 2 * sm_count && base.k <= 4096)
+    return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer, 2);
   if (base.m <= 64) return launch_skinny_boxes<MX, OutT, 4>(base, a, b, sm_count, stream, after_producer);
   return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer);
 }
