@@ -608,10 +608,13 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
     }
   }
   p.after_producer = after_producer ? 1 : 0;     // the tile kernel below knows to fetch only B before it waits
-  // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a
-  // single accumulator buffer; use them when there are enough tiles to fill the GPU.
-  const int64_t tiles256 = ceil_div(m, kBM) * ceil_div(n, 256);
-  const bool wide = n >= 256 && tiles256 >= info.sm_count;
+  // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a single accumulator
+  // buffer; use them when there are enough of them to fill the GPU, and also when 128-wide tiles would need more
+  // than one wave of CTAs (measured: 512 x 6144 x 4096 21.4 against 24.6 us, 256 x 14336 x 4096 22.5 against 25.5,
+  // 128 x 28672 x 4096 25.5 against 26.6; with at most one wave of 128-wide tiles the wide ones lose, 128 x 14336 x
+  // 4096 22.0 against 18.4).
+  const int64_t tiles256 = ceil_div(m, kBM) * ceil_div(n, 256), tiles128 = ceil_div(m, kBM) * ceil_div(n, 128);
+  const bool wide = n >= 256 && (tiles256 >= info.sm_count || (tiles128 > info.sm_count && k >= 2048));
   if (wide) {
     switch (out_dtype) {
       case NVFP_DTYPE_BF16: return launch_config<256, MX, __nv_bfloat16>(p, a, b, info.sm_count, stream);
