@@ -120,10 +120,35 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------------------------------------ producer ---
     if (elect_one()) {
       uint32_t kc = 0;
+      int ks0 = 0;
       bool ok = true;
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      if (p.after_producer && first_tile < num_tiles) {
+        // Launched under the kernel that writes A, its scales and alpha: the ring's first fill fetches the B side
+        // (which that kernel does not touch) at once and the A side after griddepcontrol.wait.
+        const int tm = first_tile % p.tiles_m, tn = first_tile / p.tiles_m;
+        const int early = min(k_stages, C::kStages);
+        for (int ks = 0; ks < early; ++ks) {
+          const uint32_t st = smem_base + (uint32_t)ks * C::kStageBytes;
+          const uint32_t full = map_to_cta(bar(kFull + ks), 0);
+          if (rank == 0) mbar_arrive_expect_tx(bar(kFull + ks), 2 * C::kStageBytes);
+          tma_load_2d_pair(st + C::kABytes, &tmap_b, full, ks * kStageKBytes, tn * kPairBN + (int)rank * 128);
+          tma_load_3d_pair(st + C::kABytes + C::kBBytes + C::kSfaBytes, &tmap_sfb, full, 0,
+                           ks * C::kChunksPerStage, tn * 2);
+        }
+        griddep_wait();
+        for (int ks = 0; ks < early; ++ks) {
+          const uint32_t st = smem_base + (uint32_t)ks * C::kStageBytes;
+          const uint32_t full = map_to_cta(bar(kFull + ks), 0);
+          tma_load_2d_pair(st, &tmap_a, full, ks * kStageKBytes, tm * kPairBM + (int)rank * 128);
+          tma_load_3d_pair(st + C::kABytes + C::kBBytes, &tmap_sfa, full, 0, ks * C::kChunksPerStage,
+                           tm * 2 + (int)rank);
+        }
+        kc = (uint32_t)early;
+        ks0 = early;
+      }
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ks0 = 0) {
         const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-        for (int ks = 0; ks < k_stages; ++ks, ++kc) {
+        for (int ks = ks0; ks < k_stages; ++ks, ++kc) {
           const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
           if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
             *abort_flag = 1;
@@ -247,7 +272,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     constexpr int kSteps = kPairBN / kCols;
     constexpr int kEarlySteps = 64 / kCols;                  // steps that cover the 48 shared columns
     const int q = warp & 3;
-    const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+    if (p.after_producer) griddep_wait();   // alpha comes from the kernel before this one
+    const float alpha = p.alpha ? *reinterpret_cast<const volatile float*>(p.alpha) : 1.0f;
     const OutT* bias = static_cast<const OutT*>(p.bias);
     const float out_gs = (OUT_MODE == kOutFused && p.out_gs) ? __ldg(p.out_gs) : 1.0f;
     const float rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
@@ -390,13 +416,15 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = p.after_producer ? 2 : 1;
   NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, out_maps, n_out, rows_per_owner, p));
   return NVFP_OK;
 }

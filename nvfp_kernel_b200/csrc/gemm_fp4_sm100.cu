@@ -594,6 +594,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
       default: return launch_skinny<MX, float>(p, a, b, info.sm_count, stream, after_producer);
     }
   }
+  p.after_producer = (after_producer && n_out == 1) ? 1 : 0;   // the kernels below fetch only B before they wait
   // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
   const int64_t pair_tiles = ceil_div(m, kPairBM) * ceil_div(n, kPairBN);
   if (n_out > 1 || ld != n || (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2)) {
@@ -607,7 +608,6 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
       default: return launch_pair<MX, float>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
     }
   }
-  p.after_producer = after_producer ? 1 : 0;     // the tile kernel below knows to fetch only B before it waits
   // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a single accumulator
   // buffer; use them when there are enough of them to fill the GPU, and also when 128-wide tiles would need more
   // than one wave of CTAs (measured: 512 x 6144 x 4096 21.4 against 24.6 us, 256 x 14336 x 4096 22.5 against 25.5,
@@ -728,9 +728,8 @@ extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k,
   uint8_t* a_sf = a_fp4 + round_up(m * (k / 2), 256);
   float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
   float* alpha = gs + 1;
-  // The GEMM may start under the quantizer when the quantizer is the single cooperative launch; the few-rows and
-  // the 128-row-tile kernels then fetch nothing but weights before their griddepcontrol.wait (the CTA-pair kernel
-  // is launched the ordinary way).
+  // The GEMM may start under the quantizer when the quantizer is the single cooperative launch; every GEMM kernel
+  // then fetches nothing but weights before its griddepcontrol.wait.
   const bool overlap = dynamic_fp4_quant_is_one_pass(m, k, x_dtype);
   bool one_pass = false;
   if (int rc = dynamic_fp4_quant_launch(a_fp4, a_sf, gs, alpha, scratch, x, m, k, x_row_stride, x_dtype, w_global_scale,

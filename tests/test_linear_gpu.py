@@ -137,11 +137,13 @@ def test_host_pipeline_matches_direct_calls():
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 6144, 4096), (8, 4096, 14336), (48, 256, 1024), (128, 512, 2048),
-                                   (300, 384, 1024), (2048, 4096, 4096)])
+                                   (300, 384, 1024), (2048, 4096, 4096), (1024, 8192, 1024), (2048, 4096, 2048),
+                                   (100, 1024, 8192)])
 def test_one_call_forward_equals_the_separate_calls(m, n, k):
-    """nvfp_linear_forward (quantizer and GEMM issued by one call; for few rows the GEMM is launched under the
-    quantizer and streams its weights meanwhile) gives the bytes of nvfp_dynamic_fp4_quant + nvfp_scaled_fp4_mm(_bias),
-    call after call with changing inputs, with and without a bias."""
+    """nvfp_linear_forward (quantizer and GEMM issued by one call; while the quantizer is the one-pass kernel the
+    GEMM -- few-rows, 128-row-tile or CTA-pair kernel -- is launched under it and fetches its weights meanwhile) gives
+    the bytes of nvfp_dynamic_fp4_quant + nvfp_scaled_fp4_mm(_bias), call after call with changing inputs, with and
+    without a bias."""
     from helpers import capi_dynamic_quant, capi_global_scale, capi_linear_forward, capi_mm, capi_quant
     a, w = gemm_inputs(m, n, k, seed=m + n + k, w_std=0.05)
     a, w = a.cuda(), w.cuda()
