@@ -31,7 +31,7 @@ inline int64_t ceil_div(int64_t x, int64_t y) { return (x + y - 1) / y; }
 // Device status word written by kernels whose bounded waits expire.
 uint32_t* device_status_word();
 
-// nvfp_dynamic_fp4_quant without the argument checks.  release_next: the one-pass kernel lets a following
+// nvfp_dynamic_fp4_quant without the argument checks.  release_next: the (last) kernel of the call lets a following
 // kernel launched with programmatic stream serialization start at once (that kernel must not touch this
 // call's outputs before its own griddepcontrol.wait).  *one_pass tells whether the single cooperative launch ran.
 int dynamic_fp4_quant_launch(void* out_fp4, void* out_sf, float* gs_out, float* alpha_out, uint32_t* scratch,

@@ -728,15 +728,14 @@ extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k,
   uint8_t* a_sf = a_fp4 + round_up(m * (k / 2), 256);
   float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
   float* alpha = gs + 1;
-  // The GEMM may start under the quantizer when the quantizer is the single cooperative launch; every GEMM kernel
-  // then fetches nothing but weights before its griddepcontrol.wait.
-  const bool overlap = dynamic_fp4_quant_is_one_pass(m, k, x_dtype);
-  bool one_pass = false;
+  // The launches are chained with programmatic dependent launch: each kernel lets the next one come up while it
+  // runs, and the next one touches what its predecessor writes only after griddepcontrol.wait (the quantize launch
+  // of the two-launch quantizer loads its tiles first; every GEMM kernel fetches nothing but weights first).
   if (int rc = dynamic_fp4_quant_launch(a_fp4, a_sf, gs, alpha, scratch, x, m, k, x_row_stride, x_dtype, w_global_scale,
-                                        overlap, &one_pass, stream))
+                                        /*release_next=*/true, nullptr, stream))
     return rc;
   return scaled_mm<false>(&d, 1, n, a_fp4, w_fp4, a_sf, w_sf, alpha, m, n, k, out_dtype, stream, bias,
-                          overlap && one_pass);
+                          /*after_producer=*/true);
 }
 
 extern "C" int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void* a, const void* b,

@@ -110,6 +110,8 @@ struct DynamicScale {
   float* alpha_out;       // 1 / (gs_out * gs_other), written when gs_other is given
   uint32_t* status;       // device status word
   int release_next;       // let a programmatically dependent next kernel start while this one runs
+  int wait_prev;          // launched with programmatic stream serialization behind the kernel that writes the
+                          // global scale: the tile is loaded first, the scale read after griddepcontrol.wait
 };
 constexpr uint32_t kErrQuantBarrier = 1u << 8;
 
@@ -119,9 +121,7 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
                  uint8_t* __restrict__ out, uint8_t* __restrict__ sf_out, int m, int n,
                  int num_col_tiles, int num_k_chunks, int mx_rounding, int aligned32, const DynamicScale dyn) {
   static_assert(!DYNAMIC || BLOCK == 16, "only NVFP4 has a global scale");
-  if constexpr (DYNAMIC) {
-    if (dyn.release_next) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  }
+  if (dyn.release_next) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int kThreadsPerRow = kTileCols / 16;                    // 8
   constexpr int kRowsPerPass = kThreads / kThreadsPerRow;           // 32
   constexpr int kPasses = kTileRows / kRowsPerPass;                 // 4: all in flight at once
@@ -143,7 +143,7 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
   const bool col_ok = col < n;
 
   float gs = 1.0f, rcp_gs = 1.0f;
-  if (BLOCK == 16 && !DYNAMIC) {
+  if (BLOCK == 16 && !DYNAMIC && !dyn.wait_prev) {
     gs = gs_ptr ? __ldg(gs_ptr) : 1.0f;
     rcp_gs = rcp_approx_ftz(gs);
   }
@@ -158,6 +158,11 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
     v[p].raw[0] = make_uint4(0u, 0u, 0u, 0u);
     v[p].raw[1] = make_uint4(0u, 0u, 0u, 0u);
     if (col_ok && row < m) load16<T>(v[p], in + (int64_t)row * in_stride + col, aligned32 != 0);
+  }
+  if (BLOCK == 16 && !DYNAMIC && dyn.wait_prev) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // the global scale is written by the kernel before
+    gs = gs_ptr ? *reinterpret_cast<const volatile float*>(gs_ptr) : 1.0f;
+    rcp_gs = rcp_approx_ftz(gs);
   }
   if constexpr (DYNAMIC) {
     __shared__ float warp_max[kThreads / 32];
@@ -275,7 +280,8 @@ __global__ void rcp_kernel(float* __restrict__ out, const float* __restrict__ in
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, uint32_t* scratch, float* gs_out,
-            uint32_t* toggle, const float* gs_other, float* alpha_out) {
+            uint32_t* toggle, const float* gs_other, float* alpha_out, int release_next) {
+  if (release_next) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // self-cleaning mode: scratch holds two (maximum, counter) pairs; *toggle says which one this launch uses
   if (toggle) scratch += 2u * (*reinterpret_cast<volatile uint32_t*>(toggle) & 1u);
   const int64_t vec_per_row = n / VEC;
@@ -341,7 +347,7 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
 template <typename T>
 int launch_amax(float* gs_out, uint32_t* scratch, const void* in, int64_t m, int64_t n, int64_t stride,
                 cudaStream_t stream, bool self_cleaning = false, const float* gs_other = nullptr,
-                float* alpha_out = nullptr) {
+                float* alpha_out = nullptr, bool release_next = false) {
   DeviceInfo info;
   if (int rc = current_device_info(&info)) return rc;
   uint32_t* toggle = self_cleaning ? scratch + 4 : nullptr;
@@ -357,10 +363,10 @@ int launch_amax(float* gs_out, uint32_t* scratch, const void* in, int64_t m, int
   const unsigned grid = (unsigned)std::max<int64_t>(1, ctas);
   if (wide)
     amax_kernel<T, 16><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out, toggle,
-                                                 gs_other, alpha_out);
+                                                 gs_other, alpha_out, release_next ? 1 : 0);
   else
     amax_kernel<T, 8><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), stride, m, n, scratch, gs_out, toggle,
-                                                gs_other, alpha_out);
+                                                gs_other, alpha_out, release_next ? 1 : 0);
   NVFP_CUDA(cudaGetLastError());
   return NVFP_OK;
 }
@@ -384,7 +390,8 @@ int check_16bit_input(const void* in, int64_t m, int64_t n, int64_t stride, int 
 
 template <int BLOCK>
 int launch_quant(void* out_fp4, void* out_sf, const void* in, const float* gs, int64_t m, int64_t n,
-                 int64_t stride, int dtype, int rounding, cudaStream_t stream) {
+                 int64_t stride, int dtype, int rounding, cudaStream_t stream, bool wait_prev = false,
+                 bool release_next = false) {
   if (int rc = check_16bit_input(in, m, n, stride, dtype, BLOCK)) return rc;
   if (m == 0 || n == 0) return NVFP_OK;
   NVFP_REQUIRE(out_fp4 != nullptr && out_sf != nullptr, "output pointer is null");
@@ -397,14 +404,27 @@ int launch_quant(void* out_fp4, void* out_sf, const void* in, const float* gs, i
   NVFP_REQUIRE(m_tiles * col_tiles < (1ll << 31), "too many tiles");
   const dim3 grid((unsigned)(m_tiles * col_tiles));
   const int aligned32 = (reinterpret_cast<uintptr_t>(in) % 32 == 0 && stride % 16 == 0) ? 1 : 0;
+  DynamicScale chain{};
+  chain.release_next = release_next ? 1 : 0;
+  chain.wait_prev = wait_prev ? 1 : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = wait_prev ? 1 : 0;
   if (dtype == NVFP_DTYPE_F16) {
-    quant_fp4_kernel<__half, BLOCK, false><<<grid, kThreads, 0, stream>>>(
-        static_cast<const __half*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
-        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32, DynamicScale{});
+    NVFP_CUDA(cudaLaunchKernelEx(&cfg, quant_fp4_kernel<__half, BLOCK, false>, static_cast<const __half*>(in), stride, gs,
+                                 static_cast<uint8_t*>(out_fp4), static_cast<uint8_t*>(out_sf), (int)m, (int)n,
+                                 (int)col_tiles, (int)k_chunks, rounding, aligned32, chain));
   } else {
-    quant_fp4_kernel<__nv_bfloat16, BLOCK, false><<<grid, kThreads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
-        static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding, aligned32, DynamicScale{});
+    NVFP_CUDA(cudaLaunchKernelEx(&cfg, quant_fp4_kernel<__nv_bfloat16, BLOCK, false>,
+                                 static_cast<const __nv_bfloat16*>(in), stride, gs, static_cast<uint8_t*>(out_fp4),
+                                 static_cast<uint8_t*>(out_sf), (int)m, (int)n, (int)col_tiles, (int)k_chunks, rounding,
+                                 aligned32, chain));
   }
   NVFP_CUDA(cudaGetLastError());
   return NVFP_OK;
@@ -446,10 +466,13 @@ int launch_dynamic_quant(void* out_fp4, void* out_sf, float* gs_out, float* alph
   if (one_pass) *one_pass = fits;
   if (!fits) {
     // too large to keep in registers across the grid: global-scale pass, then quantize pass
-    if (int rc = launch_amax<T>(gs_out, scratch, in, m, n, stride, stream, true, gs_other, gs_other ? alpha_out : nullptr))
+    // The quantize launch comes up under the global-scale launch, loads its tiles and waits for the scale.
+    if (int rc = launch_amax<T>(gs_out, scratch, in, m, n, stride, stream, true, gs_other, gs_other ? alpha_out : nullptr,
+                                /*release_next=*/true))
       return rc;
     return launch_quant<16>(out_fp4, out_sf, in, gs_out, m, n, stride,
-                            std::is_same<T, __half>::value ? NVFP_DTYPE_F16 : NVFP_DTYPE_BF16, 0, stream);
+                            std::is_same<T, __half>::value ? NVFP_DTYPE_F16 : NVFP_DTYPE_BF16, 0, stream,
+                            /*wait_prev=*/true, release_next);
   }
   DynamicScale dyn{scratch, gs_out, gs_other, alpha_out, device_status_word(), release_next ? 1 : 0};
   NVFP_REQUIRE(dyn.status != nullptr, "cannot locate the device status word");
