@@ -139,10 +139,12 @@ __device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t 
 }
 
 // silu(g) * u the way a framework evaluates it on 16-bit tensors: silu in fp32, rounded to T, times u in fp32,
-// rounded to T.
+// rounded to T.  exp and the division are the hardware approximations (a few fp32 ulps): the result is rounded to
+// 8 or 11 bits right away, so it differs from the exact evaluation in about one element in ten thousand, by one
+// ulp of T, and the epilogue of a 256 x 256 tile stays shorter than the tile's MMAs.
 template <typename T>
 __device__ __forceinline__ float silu_mul_16bit(float g, float u) {
-  const float s = g / (1.0f + expf(-g));
+  const float s = __fdividef(g, 1.0f + __expf(-g));
   if constexpr (std::is_same<T, __half>::value) return __half2float(__float2half_rn(s)) * u;
   else return __bfloat162float(__float2bfloat16_rn(s)) * u;
 }
