@@ -7,7 +7,6 @@ from __future__ import annotations
 
 from typing import Callable, Iterable
 
-import torch
 import torch.nn as nn
 
 from .linear import QuantLinear

@@ -2,7 +2,6 @@
 as device buffers, and comparison utilities."""
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from nvfp_kernel_b200 import _capi

@@ -5,7 +5,6 @@ unrounded -- from the CPU oracle (fp64) at small sizes, and on the GPU as an fp3
 of the dequantized operands at large ones (e2m1 x ue4m3 products are exact in fp32), with
 fp64 spot checks.  Tolerance (max rel err <= 1e-2) is spelled out in helpers.check_gemm.
 """
-import numpy as np
 import pytest
 import torch
 

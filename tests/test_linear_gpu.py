@@ -2,7 +2,6 @@
 import pytest
 import torch
 
-from helpers import check_gemm
 from inputs import gemm_inputs
 
 pytestmark = pytest.mark.gpu
