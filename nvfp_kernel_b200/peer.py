@@ -28,8 +28,10 @@ class GatherBuffer:
         self.handle = symm_mem.rendezvous(self.buf, group)
         col_offset = self.rank * n_local * self.buf.element_size()
         ptrs = list(self.handle.buffer_ptrs)
-        # destination list for the GEMM: own buffer first, then the peers; always this rank's columns
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        # destination list for the GEMM: own buffer first, then the peers starting with the next rank, so that at
+        # any moment the ranks (which walk their lists in step) write to different peers instead of all to one;
+        # always this rank's columns
+        order = [(self.rank + i) % self.world for i in range(self.world)]
         self.dst_ptrs = [int(ptrs[r]) + col_offset for r in order]
 
     def barrier(self) -> None:
