@@ -15,6 +15,12 @@
 // The kernel is persistent (one CTA per SM walks the output tiles).  Every wait is
 // bounded; on expiry the CTA records a code in the device status word and leaves
 // through the common exit, which also frees its tensor memory.
+//
+// This file holds that kernel (one CTA per 128 x BN tile: mid-size shapes), the shape dispatch and the C entry
+// points; gemm_fp4_pair_sm100.cuh holds the kernel for large shapes (CTA pairs, cta_group::2, 256 x 256 tiles),
+// gemm_fp4_skinny_sm100.cuh the one for up to 128 activation rows (operands swapped, K split over a cluster).
+// The epilogues can, beyond alpha: add a bias, apply silu(gate) * up on interleaved gate/up columns, quantize
+// the result to NVFP4 (finish_row_chunk), store to several GPUs or add into the owning GPU's buffer.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
