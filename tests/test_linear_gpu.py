@@ -283,3 +283,12 @@ def test_empty_batches():
     ref = QuantLinear(512, 256, bias=True, device="cuda").load_weight(w)
     assert torch.equal(layer(x), ref(x))
     assert nv.device_status() == 0
+
+
+def test_speed_test_tables_run(capsys):
+    """The timing tables of the package (the counterpart of the reference's speed_test.py) still run end to end."""
+    from nvfp_kernel_b200 import speed_test
+    speed_test.decode(1)
+    speed_test.quant(1)
+    out = capsys.readouterr().out
+    assert out.count("\n") >= 12 + 5 + 4 and "14336" in out and "28672" in out
