@@ -19,6 +19,9 @@
 //     own (drained) shared memory, then one bulk copy per warp and owner, shared memory to shared memory inside
 //     the cluster, completion on an mbarrier of the owner.  An owner adds what it receives to its own partial,
 //     scales by alpha, adds the bias and stores its tokens.  No global scratch, no second kernel, no atomics.
+//   * the owner's epilogue can also apply the gated activation (a warp's 32 weight rows are 16 gate rows and their
+//     16 up rows: lane l reads its up value from lane l + 16) and quantize the result to NVFP4 from the staging
+//     tile, as the other two kernels do from registers.
 #pragma once
 
 constexpr int kSkinnyMaxTokens = 128;
@@ -326,6 +329,9 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
     // staging tile [16 tokens][128 columns] in the drained stage area, behind the blocks staged for sending
     OutT* out_tile = reinterpret_cast<OutT*>(smem + sp.out_tile_offset);
     const int tok0 = (int)rank * sp.tok;
+    const bool fused = p.act != 0 || p.out_gs != nullptr;            // 16-bit value types only
+    const int tile_w = p.act ? 64 : 128;                              // output columns this tile of 128 weight rows yields
+    const float out_gs = p.out_gs ? __ldg(p.out_gs) : 1.0f, rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
     for (int c = 0; c < sp.tok; c += 16) {
       uint32_t r[16];
       if (have_acc) {
@@ -351,6 +357,60 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       // Transpose through shared memory: this thread holds 16 tokens of one output column, the output rows are
       // tokens.  Writing them as they are costs 16 two-byte stores per thread; staged, a thread stores 16 bytes.
       if (c != 0) named_barrier_sync(1, 128);            // the previous chunk has left the staging tile
+      if constexpr (sizeof(OutT) == 2) {
+        if (fused) {
+          // Gated activation: the 32 weight rows of this warp are 16 gate rows and their 16 up rows, so lane l < 16
+          // finds its up value in lane l + 16 and the warp yields 16 output columns.  Then (or instead) the staged
+          // tile is quantized to NVFP4 block by block, each block by one thread, with the quantizer's own function.
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            float v = fmaf(part[t], alpha, bias);
+            if constexpr (std::is_same<OutT, __half>::value) v = __half2float(__float2half_rn(v));
+            else v = __bfloat162float(__float2bfloat16_rn(v));
+            if (p.act) {
+              const float up = __shfl_down_sync(0xffffffffu, v, 16);
+              v = silu_mul_16bit<OutT>(v, up);
+            }
+            if (!p.act || lane < 16) {
+              const int oc = p.act ? q * 16 + lane : wrow;
+              if constexpr (std::is_same<OutT, __half>::value) out_tile[t * tile_w + oc] = __float2half_rn(v);
+              else out_tile[t * tile_w + oc] = __float2bfloat16_rn(v);
+            }
+          }
+          named_barrier_sync(1, 128);
+          const int out_cols = p.act ? p.n / 2 : p.n;
+          if (p.out_gs == nullptr) {
+            const int segs = tile_w / 8;                   // 16-byte segments per token row of the tile
+            for (int sidx = (int)threadIdx.x - 64; sidx < 16 * segs; sidx += 128) {
+              const int t = sidx / segs, seg = sidx % segs;
+              const int token = tok0 + c + t, col = n_tile * tile_w + seg * 8;
+              if (token < p.m && col < out_cols)
+                *reinterpret_cast<uint4*>(d + (int64_t)token * out_cols + col) = *reinterpret_cast<const uint4*>(out_tile + t * tile_w + seg * 8);
+            }
+          } else {
+            using V2 = typename Vec2<OutT>::type;
+            const int nblk = tile_w / 16, k_tiles = (out_cols + 63) / 64;
+            uint8_t* out_fp4 = static_cast<uint8_t*>(p.d);
+            for (int e = (int)threadIdx.x - 64; e < 16 * nblk; e += 128) {
+              const int t = e / nblk, b = e % nblk;
+              const int token = tok0 + c + t, ocol = n_tile * tile_w + b * 16;
+              const uint4* src = reinterpret_cast<const uint4*>(out_tile + t * tile_w + b * 16);
+              const uint4 lo = src[0], hi = src[1];
+              const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+              V2 h2[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) h2[i] = *reinterpret_cast<const V2*>(&w[i]);
+              uint8_t sf;
+              const uint2 qv = nvfp4_quantize_block<OutT>(h2, out_gs, rcp_out_gs, rcp6, sf);
+              if (token < p.m && ocol < out_cols)
+                *reinterpret_cast<uint2*>(out_fp4 + (int64_t)token * (out_cols / 2) + ocol / 2) = qv;
+              if (ocol / 64 < k_tiles)      // token < 128: rows [m, nt) of the one 128-row scale tile get zero scales
+                p.out_sf[(int64_t)(ocol / 64) * 512 + (token % 32) * 16 + (token / 32) * 4 + (ocol % 64) / 16] = token < p.m ? sf : (uint8_t)0;
+            }
+          }
+          continue;
+        }
+      }
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
         const float v = fmaf(part[t], alpha, bias);
@@ -366,6 +426,18 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
         const int token = tok0 + c + t, col = n_tile * 128 + seg * kSegElems;
         if (token < p.m && col < p.n)
           *reinterpret_cast<uint4*>(d + (int64_t)token * p.n + col) = *reinterpret_cast<const uint4*>(out_tile + t * 128 + seg * kSegElems);
+      }
+    }
+    // NVFP4 output: the scale rows between the padded token count and 128 are zero in the quantizer's output too
+    if constexpr (sizeof(OutT) == 2) {
+      if (fused && p.out_gs != nullptr && rank == 0) {
+        const int out_cols = p.act ? p.n / 2 : p.n;
+        const int nblk = tile_w / 16, k_tiles = (out_cols + 63) / 64;
+        for (int e = (int)threadIdx.x - 64; e < (128 - sp.nt) * nblk; e += 128) {
+          const int row = sp.nt + e / nblk, ocol = n_tile * tile_w + (e % nblk) * 16;
+          if (ocol / 64 < k_tiles)
+            p.out_sf[(int64_t)(ocol / 64) * 512 + (row % 32) * 16 + (row / 32) * 4 + (ocol % 64) / 16] = (uint8_t)0;
+        }
       }
     }
   }

@@ -595,7 +595,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.status = device_status_word();
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
   // Few activation rows (decode): weights are streamed once; swap the operands and split K over a cluster.
-  if (n_out == 1 && ld == n && !fused && skinny_preferred(m, n, info.sm_count)) {
+  if (n_out == 1 && ld == n && skinny_preferred(m, n, info.sm_count)) {
     switch (out_dtype) {
       case NVFP_DTYPE_BF16: return launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream, after_producer);
       case NVFP_DTYPE_F16: return launch_skinny<MX, __half>(p, a, b, info.sm_count, stream, after_producer);

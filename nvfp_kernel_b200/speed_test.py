@@ -52,6 +52,20 @@ def time_us(fn, repeats: int, flush: bool = True) -> float:
     return statistics.median(times)
 
 
+def _graphed(fn):
+    """fn captured in a CUDA graph; returns the replay callable (decode-sized work is launch-bound otherwise)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph.replay
+
+
 def sweep(batch_size: int, repeats: int):
     print(f"{'Size (K=N)':<10} {'BF16 (us)':<12} {'FP4 (us)':<12} {'Speedup':<10} {'BF16 TFLOPS':<14} {'FP4 TFLOPS':<12}")
     print("-" * 74)
@@ -161,12 +175,14 @@ def fp4out(repeats: int):
 
 def mlp(repeats: int):
     """Gated MLP (Llama shapes) from a bf16 activation to a bf16 result: every step a separate kernel, against the
-    gate/up GEMM that applies silu(gate) * up and quantizes for the down projection in its epilogue."""
+    gate/up GEMM that applies silu(gate) * up and quantizes for the down projection in its epilogue.  Rows of 128
+    tokens or fewer are timed as CUDA graph replays."""
     import torch.nn.functional as F
     print(f"{'model':<12} {'M':<6} {'hidden':<7} {'inter':<7} {'separate (us)':<15} {'fused epilogue (us)':<21} {'TFLOP/s fused':<14}")
     print("-" * 86)
     for name, m, hidden, inter in (("llama-3-8b", 8192, 4096, 14336), ("llama-3-70b", 8192, 8192, 28672),
-                                   ("llama-3-8b", 512, 4096, 14336)):
+                                   ("llama-3-8b", 512, 4096, 14336), ("llama-3-8b", 128, 4096, 14336),
+                                   ("llama-3-8b", 16, 4096, 14336), ("llama-3-70b", 16, 8192, 28672)):
         x = torch.randn(m, hidden, dtype=torch.bfloat16, device="cuda")
         w_gu = (torch.randn(2 * inter, hidden, device="cuda") * 0.02).to(torch.bfloat16)   # already interleaved
         w_d = (torch.randn(hidden, inter, device="cuda") * 0.02).to(torch.bfloat16)
@@ -192,6 +208,8 @@ def mlp(repeats: int):
             h_fp4, h_sf = ops.scaled_fp4_mm_silu_mul(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, torch.bfloat16, out_global_scale=gh)
             return ops.cutlass_scaled_fp4_mm(h_fp4, d_fp4, h_sf, d_sf, alpha2, torch.bfloat16)
 
+        if m <= 128:
+            separate, fused = _graphed(separate), _graphed(fused)
         t_sep = time_us(separate, repeats)
         t_fused = time_us(fused, repeats)
         flops = 2.0 * m * hidden * inter * 3

@@ -149,12 +149,14 @@ def test_bias_added_in_the_epilogue(m, n, k, mx):
 
 
 @pytest.mark.parametrize("m,n,k", [(8, 256, 512), (128, 96, 512), (300, 4128, 1024), (1000, 512, 2048), (512, 4096, 1024),
-                                   (2048, 4096, 512), (1100, 4000, 256)])
+                                   (2048, 4096, 512), (1100, 4000, 256), (1, 4096, 8192), (17, 160, 9216),
+                                   (48, 4096, 4096), (100, 416, 2048), (128, 4128, 1024), (33, 28672, 512)])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 def test_result_written_as_nvfp4_equals_gemm_then_quantizer(m, n, k, dt):
     """nvfp_scaled_fp4_mm_fp4out (the epilogue quantizes alpha*acc+bias, rounded to fp16/bf16, with a given global
     scale) against the two separate calls: same packed bytes, same scale tensor including its zero padding.  Shapes
-    reach the 128-row-tile kernel and the CTA-pair kernel, with ragged rows, ragged 64-column scale tiles, a scale
+    reach the 128-row-tile kernel, the CTA-pair kernel and the few-rows kernel (one and several owners of the split-K
+    sum), with ragged rows, ragged 64-column scale tiles, a scale
     that fits and one that saturates."""
     from helpers import capi_mm_fp4out
     a, w = gemm_inputs(m, n, k, seed=m + n, w_std=0.05)
