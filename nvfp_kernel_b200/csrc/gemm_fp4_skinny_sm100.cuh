@@ -10,9 +10,12 @@
 //     operand, so every weight row contributes 512 (256) contiguous bytes per stage, and the issuer pays one
 //     barrier round trip per 16 (8) MMAs; all scale copies of a stage are queued before its MMAs (a barrier
 //     per box measured 60 % slower per stage);
-//   * the epilogue warps, idle during the main loop, prefetch this CTA's whole slab of weights into L2
-//     with plain prefetch instructions (the ring only keeps two or three stages in flight, too few to cover DRAM
-//     latency; a prefetch through the TMA unit halved the load rate);
+//   * with more weight tiles than SMs (and at most 32 tokens) the kernel is persistent: every CTA takes the same
+//     number of tiles, its ring runs on across tile boundaries and the MMAs alternate between two accumulators, so
+//     one tile's epilogue and the next tile's first loads overlap (N = 57344, K = 8192, 16 tokens: 50 us against
+//     69 us as three and a bit waves of one-tile CTAs).  L2 prefetches of the weights ahead of the ring, by the
+//     idle epilogue warps or rolling in the producer warp, measured neutral on one-tile shapes and 10 % slower here,
+//     and a prefetch through the TMA unit halved the load rate: there are none;
 //   * K is split over a cluster of CTAs; each computes a partial [128 weight rows x NT tokens] in tensor
 //     memory.  The tokens are divided among "owners" -- the leader alone, or every rank when each can get a
 //     multiple of 16 tokens -- and every rank sends each owner that owner's tokens of its partial: staged in its
@@ -53,7 +56,6 @@ struct SkinnyParams {
   int stages_per_rank;  // stages each rank of a cluster processes
   int num_stages;       // pipeline depth
   uint32_t stage_bytes;
-  const void* w;           // weights [n, k/2], for the L2 prefetch
   int after_producer;      // launched with programmatic stream serialization behind the kernel that writes the
                            // activation operand, its scales and alpha: weights may be fetched before that kernel
                            // has finished, everything it writes only after griddepcontrol.wait
@@ -63,6 +65,11 @@ struct SkinnyParams {
   uint32_t out_tile_offset;
   uint32_t recv_offset;
   int recv_behind_ring;
+  uint32_t bars_offset;    // barriers, behind everything else
+  // More weight tiles than SMs (then split == 1): a CTA works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+  // with the ring running on across tile boundaries and two accumulators, so that one tile's epilogue and the next
+  // tile's first loads cost no time of their own.  The staging tile then lies behind the ring, which is never drained.
+  int persistent;
 };
 
 // Partial sums travel as [128 weight rows][tok + 4] fp32 per (sender, owner) pair.  The 4 floats of padding make the
@@ -87,14 +94,13 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const GemmParams& p = sp.g;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // [stages ...][receive buffer, when it is behind the ring][barriers]
-  const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
+  // [stages ...][receive buffer, when it is behind the ring | staging tile, when persistent][barriers]
   const uint32_t block_bytes = skinny_block_bytes(sp.tok);                  // one sender's tokens for one owner
   const uint32_t recv_bytes = (uint32_t)(sp.split - 1) * block_bytes;
   const uint32_t ld = skinny_block_ld(sp.tok);
   float* recv_buf = reinterpret_cast<float*>(smem + sp.recv_offset);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes + (sp.recv_behind_ring ? recv_bytes : 0u));
-  const int kFull = 0, kEmpty = sp.num_stages, kAccFull = 2 * sp.num_stages, kReduce = kAccFull + 1;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + sp.bars_offset);
+  const int kFull = 0, kEmpty = sp.num_stages, kAccFull = 2 * sp.num_stages, kAccEmpty = kAccFull + 2, kReduce = kAccEmpty + 2;
   const int kNumBars = kReduce + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -102,7 +108,9 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = sp.split > 1 ? cluster_ctarank() : 0u;
-  const int n_tile = sp.split > 1 ? (int)cluster_id_x() : (int)blockIdx.x;
+  const int tile0 = sp.split > 1 ? (int)cluster_id_x() : (int)blockIdx.x;
+  const int tile_stride = sp.persistent ? (int)gridDim.x : 0;
+  const int my_tiles = sp.persistent ? (p.sfb_row_tiles - tile0 + tile_stride - 1) / tile_stride : 1;
   const bool owner = (int)rank < sp.owners;
   const uint32_t stage_base = smem_u32(smem);
   auto bar = [&](int i) { return smem_u32(bars + i); };
@@ -115,14 +123,18 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const int ks_end = min(ks_begin + sp.stages_per_rank, total_stages);
   const int my_stages = ks_end - ks_begin;
   const int k_boxes_total = (p.k + kStageK - 1) / kStageK;
-  const uint8_t* sfw_tile = p.sfb + (int64_t)n_tile * p.sf_k_chunks * 512;
+  // Stages are counted through all of this CTA's tiles: stage g belongs to tile g / my_stages.
+  const int total_g = my_tiles * my_stages;
+  constexpr uint32_t kAccBufCols = 64;            // second accumulator (persistent: at most 32 tokens)
 
-  // Loads of local stage i into ring slot i % num_stages, all reported to the slot's one barrier.  `what` selects
+  // Loads of stage g into ring slot g % num_stages, all reported to the slot's one barrier.  `what` selects
   // the weight side (which also arms the barrier with the bytes of both sides), the activation side, or both.
   constexpr int kWeights = 1, kActivations = 2;
-  auto load_stage = [&](int i, int what) {
-    const int ks = ks_begin + i;
-    const uint32_t s = (uint32_t)i % sp.num_stages;
+  auto load_stage = [&](int g, int what) {
+    const int n_tile = tile0 + (g / my_stages) * tile_stride;
+    const uint8_t* sfw_tile = p.sfb + (int64_t)n_tile * p.sf_k_chunks * 512;
+    const int ks = ks_begin + g % my_stages;
+    const uint32_t s = (uint32_t)g % sp.num_stages;
     const uint32_t st = stage_base + s * sp.stage_bytes;
     const int boxes = min(BOXES, k_boxes_total - ks * BOXES);
     const int chunk0 = ks * C::kChunksPerStage;
@@ -145,7 +157,10 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
     // the CTA (tensor memory allocation, the other warps) is ready.
     if (elect_one()) {
       for (int i = 0; i < kAccFull; ++i) mbar_init(bar(i), 1);
-      mbar_init(bar(kAccFull), 1);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(bar(kAccFull + i), 1);
+        mbar_init(bar(kAccEmpty + i), 4);          // one arrival per epilogue warp
+      }
       mbar_init(bar(kReduce), 1);
       *abort_flag = 0;
       fence_mbar_init();
@@ -153,7 +168,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       if (sp.split > 1 && owner) mbar_arrive_expect_tx(bar(kReduce), recv_bytes);
       prefetch_tensormap(&tmap_w);
       prefetch_tensormap(&tmap_x);
-      const int first = min(my_stages, sp.num_stages);
+      const int first = min(total_g, sp.num_stages);
       if (sp.after_producer) {
         // the weights do not depend on the kernel before this one: fetch them while it still runs
         for (int i = 0; i < first; ++i) load_stage(i, kWeights);
@@ -178,14 +193,14 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   if (warp == 0) {
     // ------------------------------------------------------------ producer ---
     if (elect_one()) {
-      for (int i = sp.num_stages; i < my_stages; ++i) {
-        const uint32_t s = (uint32_t)i % sp.num_stages, ph = ((uint32_t)i / sp.num_stages) & 1u;
+      for (int g = sp.num_stages; g < total_g; ++g) {
+        const uint32_t s = (uint32_t)g % sp.num_stages, ph = ((uint32_t)g / sp.num_stages) & 1u;
         if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicOr(p.status, kErrProducer);
           break;
         }
-        load_stage(i, kWeights | kActivations);
+        load_stage(g, kWeights | kActivations);
       }
     }
     __syncwarp();
@@ -195,11 +210,22 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       const uint32_t sfw_tmem = tmem_base + C::kSfwCol, sfx_tmem = tmem_base + C::kSfxCol;
       const uint32_t idesc0 = make_idesc_fp4_block_scaled(128, sp.nt, MX, 0u, 0u);
       const uint32_t idesc1 = MX ? make_idesc_fp4_block_scaled(128, sp.nt, true, 2u, 2u) : idesc0;
-      for (int i = 0; i < my_stages; ++i) {
+      for (int g = 0; g < total_g; ++g) {
+        const int j = g / my_stages, i = g % my_stages;
         const int ks = ks_begin + i;
-        const uint32_t s = (uint32_t)i % sp.num_stages, ph = ((uint32_t)i / sp.num_stages) & 1u;
+        const uint32_t s = (uint32_t)g % sp.num_stages, ph = ((uint32_t)g / sp.num_stages) & 1u;
         const uint32_t st = stage_base + s * sp.stage_bytes;
         const int boxes = min(BOXES, k_boxes_total - ks * BOXES);
+        const uint32_t acc = tmem_base + (uint32_t)(j & 1) * kAccBufCols;
+        if (i == 0 && j >= 2) {
+          // the epilogue has read this accumulator's previous tile
+          if (!mbar_wait_bounded(bar(kAccEmpty + (j & 1)), (uint32_t)((j >> 1) - 1) & 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicOr(p.status, kErrIssuer);
+            break;
+          }
+          tc_fence_after_sync();
+        }
         if (!mbar_wait_bounded(bar(kFull + (int)s), ph, abort_flag)) {
           *abort_flag = 1;
           atomicOr(p.status, kErrIssuer);
@@ -225,15 +251,15 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
             const int c = j / C::kMmasPerChunk;
             const uint32_t accumulate = (i | b | j) != 0 ? 1u : 0u;
             if (MX)
-              tc_mma_mxf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), (j & 1) ? idesc1 : idesc0,
+              tc_mma_mxf4(acc, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), (j & 1) ? idesc1 : idesc0,
                           sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
             else
-              tc_mma_nvf4(tmem_base, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), idesc0,
+              tc_mma_nvf4(acc, w_desc + (uint64_t)(2 * j), x_desc + (uint64_t)(2 * j), idesc0,
                           sfw_tmem + bcol + 4 * c, sfx_tmem + bcol + 4 * c, accumulate);
           }
         }
         tc_commit(bar(kEmpty + s));
-        if (i == my_stages - 1) tc_commit(bar(kAccFull));
+        if (i == my_stages - 1) tc_commit(bar(kAccFull + (j & 1)));
       }
     }
     __syncwarp();
@@ -243,35 +269,31 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const bool epi = warp >= 2;
   const int q = warp & 3;
   const int wrow = q * 32 + lane;                 // weight row within the tile = accumulator lane
-  bool have_acc = false;
-  float alpha = 1.0f, bias = 0.0f;
+  float alpha = 1.0f;
   if (epi) {
-    // Rows of this tile beyond the ring's first fill, one 128-byte line per instruction; thread = weight row.
-    const int row = n_tile * 128 + wrow;
-    if (row < p.n) {
-      const uint8_t* w_row = static_cast<const uint8_t*>(sp.w) + (int64_t)row * (p.k / 2);
-      const int byte_begin = (ks_begin + min(my_stages, sp.num_stages)) * (C::kStageElems / 2);
-      const int byte_end = min(ks_end * (C::kStageElems / 2), p.k / 2);
-      for (int off = byte_begin; off < byte_end; off += 128) prefetch_l2(w_row + off);
-    }
     if (sp.after_producer) griddep_wait();         // alpha comes from the kernel before this one
     if (owner && p.alpha) alpha = *reinterpret_cast<const volatile float*>(p.alpha);
-    if (owner && p.bias && row < p.n) {
-      if constexpr (sizeof(OutT) == 4) bias = __ldg(static_cast<const float*>(p.bias) + row);
-      else if constexpr (std::is_same<OutT, __half>::value) bias = __half2float(static_cast<const __half*>(p.bias)[row]);
-      else bias = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row]);
-    }
+  }
+  bool have_peers = true;
+  for (int j = 0; j < my_tiles; ++j) {             // one pass unless persistent
+  const int n_tile = tile0 + j * tile_stride;
+  bool have_acc = false;
+  float bias = 0.0f;
+  if (epi && owner && p.bias && n_tile * 128 + wrow < p.n) {
+    const int row = n_tile * 128 + wrow;
+    if constexpr (sizeof(OutT) == 4) bias = __ldg(static_cast<const float*>(p.bias) + row);
+    else if constexpr (std::is_same<OutT, __half>::value) bias = __half2float(static_cast<const __half*>(p.bias)[row]);
+    else bias = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row]);
   }
   if (epi && my_stages > 0) {
-    have_acc = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull), 0, abort_flag));
+    have_acc = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull + (j & 1)), (uint32_t)(j >> 1) & 1u, abort_flag));
     if (!have_acc) {
       *abort_flag = 1;
       if (lane == 0) atomicOr(p.status, kErrEpilogue);
     }
     tc_fence_after_sync();
   }
-  const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
-  bool have_peers = true;
+  const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(j & 1) * kAccBufCols;
   if (sp.split > 1) {
     // A rank whose receive buffer lies in its stage area is ready only now: its epilogue warps arrive after its
     // last MMA has completed (all TMA writes landed, all MMA reads done).
@@ -326,7 +348,8 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   }
   if (epi && owner) {
     OutT* d = static_cast<OutT*>(p.d);
-    // staging tile [16 tokens][128 columns] in the drained stage area, behind the blocks staged for sending
+    // staging tile [16 tokens][128 columns]: in the drained stage area, behind the blocks staged for sending, or
+    // (persistent) behind the ring
     OutT* out_tile = reinterpret_cast<OutT*>(smem + sp.out_tile_offset);
     const int tok0 = (int)rank * sp.tok;
     const bool fused = p.act != 0 || p.out_gs != nullptr;            // 16-bit value types only
@@ -356,7 +379,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       }
       // Transpose through shared memory: this thread holds 16 tokens of one output column, the output rows are
       // tokens.  Writing them as they are costs 16 two-byte stores per thread; staged, a thread stores 16 bytes.
-      if (c != 0) named_barrier_sync(1, 128);            // the previous chunk has left the staging tile
+      if (c != 0 || j != 0) named_barrier_sync(1, 128);  // the previous chunk has left the staging tile
       if constexpr (sizeof(OutT) == 2) {
         if (fused) {
           // Gated activation: the 32 weight rows of this warp are 16 gate rows and their 16 up rows, so lane l < 16
@@ -441,6 +464,13 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
       }
     }
   }
+  if (epi && sp.persistent) {
+    // this tile's accumulator is in registers or stored: the issuer may overwrite it two tiles on
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(kAccEmpty + (j & 1)));
+  }
+  }  // tiles
   if (sp.split > 1) cluster_wait();
   tc_fence_before_sync();
   __syncthreads();
@@ -470,12 +500,11 @@ inline bool skinny_preferred(int64_t m, int64_t n, int sm_count) {
 
 template <bool MX, typename OutT, int BOXES>
 int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
-                        bool after_producer, int max_ring_stages = 1 << 30) {
+                        bool after_producer) {
   using C = SkinnyCfg<MX, BOXES>;
   constexpr int kMaxTokens = BOXES == 4 ? 64 : 128;
   SkinnyParams sp{};
   sp.g = base;
-  sp.w = b;
   sp.after_producer = after_producer ? 1 : 0;
   const int m = base.m, n = base.n, k = base.k;
   const int n_tiles = (int)ceil_div(n, 128);
@@ -483,7 +512,28 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
   const uint32_t budget = (uint32_t)kSmemLimit - 2048u;
   int split = skinny_split(n_tiles, k, sm_count);
   uint32_t smem_bytes = 0;
-  for (;; split /= 2) {
+  unsigned grid = 0;
+  // More tiles than SMs: every CTA takes the same number of tiles (448 tiles on 148 SMs: 112 CTAs with 4 each, not
+  // three full waves and a fourth of 4 CTAs) and streams through them without draining its ring in between.
+  const bool persistent = m <= 32 && n_tiles > sm_count;
+  if (persistent) {
+    const int rounds = (int)ceil_div(n_tiles, sm_count);
+    grid = (unsigned)ceil_div(n_tiles, rounds);
+    sp.persistent = 1;
+    sp.nt = sp.tok = (int)round_up(m, 16);
+    sp.split = sp.owners = split = 1;
+    sp.stage_bytes = (uint32_t)round_up(BOXES * (C::kWBoxBytes + (uint32_t)sp.nt * kStageKBytes) + 2 * C::kSfBytes, 1024);
+    const int max_stages = (int)((budget - kSkinnyOutTileBytes) / sp.stage_bytes);
+    NVFP_REQUIRE(max_stages >= 1, "internal: a stage of %u bytes does not fit shared memory", sp.stage_bytes);
+    sp.stages_per_rank = total_stages;
+    sp.num_stages = std::max(1, std::min(total_stages * rounds, max_stages));
+    const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
+    sp.out_tile_offset = sp.recv_offset = ring_bytes;
+    sp.recv_behind_ring = 1;
+    sp.bars_offset = ring_bytes + kSkinnyOutTileBytes;
+    smem_bytes = sp.bars_offset + 2048;
+  }
+  for (; !persistent; split /= 2) {
     // Every rank an owner when each can have a multiple of 16 tokens without padding the MMA beyond its limit and
     // there is more than one chunk of tokens to share out; else the leader alone, which is only worth it for one
     // chunk of tokens (32 and more tokens into one CTA cost more than the split saves).
@@ -504,7 +554,6 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
     NVFP_REQUIRE(max_stages >= 1, "internal: a stage of %u bytes does not fit shared memory", sp.stage_bytes);
     sp.stages_per_rank = (int)ceil_div(total_stages, split);
     sp.num_stages = std::max(1, std::min(sp.stages_per_rank, max_stages));
-    sp.num_stages = std::min(sp.num_stages, max_ring_stages);
     const uint32_t ring_bytes = (uint32_t)sp.num_stages * sp.stage_bytes;
     const uint32_t block_bytes = skinny_block_bytes(sp.tok);
     const uint32_t staging_bytes = split > 1 ? (uint32_t)owners * block_bytes : 0u;
@@ -513,12 +562,14 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
     if (ring_bytes + recv_bytes <= budget && staging_bytes + kSkinnyOutTileBytes <= ring_bytes) {
       sp.recv_behind_ring = 1;
       sp.recv_offset = ring_bytes;
+      sp.bars_offset = ring_bytes + recv_bytes;
       smem_bytes = ring_bytes + recv_bytes + 2048;
       break;
     }
     if (staging_bytes + kSkinnyOutTileBytes + recv_bytes <= ring_bytes) {
       sp.recv_behind_ring = 0;
       sp.recv_offset = staging_bytes + kSkinnyOutTileBytes;
+      sp.bars_offset = ring_bytes;
       smem_bytes = ring_bytes + 2048;
       break;
     }
@@ -530,7 +581,7 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
   auto kernel = fp4_gemm_skinny_kernel<MX, OutT, BOXES>;
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(n_tiles * sp.split));
+  cfg.gridDim = dim3(persistent ? grid : (unsigned)(n_tiles * sp.split));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
@@ -559,12 +610,6 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
 template <bool MX, typename OutT>
 int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
                   bool after_producer = false) {
-  // More weight tiles than SMs but at most two per SM, short K: with two 512-element stages a CTA needs under half
-  // of an SM's shared memory, so all CTAs are resident at once and share the DRAM bandwidth instead of running as one
-  // full wave and a partial one (N = 28672, K = 4096, up to 32 tokens: 24.5 against 26.7 us; at K = 8192 it loses).
-  const int64_t n_tiles = ceil_div(base.n, 128);
-  if (base.m <= 32 && n_tiles > sm_count && n_tiles <= 2 * sm_count && base.k <= 4096)
-    return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer, 2);
   if (base.m <= 64) return launch_skinny_boxes<MX, OutT, 4>(base, a, b, sm_count, stream, after_producer);
   return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer);
 }

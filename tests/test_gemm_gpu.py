@@ -102,13 +102,15 @@ def test_edge_shapes_vs_cpu_oracle(m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(1, 96, 8192), (17, 128, 8448), (48, 4096, 14336), (64, 160, 9216),
                                    (8, 1024, 32768), (33, 256, 4608), (64, 19072, 1024), (2, 32, 64),
-                                   (128, 1024, 8192), (100, 4096, 14336), (65, 160, 4352), (96, 6144, 512)])
+                                   (128, 1024, 8192), (100, 4096, 14336), (65, 160, 4352), (96, 6144, 512),
+                                   (5, 19040, 1088), (32, 20000, 4160), (17, 38016, 512), (16, 57344, 2048)])
 @pytest.mark.parametrize("mx", [False, True])
 def test_split_k_cluster_path_for_few_rows_and_long_k(m, n, k, mx):
     """Shapes the dispatcher sends to the swap-operands / cluster split-K kernel: clusters of 1, 2, 4 and 8, the
     leader reducing alone (one chunk of tokens) and every rank reducing its share of the tokens, receive buffers
     behind the ring and in the drained stage area, ragged last stages, more weight tiles than SMs, 1024- and
-    512-element stages (up to 64 / 128 tokens)."""
+    512-element stages (up to 64 / 128 tokens), and the persistent form (up to 32 tokens, more tiles than SMs: 2 to 4
+    tiles per CTA, the last round ragged)."""
     a, w = gemm_inputs(m, n, k, seed=m + k, w_std=0.05)
     if mx:
         a_fp4, a_sf = capi_mx_quant(a.cuda())
@@ -122,7 +124,7 @@ def test_split_k_cluster_path_for_few_rows_and_long_k(m, n, k, mx):
 
 
 @pytest.mark.parametrize("m,n,k", [(8, 4096, 4096), (48, 160, 9216), (100, 384, 1024), (128, 96, 512),
-                                   (512, 4096, 1024), (300, 4128, 2048)])
+                                   (512, 4096, 1024), (300, 4128, 2048), (9, 20000, 512)])
 @pytest.mark.parametrize("mx", [False, True])
 def test_bias_added_in_the_epilogue(m, n, k, mx):
     """nvfp_scaled_fp4_mm_bias on shapes that reach each of the three kernels (few rows, 128-row tiles, CTA pairs):
@@ -150,7 +152,8 @@ def test_bias_added_in_the_epilogue(m, n, k, mx):
 
 @pytest.mark.parametrize("m,n,k", [(8, 256, 512), (128, 96, 512), (300, 4128, 1024), (1000, 512, 2048), (512, 4096, 1024),
                                    (2048, 4096, 512), (1100, 4000, 256), (1, 4096, 8192), (17, 160, 9216),
-                                   (48, 4096, 4096), (100, 416, 2048), (128, 4128, 1024), (33, 28672, 512)])
+                                   (48, 4096, 4096), (100, 416, 2048), (128, 4128, 1024), (33, 28672, 512), (16, 24064, 1024),
+                                   (3, 19040, 512)])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 def test_result_written_as_nvfp4_equals_gemm_then_quantizer(m, n, k, dt):
     """nvfp_scaled_fp4_mm_fp4out (the epilogue quantizes alpha*acc+bias, rounded to fp16/bf16, with a given global

@@ -190,7 +190,7 @@ def test_two_layers_chained_through_nvfp4_output():
 
 @pytest.mark.parametrize("m,k,inter,hidden", [(300, 1024, 1440, 512), (2048, 1024, 2048, 1024), (40, 512, 256, 256),
                                               (1, 4096, 1024, 512), (16, 8192, 2048, 256), (40, 512, 1440, 512),
-                                              (100, 2048, 1440, 256), (128, 1024, 4096, 128)])
+                                              (100, 2048, 1440, 256), (128, 1024, 4096, 128), (16, 1024, 12288, 256), (7, 512, 9536, 128)])
 def test_gated_mlp_with_activation_and_quantizer_in_the_epilogue(m, k, inter, hidden):
     """x -> gate/up GEMM with silu(gate)*up (and the NVFP4 quantization of the result) in its epilogue -> down GEMM,
     against the same chain with the bf16 gate/up product, torch's silu * mul and the quantizer kernel in between."""
