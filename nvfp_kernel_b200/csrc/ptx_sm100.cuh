@@ -302,10 +302,6 @@ __device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t 
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst_cluster), "r"(src_smem), "r"(bytes), "r"(cluster_bar) : "memory");
 }
-// The 128-byte line holding src into L2; nothing to wait for.
-__device__ __forceinline__ void prefetch_l2(const void* src) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(src) : "memory");
-}
 // shared::cta address -> shared::cluster address of the same offset in CTA `rank`.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;

@@ -86,7 +86,7 @@ def decode(repeats: int):
     print(f"{'M':<5} {'K':<7} {'N':<7} {'GEMM (us)':<11} {'GB/s':<9} {'forward (us)':<13} {'graph replay (us)':<13}")
     print("-" * 76)
     for m in (1, 16, 128):
-        for k, n in ((4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)):
+        for k, n in ((4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096), (8192, 57344)):
             a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
             w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
             layer = QuantLinear(k, n, device="cuda").load_weight(w)
