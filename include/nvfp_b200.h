@@ -162,6 +162,31 @@ int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k, int64_t x_
                         const void* bias, void* workspace, uint32_t* scratch, int out_dtype, void* stream);
 
 /*
+ * One call for a gated MLP with NVFP4 weights, y = down(silu(gate(x)) * up(x)): the quantizer of x, the gate/up GEMM
+ * with the activation and the NVFP4 quantization of its result in the epilogue (nvfp_scaled_fp4_mm_silu_mul), and
+ * the down GEMM, chained with programmatic dependent launch: each GEMM comes up while the kernel before it still
+ * runs, streams its WEIGHTS meanwhile and touches what that kernel writes only after it has finished.  Same bytes as
+ * the three separate calls.  No counterpart in the reference (its FP4GemmWithOnlineActivation, speed_test.py:36-50,
+ * is one layer).
+ *   x             device, [m, hidden] fp16 / bf16, row stride x_row_stride elements, 16-byte aligned
+ *   gate_up_fp4/sf  [2 * inter, hidden / 2] and swizzled scales: gate and up rows interleaved in groups of 16,
+ *                 quantized as one tensor with global scale gate_up_global_scale
+ *   down_fp4/sf   [n_out, inter / 2] and swizzled scales
+ *   act_global_scale  device fp32, the (calibrated) global scale of silu(gate) * up
+ *   down_alpha    device fp32, 1 / (act_global_scale * global scale of the down weight)
+ *   y             device, [m, n_out] of out_dtype (fp16 or bf16, also the type the hidden activation is rounded to)
+ *   workspace     device, nvfp_gated_mlp_workspace_bytes(m, hidden, inter) bytes, 256-byte aligned; dead afterwards
+ *   scratch       eight uint32 zeroed once, as for nvfp_activation_scales
+ * All weights and scales must be complete before this call's stream position is reached.
+ */
+int64_t nvfp_gated_mlp_workspace_bytes(int64_t m, int64_t hidden, int64_t inter);
+int nvfp_gated_mlp_forward(void* y, const void* x, int64_t m, int64_t hidden, int64_t x_row_stride, int x_dtype,
+                           const void* gate_up_fp4, const void* gate_up_sf, const float* gate_up_global_scale,
+                           int64_t inter, const void* down_fp4, const void* down_sf, const float* act_global_scale,
+                           const float* down_alpha, int64_t n_out, void* workspace, uint32_t* scratch,
+                           int out_dtype, void* stream);
+
+/*
  * The same GEMM with the [m, n] result written to n_dst (1..8) destinations instead of one, each a
  * row-major matrix with leading dimension dst_ld elements (>= n, multiple of 8), so that a slab can land
  * directly in its columns of a wider gathered matrix: dst[0] is

@@ -9,6 +9,7 @@ from .ops import (
     get_active_backend,
     global_scale,
     linear_forward,
+    gated_mlp_forward,
     mxfp4_scaled_mm,
     reciprocal_approximate_ftz_tensor,
     interleave_gate_up,
@@ -34,6 +35,7 @@ __all__ = [
     "device_status",
     "dynamic_scaled_fp4_quant",
     "linear_forward",
+    "gated_mlp_forward",
     "scaled_fp4_mm_fp4out",
     "scaled_fp4_mm_silu_mul",
     "interleave_gate_up",

@@ -259,6 +259,30 @@ def linear_forward(input: torch.Tensor, weight_fp4: torch.Tensor, weight_sf: tor
     return out
 
 
+def gated_mlp_forward(input: torch.Tensor, gate_up_fp4: torch.Tensor, gate_up_sf: torch.Tensor,
+                      gate_up_global_scale: torch.Tensor, down_fp4: torch.Tensor, down_sf: torch.Tensor,
+                      act_global_scale: torch.Tensor, down_alpha: torch.Tensor, scratch: torch.Tensor,
+                      out_dtype: torch.dtype) -> torch.Tensor:
+    """down(silu(gate(x)) * up(x)) with NVFP4 weights in ONE extension call (three chained launches: quantizer,
+    gate/up GEMM with activation and quantizer in its epilogue, down GEMM).  gate_up: rows interleaved with
+    interleave_gate_up and quantized as one tensor; act_global_scale: calibrated scale of the hidden activation;
+    down_alpha = alpha_from_scales(act_global_scale, down weight's global scale).  Same bytes as
+    dynamic_scaled_fp4_quant -> scaled_fp4_mm_silu_mul(out_global_scale=...) -> cutlass_scaled_fp4_mm."""
+    assert input.is_cuda and input.ndim == 2, "input must be a CUDA matrix"
+    assert input.dtype in (torch.float16, torch.bfloat16), f"input.dtype needs to be fp16 or bf16 but got {input.dtype}."
+    assert out_dtype in (torch.float16, torch.bfloat16), f"out_dtype needs to be fp16 or bf16 but got {out_dtype}."
+    m, hidden = input.shape
+    if input.stride(-1) != 1 or (m > 1 and input.stride(0) % 8 != 0) or input.data_ptr() % 16 != 0:
+        input = input.contiguous()
+    inter = gate_up_fp4.shape[0] // 2
+    ext = _load_scaled_fp4_ops(("gated_mlp_forward", "gated_mlp_workspace_bytes"))
+    out = torch.empty((m, down_fp4.shape[0]), dtype=out_dtype, device=input.device)
+    workspace = torch.empty(ext.gated_mlp_workspace_bytes(m, hidden, inter), dtype=torch.uint8, device=input.device)
+    ext.gated_mlp_forward(out, input, gate_up_fp4, gate_up_sf, gate_up_global_scale, down_fp4, down_sf,
+                          act_global_scale, down_alpha, workspace, scratch)
+    return out
+
+
 def alpha_from_scales(gs_a: torch.Tensor, gs_b: torch.Tensor) -> torch.Tensor:
     out = torch.empty(1, dtype=torch.float32, device=gs_a.device)
     ext = _load_scaled_fp4_ops(("alpha_from_scales",))

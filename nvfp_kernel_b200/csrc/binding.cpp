@@ -387,6 +387,49 @@ void linear_forward(torch::Tensor& D, torch::Tensor const& X, torch::Tensor cons
                                    workspace.data_ptr(), static_cast<uint32_t*>(scratch.data_ptr()), dt, current_stream(X)));
 }
 
+// Gated MLP in one call: Y = down(silu(gate(X)) * up(X)); see nvfp_gated_mlp_forward.
+int64_t gated_mlp_workspace_bytes(int64_t m, int64_t hidden, int64_t inter) {
+  return nvfp_gated_mlp_workspace_bytes(m, hidden, inter);
+}
+
+void gated_mlp_forward(torch::Tensor& Y, torch::Tensor const& X, torch::Tensor const& GU, torch::Tensor const& GU_sf,
+                       torch::Tensor const& gs_gu, torch::Tensor const& DW, torch::Tensor const& DW_sf,
+                       torch::Tensor const& gs_act, torch::Tensor const& alpha_down, torch::Tensor& workspace,
+                       torch::Tensor& scratch) {
+  TORCH_CHECK(X.dim() == 2 && X.stride(1) == 1, "input must be a matrix with dense rows");
+  CHECK_OPERAND(GU, at::ScalarType::Byte, "gate/up weight");
+  CHECK_OPERAND(DW, at::ScalarType::Byte, "down weight");
+  TORCH_CHECK(GU_sf.is_cuda() && GU_sf.is_contiguous() && DW_sf.is_cuda() && DW_sf.is_contiguous(),
+              "weight scales must be contiguous CUDA tensors");
+  TORCH_CHECK(Y.is_cuda() && Y.is_contiguous() && X.is_cuda() && gs_gu.is_cuda() && gs_act.is_cuda() &&
+                  alpha_down.is_cuda() && workspace.is_cuda() && scratch.is_cuda(), "all tensors must be CUDA tensors");
+  TORCH_CHECK(gs_gu.scalar_type() == at::ScalarType::Float && gs_act.scalar_type() == at::ScalarType::Float &&
+                  alpha_down.scalar_type() == at::ScalarType::Float, "scales must be fp32");
+  const int64_t m = X.size(0), hidden = X.size(1), inter = GU.size(0) / 2, n_out = DW.size(0);
+  TORCH_CHECK(GU.dim() == 2 && GU.size(0) % 32 == 0 && GU.size(1) * 2 == hidden,
+              "gate/up weight must be (2 * inter) x (hidden / 2) bytes with 2 * inter divisible by 32");
+  TORCH_CHECK(DW.dim() == 2 && DW.size(1) * 2 == inter && n_out % 32 == 0,
+              "down weight must be n x (inter / 2) bytes with n divisible by 32");
+  TORCH_CHECK(GU_sf.element_size() * GU_sf.numel() == nvfp_sf_rows_padded(2 * inter) * nvfp_sf_cols_padded(hidden, 16) &&
+                  DW_sf.element_size() * DW_sf.numel() == nvfp_sf_rows_padded(n_out) * nvfp_sf_cols_padded(inter, 16),
+              "weight scales must be padded and swizzled");
+  TORCH_CHECK(Y.dim() == 2 && Y.size(0) == m && Y.size(1) == n_out, "out must have shape (", m, "x", n_out, ")");
+  TORCH_CHECK(workspace.element_size() * workspace.numel() >= nvfp_gated_mlp_workspace_bytes(m, hidden, inter),
+              "workspace too small");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 32, "scratch must hold 32 bytes");
+  int dt;
+  if (Y.scalar_type() == at::ScalarType::BFloat16) dt = NVFP_DTYPE_BF16;
+  else if (Y.scalar_type() == at::ScalarType::Half) dt = NVFP_DTYPE_F16;
+  else TORCH_CHECK(false, "the gated MLP writes fp16 or bf16 (", Y.scalar_type(), ")");
+  const int xdt = dtype_code(X, "Unsupported input data type for quantize_to_fp4.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(X));
+  check_status(nvfp_gated_mlp_forward(Y.data_ptr(), X.data_ptr(), m, hidden, m > 1 ? X.stride(0) : hidden, xdt,
+                                      GU.data_ptr(), GU_sf.data_ptr(), static_cast<const float*>(gs_gu.data_ptr()), inter,
+                                      DW.data_ptr(), DW_sf.data_ptr(), static_cast<const float*>(gs_act.data_ptr()),
+                                      static_cast<const float*>(alpha_down.data_ptr()), n_out, workspace.data_ptr(),
+                                      static_cast<uint32_t*>(scratch.data_ptr()), dt, current_stream(X)));
+}
+
 void alpha_from_scales(torch::Tensor& alpha_out, torch::Tensor const& gs_a, torch::Tensor const& gs_b) {
   TORCH_CHECK(alpha_out.is_cuda() && gs_a.is_cuda() && gs_b.is_cuda(), "all tensors must be CUDA tensors");
   TORCH_CHECK(alpha_out.scalar_type() == at::ScalarType::Float && gs_a.scalar_type() == at::ScalarType::Float &&
@@ -422,6 +465,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dynamic_scaled_fp4_quant", &dynamic_scaled_fp4_quant);
   m.def("linear_workspace_bytes", &linear_workspace_bytes);
   m.def("linear_forward", &linear_forward);
+  m.def("gated_mlp_workspace_bytes", &gated_mlp_workspace_bytes);
+  m.def("gated_mlp_forward", &gated_mlp_forward);
   m.def("alpha_from_scales", &alpha_from_scales);
   m.def("device_status", &device_status);
 }

@@ -109,6 +109,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   __syncthreads();
   cluster_sync_all();                    // the peer's barriers and tensor memory exist from here on
   tc_fence_after_sync();
+  if (p.release_next) griddep_launch_dependents();
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tiles_m * p.tiles_n;

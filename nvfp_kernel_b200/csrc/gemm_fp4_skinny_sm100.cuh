@@ -187,6 +187,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (p.release_next) griddep_launch_dependents();
   // With receive buffers behind the rings every rank is ready for the others' partial sums from here on.
   if (sp.split > 1 && sp.recv_behind_ring) cluster_arrive();
 

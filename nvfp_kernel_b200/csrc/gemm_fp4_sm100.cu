@@ -91,6 +91,8 @@ struct GemmParams {
   uint32_t* status;
   int after_producer;   // launched with programmatic stream serialization behind the kernel that writes A, its
                         // scales and alpha: B and its scales may be fetched before that kernel has finished
+  int release_next;     // the next kernel in the stream is launched the same way behind this one and reads nothing
+                        // this kernel writes before its own griddepcontrol.wait: let it come up as CTAs retire
 };
 
 template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -282,6 +284,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  if (p.release_next) griddep_launch_dependents();
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
@@ -541,7 +544,7 @@ template <bool MX>
 int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream,
               const void* bias = nullptr, bool after_producer = false, const float* out_gs = nullptr,
-              void* out_sf = nullptr, int act = 0) {
+              void* out_sf = nullptr, int act = 0, bool release_next = false) {
   NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
   const bool fused = out_gs != nullptr || act != 0;
   if (fused) {
@@ -588,6 +591,7 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.out_gs = out_gs;
   p.out_sf = static_cast<uint8_t*>(out_sf);
   p.act = act;
+  p.release_next = release_next ? 1 : 0;
   p.d = d;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.sf_k_chunks = (int)ceil_div(k / kBlock, 4);
@@ -744,6 +748,52 @@ extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k,
     return rc;
   return scaled_mm<false>(&d, 1, n, a_fp4, w_fp4, a_sf, w_sf, alpha, m, n, k, out_dtype, stream, bias,
                           /*after_producer=*/true);
+}
+
+extern "C" int64_t nvfp_gated_mlp_workspace_bytes(int64_t m, int64_t hidden, int64_t inter) {
+  if (m < 0 || hidden < 0 || inter < 0) return -1;
+  return nvfp_linear_workspace_bytes(m, hidden) + round_up(m * (inter / 2), 256) +
+         round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(inter, 16), 256);
+}
+
+extern "C" int nvfp_gated_mlp_forward(void* y, const void* x, int64_t m, int64_t hidden, int64_t x_row_stride, int x_dtype,
+                                      const void* gate_up_fp4, const void* gate_up_sf, const float* gate_up_global_scale,
+                                      int64_t inter, const void* down_fp4, const void* down_sf,
+                                      const float* act_global_scale, const float* down_alpha, int64_t n_out,
+                                      void* workspace, uint32_t* scratch, int out_dtype, void* stream_) {
+  clear_error();
+  NVFP_REQUIRE(m >= 0 && hidden >= 0 && inter >= 0 && n_out >= 0, "negative shape");
+  NVFP_REQUIRE(hidden % 32 == 0 && inter % 32 == 0,
+               "Expected hidden and intermediate sizes to be divisible by 32, but got %lld and %lld.", (long long)hidden,
+               (long long)inter);
+  NVFP_REQUIRE(out_dtype == NVFP_DTYPE_F16 || out_dtype == NVFP_DTYPE_BF16,
+               "the gated MLP computes its hidden activation in fp16 or bf16 (dtype code %d)", out_dtype);
+  if (m == 0 || n_out == 0) return NVFP_OK;
+  NVFP_REQUIRE(inter > 0 && hidden > 0, "empty weight");
+  NVFP_REQUIRE(x != nullptr && workspace != nullptr && scratch != nullptr && gate_up_global_scale != nullptr &&
+                   act_global_scale != nullptr && down_alpha != nullptr, "null pointer");
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  NVFP_REQUIRE(x_dtype == NVFP_DTYPE_F16 || x_dtype == NVFP_DTYPE_BF16,
+               "Unsupported input data type for quantize_to_fp4 (dtype code %d).", x_dtype);
+  NVFP_REQUIRE(x_row_stride >= hidden && x_row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0,
+               "activation must be 16-byte aligned with a row stride that is >= hidden and a multiple of 8 elements");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* x_fp4 = ws;
+  uint8_t* x_sf = x_fp4 + round_up(m * (hidden / 2), 256);
+  float* gs = reinterpret_cast<float*>(x_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(hidden, 16), 256));
+  float* alpha = gs + 1;
+  void* h_fp4 = ws + nvfp_linear_workspace_bytes(m, hidden);
+  void* h_sf = static_cast<uint8_t*>(h_fp4) + round_up(m * (inter / 2), 256);
+  if (int rc = dynamic_fp4_quant_launch(x_fp4, x_sf, gs, alpha, scratch, x, m, hidden, x_row_stride, x_dtype,
+                                        gate_up_global_scale, /*release_next=*/true, nullptr, stream))
+    return rc;
+  if (int rc = scaled_mm<false>(&h_fp4, 1, 2 * inter, x_fp4, gate_up_fp4, x_sf, gate_up_sf, alpha, m, 2 * inter, hidden,
+                                out_dtype, stream, nullptr, /*after_producer=*/true, act_global_scale, h_sf, /*act=*/1,
+                                /*release_next=*/true))
+    return rc;
+  return scaled_mm<false>(&y, 1, n_out, h_fp4, down_fp4, h_sf, down_sf, down_alpha, m, n_out, inter, out_dtype, stream,
+                          nullptr, /*after_producer=*/true);
 }
 
 extern "C" int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void* a, const void* b,

@@ -52,6 +52,27 @@ def time_us(fn, repeats: int, flush: bool = True) -> float:
     return statistics.median(times)
 
 
+def time_us_interleaved(fns, repeats: int):
+    """Median device times of several alternatives, measured in turn within every repeat: on second-long,
+    power-limited work the clocks drift during a table row, and alternatives timed one after the other would not
+    see the same clocks."""
+    for fn in fns:
+        for _ in range(5):
+            fn()
+    torch.cuda.synchronize()
+    times = [[] for _ in fns]
+    for _ in range(repeats):
+        for i, fn in enumerate(fns):
+            _flush_l2()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            times[i].append(e0.elapsed_time(e1) * 1e3)
+    return [statistics.median(t) for t in times]
+
+
 def _graphed(fn):
     """fn captured in a CUDA graph; returns the replay callable (decode-sized work is launch-bound otherwise)."""
     side = torch.cuda.Stream()
@@ -175,11 +196,13 @@ def fp4out(repeats: int):
 
 def mlp(repeats: int):
     """Gated MLP (Llama shapes) from a bf16 activation to a bf16 result: every step a separate kernel, against the
-    gate/up GEMM that applies silu(gate) * up and quantizes for the down projection in its epilogue.  Rows of 128
-    tokens or fewer are timed as CUDA graph replays."""
+    gate/up GEMM that applies silu(gate) * up and quantizes for the down projection in its epilogue, and against
+    the same three kernels issued by one call and chained with programmatic dependent launch (what QuantGatedMLP
+    runs).  Rows of 128 tokens or fewer are timed as CUDA graph replays."""
     import torch.nn.functional as F
-    print(f"{'model':<12} {'M':<6} {'hidden':<7} {'inter':<7} {'separate (us)':<15} {'fused epilogue (us)':<21} {'TFLOP/s fused':<14}")
-    print("-" * 86)
+    print(f"{'model':<12} {'M':<6} {'hidden':<7} {'inter':<7} {'separate (us)':<15} {'fused epilogue (us)':<21} "
+          f"{'one call, chained (us)':<24} {'TFLOP/s':<8}")
+    print("-" * 106)
     for name, m, hidden, inter in (("llama-3-8b", 8192, 4096, 14336), ("llama-3-70b", 8192, 8192, 28672),
                                    ("llama-3-8b", 512, 4096, 14336), ("llama-3-8b", 128, 4096, 14336),
                                    ("llama-3-8b", 16, 4096, 14336), ("llama-3-70b", 16, 8192, 28672)):
@@ -208,12 +231,15 @@ def mlp(repeats: int):
             h_fp4, h_sf = ops.scaled_fp4_mm_silu_mul(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, torch.bfloat16, out_global_scale=gh)
             return ops.cutlass_scaled_fp4_mm(h_fp4, d_fp4, h_sf, d_sf, alpha2, torch.bfloat16)
 
+        def chained():
+            return ops.gated_mlp_forward(x, gu_fp4, gu_sf, ggu, d_fp4, d_sf, gh, alpha2, scratch, torch.bfloat16)
+
         if m <= 128:
-            separate, fused = _graphed(separate), _graphed(fused)
-        t_sep = time_us(separate, repeats)
-        t_fused = time_us(fused, repeats)
+            separate, fused, chained = _graphed(separate), _graphed(fused), _graphed(chained)
+        t_sep, t_fused, t_chain = time_us_interleaved((separate, fused, chained), repeats)
         flops = 2.0 * m * hidden * inter * 3
-        print(f"{name:<12} {m:<6} {hidden:<7} {inter:<7} {t_sep:<15.1f} {t_fused:<21.1f} {flops / t_fused / 1e6:<14.0f}")
+        print(f"{name:<12} {m:<6} {hidden:<7} {inter:<7} {t_sep:<15.1f} {t_fused:<21.1f} {t_chain:<24.1f} "
+              f"{flops / t_chain / 1e6:<8.0f}")
         del gu_fp4, gu_sf, d_fp4, d_sf, x
         torch.cuda.empty_cache()
 

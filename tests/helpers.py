@@ -121,6 +121,23 @@ def capi_linear_forward(x, w_fp4, w_sf, w_gs, scratch, out_dtype=torch.bfloat16,
     return d
 
 
+def capi_gated_mlp_forward(x, gu_fp4, gu_sf, gu_gs, d_fp4, d_sf, act_gs, down_alpha, scratch, out_dtype=torch.bfloat16):
+    """Whole gated MLP through nvfp_gated_mlp_forward."""
+    lib = _capi.load()
+    m, hidden = x.shape
+    inter, n = gu_fp4.shape[0] // 2, d_fp4.shape[0]
+    buf = torch.full((m * n + 256,), float("nan"), dtype=out_dtype, device=x.device)
+    y = buf[128:128 + m * n].view(m, n)
+    ws = torch.empty(lib.nvfp_gated_mlp_workspace_bytes(m, hidden, inter), dtype=torch.uint8, device=x.device)
+    _capi.check(lib.nvfp_gated_mlp_forward(y.data_ptr(), x.data_ptr(), m, hidden, x.stride(0) if m > 1 else hidden,
+                                           _dt(x.dtype), gu_fp4.data_ptr(), gu_sf.data_ptr(), gu_gs.data_ptr(), inter,
+                                           d_fp4.data_ptr(), d_sf.data_ptr(), act_gs.data_ptr(), down_alpha.data_ptr(), n,
+                                           ws.data_ptr(), scratch.data_ptr(), _dt(out_dtype), _stream()))
+    assert _capi.device_status() == 0, "a kernel gave up on a bounded wait"
+    assert torch.isnan(buf[:128]).all() and torch.isnan(buf[128 + m * n:]).all(), "out-of-bounds write"
+    return y
+
+
 def capi_rcp(x: torch.Tensor) -> torch.Tensor:
     lib = _capi.load()
     y = torch.empty_like(x)

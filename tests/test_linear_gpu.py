@@ -230,6 +230,35 @@ def test_gated_mlp_with_activation_and_quantizer_in_the_epilogue(m, k, inter, hi
     assert nv.device_status() == 0
 
 
+@pytest.mark.parametrize("m,hidden,inter", [(1, 4096, 1024), (16, 1024, 12288), (40, 512, 1440), (128, 1024, 4096),
+                                            (300, 1024, 1440), (2048, 1024, 2048), (5000, 512, 512)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_one_call_gated_mlp_equals_the_separate_calls(m, hidden, inter, dt):
+    """nvfp_gated_mlp_forward (quantizer, gate/up GEMM and down GEMM chained with programmatic dependent launch, each
+    GEMM fetching its weights while the kernel before it still runs) against the same three steps as separate calls:
+    identical bytes, on shapes that take each of the three GEMM kernels, the one-pass and the two-launch quantizer,
+    called twice in a row so that a call's first kernel follows the previous call's last."""
+    from helpers import capi_gated_mlp_forward
+    import nvfp_kernel_b200 as nv
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, hidden).to(dt).cuda()
+    w_gu = nv.interleave_gate_up((torch.randn(inter, hidden) * 0.05).to(dt).cuda(), (torch.randn(inter, hidden) * 0.05).to(dt).cuda())
+    w_d = (torch.randn(hidden, inter) * 0.03).to(dt).cuda()
+    ggu, gd = nv.global_scale(w_gu), nv.global_scale(w_d)
+    gu_fp4, gu_sf = nv.scaled_fp4_quant(w_gu, ggu)
+    d_fp4, d_sf = nv.scaled_fp4_quant(w_d, gd)
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    x_fp4, x_sf, _, alpha1 = nv.dynamic_scaled_fp4_quant(x, scratch, ggu)
+    gh = nv.global_scale(nv.scaled_fp4_mm_silu_mul(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, dt))
+    alpha2 = nv.alpha_from_scales(gh, gd)
+    h_fp4, h_sf = nv.scaled_fp4_mm_silu_mul(x_fp4, gu_fp4, x_sf, gu_sf, alpha1, dt, out_global_scale=gh)
+    want = nv.cutlass_scaled_fp4_mm(h_fp4, d_fp4, h_sf, d_sf, alpha2, dt)
+    for _ in range(2):
+        got = capi_gated_mlp_forward(x, gu_fp4, gu_sf, ggu, d_fp4, d_sf, gh, alpha2, scratch, dt)
+        assert torch.equal(got, want)
+    assert torch.equal(nv.gated_mlp_forward(x, gu_fp4, gu_sf, ggu, d_fp4, d_sf, gh, alpha2, scratch, dt), want)
+
+
 def test_quant_gated_mlp_module():
     """QuantGatedMLP (three launches, calibrated hidden scale) against its own separate-kernel path (dynamic hidden
     scale): with the scale calibrated on the very input both quantize the hidden activation with the same scale, so
