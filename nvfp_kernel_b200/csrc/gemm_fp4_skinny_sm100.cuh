@@ -277,200 +277,205 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   }
   bool have_peers = true;
   for (int j = 0; j < my_tiles; ++j) {             // one pass unless persistent
-  const int n_tile = tile0 + j * tile_stride;
-  bool have_acc = false;
-  float bias = 0.0f;
-  if (epi && owner && p.bias && n_tile * 128 + wrow < p.n) {
-    const int row = n_tile * 128 + wrow;
-    if constexpr (sizeof(OutT) == 4) bias = __ldg(static_cast<const float*>(p.bias) + row);
-    else if constexpr (std::is_same<OutT, __half>::value) bias = __half2float(static_cast<const __half*>(p.bias)[row]);
-    else bias = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row]);
-  }
-  if (epi && my_stages > 0) {
-    have_acc = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull + (j & 1)), (uint32_t)(j >> 1) & 1u, abort_flag));
-    if (!have_acc) {
-      *abort_flag = 1;
-      if (lane == 0) atomicOr(p.status, kErrEpilogue);
+    const int n_tile = tile0 + j * tile_stride;
+    bool have_acc = false;
+    float bias = 0.0f;
+    if (epi && owner && p.bias && n_tile * 128 + wrow < p.n) {
+      const int row = n_tile * 128 + wrow;
+      if constexpr (sizeof(OutT) == 4) bias = __ldg(static_cast<const float*>(p.bias) + row);
+      else if constexpr (std::is_same<OutT, __half>::value) bias = __half2float(static_cast<const __half*>(p.bias)[row]);
+      else bias = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row]);
     }
-    tc_fence_after_sync();
-  }
-  const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(j & 1) * kAccBufCols;
-  if (sp.split > 1) {
-    // A rank whose receive buffer lies in its stage area is ready only now: its epilogue warps arrive after its
-    // last MMA has completed (all TMA writes landed, all MMA reads done).
-    if (!sp.recv_behind_ring) cluster_arrive();
-    cluster_wait();
-    if (epi) {
-      // This rank's partial for every owner but itself -> its own (drained) stage area, one block
-      // [128 rows][tok + 4] per owner, then one bulk copy per warp and owner into that owner's receive buffer;
-      // slot of sender r at owner o: r for r < o, r - 1 above.
-      for (int o = 0; o < sp.owners; ++o) {
-        if (o == (int)rank) continue;
-        const uint32_t block = stage_base + (uint32_t)o * block_bytes;
-        const uint32_t stage_row = block + (uint32_t)wrow * ld * 4u;
-        for (int c = 0; c < sp.tok; c += 16) {
-          uint32_t r[16];
-          if (have_acc) {
-            tmem_ld_32x32b_x16(t_row + o * sp.tok + c, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int t = 0; t < 16; ++t) r[t] = 0u;
-          }
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            st_shared_v4(stage_row + (uint32_t)(c + 4 * v) * 4u, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        const uint32_t warp_bytes = 32u * ld * 4u, warp_off = (uint32_t)q * warp_bytes;
-        for (int o = 0; o < sp.owners; ++o) {
-          if (o == (int)rank) continue;
-          const uint32_t slot = (int)rank < o ? rank : rank - 1u;
-          bulk_copy_to_cta(map_to_cta(smem_u32(recv_buf), (uint32_t)o) + slot * block_bytes + warp_off,
-                           stage_base + (uint32_t)o * block_bytes + warp_off, warp_bytes, map_to_cta(bar(kReduce), (uint32_t)o));
-        }
-      }
-      __syncwarp();
-    }
-    if (epi && owner) {
-      have_peers = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kReduce), 0, abort_flag));
-      if (!have_peers) {
+    if (epi && my_stages > 0) {
+      have_acc = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull + (j & 1)), (uint32_t)(j >> 1) & 1u, abort_flag));
+      if (!have_acc) {
         *abort_flag = 1;
         if (lane == 0) atomicOr(p.status, kErrEpilogue);
       }
+      tc_fence_after_sync();
     }
-    // Second phase: a rank may leave only after every owner has received every copy (the copies' source is the
-    // sender's shared memory); an owner arrives here once it has its data and adds while the others wait.  Nothing
-    // written before this arrival is read by another CTA afterwards, so it needs no release.
-    cluster_arrive_relaxed();
-  }
-  if (epi && owner) {
-    OutT* d = static_cast<OutT*>(p.d);
-    // staging tile [16 tokens][128 columns]: in the drained stage area, behind the blocks staged for sending, or
-    // (persistent) behind the ring
-    OutT* out_tile = reinterpret_cast<OutT*>(smem + sp.out_tile_offset);
-    const int tok0 = (int)rank * sp.tok;
-    const bool fused = p.act != 0 || p.out_gs != nullptr;            // 16-bit value types only
-    const int tile_w = p.act ? 64 : 128;                              // output columns this tile of 128 weight rows yields
-    const float out_gs = p.out_gs ? __ldg(p.out_gs) : 1.0f, rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
-    for (int c = 0; c < sp.tok; c += 16) {
-      uint32_t r[16];
-      if (have_acc) {
-        tmem_ld_32x32b_x16(t_row + tok0 + c, r);
-        tmem_ld_wait();
-      } else {
+    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(j & 1) * kAccBufCols;
+    if (sp.split > 1) {
+      // A rank whose receive buffer lies in its stage area is ready only now: its epilogue warps arrive after its
+      // last MMA has completed (all TMA writes landed, all MMA reads done).
+      if (!sp.recv_behind_ring) cluster_arrive();
+      cluster_wait();
+      if (epi) {
+        // This rank's partial for every owner but itself -> its own (drained) stage area, one block
+        // [128 rows][tok + 4] per owner, then one bulk copy per warp and owner into that owner's receive buffer;
+        // slot of sender r at owner o: r for r < o, r - 1 above.
+        for (int o = 0; o < sp.owners; ++o) {
+          if (o == (int)rank) continue;
+          const uint32_t block = stage_base + (uint32_t)o * block_bytes;
+          const uint32_t stage_row = block + (uint32_t)wrow * ld * 4u;
+          for (int c = 0; c < sp.tok; c += 16) {
+            uint32_t r[16];
+            if (have_acc) {
+              tmem_ld_32x32b_x16(t_row + o * sp.tok + c, r);
+              tmem_ld_wait();
+            } else {
 #pragma unroll
-        for (int t = 0; t < 16; ++t) r[t] = 0u;
-      }
-      float part[16];
+              for (int t = 0; t < 16; ++t) r[t] = 0u;
+            }
 #pragma unroll
-      for (int t = 0; t < 16; ++t) part[t] = __uint_as_float(r[t]);
-      if (have_peers) {
-        for (int pr = 0; pr < sp.split - 1; ++pr) {
-          const float4* src = reinterpret_cast<const float4*>(recv_buf + (pr * 128 + wrow) * ld + c);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const float4 f = src[v];
-            part[4 * v] += f.x; part[4 * v + 1] += f.y; part[4 * v + 2] += f.z; part[4 * v + 3] += f.w;
+            for (int v = 0; v < 4; ++v)
+              st_shared_v4(stage_row + (uint32_t)(c + 4 * v) * 4u,
+                           make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
           }
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t warp_bytes = 32u * ld * 4u, warp_off = (uint32_t)q * warp_bytes;
+          for (int o = 0; o < sp.owners; ++o) {
+            if (o == (int)rank) continue;
+            const uint32_t slot = (int)rank < o ? rank : rank - 1u;
+            bulk_copy_to_cta(map_to_cta(smem_u32(recv_buf), (uint32_t)o) + slot * block_bytes + warp_off,
+                             stage_base + (uint32_t)o * block_bytes + warp_off, warp_bytes,
+                             map_to_cta(bar(kReduce), (uint32_t)o));
+          }
+        }
+        __syncwarp();
       }
-      // Transpose through shared memory: this thread holds 16 tokens of one output column, the output rows are
-      // tokens.  Writing them as they are costs 16 two-byte stores per thread; staged, a thread stores 16 bytes.
-      if (c != 0 || j != 0) named_barrier_sync(1, 128);  // the previous chunk has left the staging tile
+      if (epi && owner) {
+        have_peers = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kReduce), 0, abort_flag));
+        if (!have_peers) {
+          *abort_flag = 1;
+          if (lane == 0) atomicOr(p.status, kErrEpilogue);
+        }
+      }
+      // Second phase: a rank may leave only after every owner has received every copy (the copies' source is the
+      // sender's shared memory); an owner arrives here once it has its data and adds while the others wait.  Nothing
+      // written before this arrival is read by another CTA afterwards, so it needs no release.
+      cluster_arrive_relaxed();
+    }
+    if (epi && owner) {
+      OutT* d = static_cast<OutT*>(p.d);
+      // staging tile [16 tokens][128 columns]: in the drained stage area, behind the blocks staged for sending, or
+      // (persistent) behind the ring
+      OutT* out_tile = reinterpret_cast<OutT*>(smem + sp.out_tile_offset);
+      const int tok0 = (int)rank * sp.tok;
+      const bool fused = p.act != 0 || p.out_gs != nullptr;            // 16-bit value types only
+      const int tile_w = p.act ? 64 : 128;                              // output columns this tile of 128 weight rows yields
+      const float out_gs = p.out_gs ? __ldg(p.out_gs) : 1.0f, rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
+      for (int c = 0; c < sp.tok; c += 16) {
+        uint32_t r[16];
+        if (have_acc) {
+          tmem_ld_32x32b_x16(t_row + tok0 + c, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) r[t] = 0u;
+        }
+        float part[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) part[t] = __uint_as_float(r[t]);
+        if (have_peers) {
+          for (int pr = 0; pr < sp.split - 1; ++pr) {
+            const float4* src = reinterpret_cast<const float4*>(recv_buf + (pr * 128 + wrow) * ld + c);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const float4 f = src[v];
+              part[4 * v] += f.x; part[4 * v + 1] += f.y; part[4 * v + 2] += f.z; part[4 * v + 3] += f.w;
+            }
+          }
+        }
+        // Transpose through shared memory: this thread holds 16 tokens of one output column, the output rows are
+        // tokens.  Writing them as they are costs 16 two-byte stores per thread; staged, a thread stores 16 bytes.
+        if (c != 0 || j != 0) named_barrier_sync(1, 128);  // the previous chunk has left the staging tile
+        if constexpr (sizeof(OutT) == 2) {
+          if (fused) {
+            // Gated activation: the 32 weight rows of this warp are 16 gate rows and their 16 up rows, so lane l < 16
+            // finds its up value in lane l + 16 and the warp yields 16 output columns.  Then (or instead) the staged
+            // tile is quantized to NVFP4 block by block, each block by one thread, with the quantizer's own function.
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+              float v = fmaf(part[t], alpha, bias);
+              if constexpr (std::is_same<OutT, __half>::value) v = __half2float(__float2half_rn(v));
+              else v = __bfloat162float(__float2bfloat16_rn(v));
+              if (p.act) {
+                const float up = __shfl_down_sync(0xffffffffu, v, 16);
+                v = silu_mul_16bit<OutT>(v, up);
+              }
+              if (!p.act || lane < 16) {
+                const int oc = p.act ? q * 16 + lane : wrow;
+                if constexpr (std::is_same<OutT, __half>::value) out_tile[t * tile_w + oc] = __float2half_rn(v);
+                else out_tile[t * tile_w + oc] = __float2bfloat16_rn(v);
+              }
+            }
+            named_barrier_sync(1, 128);
+            const int out_cols = p.act ? p.n / 2 : p.n;
+            if (p.out_gs == nullptr) {
+              const int segs = tile_w / 8;                   // 16-byte segments per token row of the tile
+              for (int sidx = (int)threadIdx.x - 64; sidx < 16 * segs; sidx += 128) {
+                const int t = sidx / segs, seg = sidx % segs;
+                const int token = tok0 + c + t, col = n_tile * tile_w + seg * 8;
+                if (token < p.m && col < out_cols)
+                  *reinterpret_cast<uint4*>(d + (int64_t)token * out_cols + col) =
+                      *reinterpret_cast<const uint4*>(out_tile + t * tile_w + seg * 8);
+              }
+            } else {
+              using V2 = typename Vec2<OutT>::type;
+              const int nblk = tile_w / 16, k_tiles = (out_cols + 63) / 64;
+              uint8_t* out_fp4 = static_cast<uint8_t*>(p.d);
+              for (int e = (int)threadIdx.x - 64; e < 16 * nblk; e += 128) {
+                const int t = e / nblk, b = e % nblk;
+                const int token = tok0 + c + t, ocol = n_tile * tile_w + b * 16;
+                const uint4* src = reinterpret_cast<const uint4*>(out_tile + t * tile_w + b * 16);
+                const uint4 lo = src[0], hi = src[1];
+                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                V2 h2[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) h2[i] = *reinterpret_cast<const V2*>(&w[i]);
+                uint8_t sf;
+                const uint2 qv = nvfp4_quantize_block<OutT>(h2, out_gs, rcp_out_gs, rcp6, sf);
+                if (token < p.m && ocol < out_cols)
+                  *reinterpret_cast<uint2*>(out_fp4 + (int64_t)token * (out_cols / 2) + ocol / 2) = qv;
+                if (ocol / 64 < k_tiles)      // token < 128: rows [m, nt) of the one 128-row scale tile get zero scales
+                  p.out_sf[(int64_t)(ocol / 64) * 512 + (token % 32) * 16 + (token / 32) * 4 + (ocol % 64) / 16] =
+                      token < p.m ? sf : (uint8_t)0;
+              }
+            }
+            continue;
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          const float v = fmaf(part[t], alpha, bias);
+          if constexpr (sizeof(OutT) == 4) out_tile[t * 128 + wrow] = v;
+          else if constexpr (std::is_same<OutT, __half>::value) out_tile[t * 128 + wrow] = __float2half_rn(v);
+          else out_tile[t * 128 + wrow] = __float2bfloat16_rn(v);
+        }
+        named_barrier_sync(1, 128);
+        constexpr int kSegs = 128 * (int)sizeof(OutT) / 16;   // 16-byte segments per token row
+        constexpr int kSegElems = 16 / (int)sizeof(OutT);
+        for (int sidx = (int)threadIdx.x - 64; sidx < 16 * kSegs; sidx += 128) {
+          const int t = sidx / kSegs, seg = sidx % kSegs;
+          const int token = tok0 + c + t, col = n_tile * 128 + seg * kSegElems;
+          if (token < p.m && col < p.n)
+            *reinterpret_cast<uint4*>(d + (int64_t)token * p.n + col) =
+                *reinterpret_cast<const uint4*>(out_tile + t * 128 + seg * kSegElems);
+        }
+      }
+      // NVFP4 output: the scale rows between the padded token count and 128 are zero in the quantizer's output too
       if constexpr (sizeof(OutT) == 2) {
-        if (fused) {
-          // Gated activation: the 32 weight rows of this warp are 16 gate rows and their 16 up rows, so lane l < 16
-          // finds its up value in lane l + 16 and the warp yields 16 output columns.  Then (or instead) the staged
-          // tile is quantized to NVFP4 block by block, each block by one thread, with the quantizer's own function.
-#pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            float v = fmaf(part[t], alpha, bias);
-            if constexpr (std::is_same<OutT, __half>::value) v = __half2float(__float2half_rn(v));
-            else v = __bfloat162float(__float2bfloat16_rn(v));
-            if (p.act) {
-              const float up = __shfl_down_sync(0xffffffffu, v, 16);
-              v = silu_mul_16bit<OutT>(v, up);
-            }
-            if (!p.act || lane < 16) {
-              const int oc = p.act ? q * 16 + lane : wrow;
-              if constexpr (std::is_same<OutT, __half>::value) out_tile[t * tile_w + oc] = __float2half_rn(v);
-              else out_tile[t * tile_w + oc] = __float2bfloat16_rn(v);
-            }
-          }
-          named_barrier_sync(1, 128);
+        if (fused && p.out_gs != nullptr && rank == 0) {
           const int out_cols = p.act ? p.n / 2 : p.n;
-          if (p.out_gs == nullptr) {
-            const int segs = tile_w / 8;                   // 16-byte segments per token row of the tile
-            for (int sidx = (int)threadIdx.x - 64; sidx < 16 * segs; sidx += 128) {
-              const int t = sidx / segs, seg = sidx % segs;
-              const int token = tok0 + c + t, col = n_tile * tile_w + seg * 8;
-              if (token < p.m && col < out_cols)
-                *reinterpret_cast<uint4*>(d + (int64_t)token * out_cols + col) = *reinterpret_cast<const uint4*>(out_tile + t * tile_w + seg * 8);
-            }
-          } else {
-            using V2 = typename Vec2<OutT>::type;
-            const int nblk = tile_w / 16, k_tiles = (out_cols + 63) / 64;
-            uint8_t* out_fp4 = static_cast<uint8_t*>(p.d);
-            for (int e = (int)threadIdx.x - 64; e < 16 * nblk; e += 128) {
-              const int t = e / nblk, b = e % nblk;
-              const int token = tok0 + c + t, ocol = n_tile * tile_w + b * 16;
-              const uint4* src = reinterpret_cast<const uint4*>(out_tile + t * tile_w + b * 16);
-              const uint4 lo = src[0], hi = src[1];
-              const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-              V2 h2[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) h2[i] = *reinterpret_cast<const V2*>(&w[i]);
-              uint8_t sf;
-              const uint2 qv = nvfp4_quantize_block<OutT>(h2, out_gs, rcp_out_gs, rcp6, sf);
-              if (token < p.m && ocol < out_cols)
-                *reinterpret_cast<uint2*>(out_fp4 + (int64_t)token * (out_cols / 2) + ocol / 2) = qv;
-              if (ocol / 64 < k_tiles)      // token < 128: rows [m, nt) of the one 128-row scale tile get zero scales
-                p.out_sf[(int64_t)(ocol / 64) * 512 + (token % 32) * 16 + (token / 32) * 4 + (ocol % 64) / 16] = token < p.m ? sf : (uint8_t)0;
-            }
+          const int nblk = tile_w / 16, k_tiles = (out_cols + 63) / 64;
+          for (int e = (int)threadIdx.x - 64; e < (128 - sp.nt) * nblk; e += 128) {
+            const int row = sp.nt + e / nblk, ocol = n_tile * tile_w + (e % nblk) * 16;
+            if (ocol / 64 < k_tiles)
+              p.out_sf[(int64_t)(ocol / 64) * 512 + (row % 32) * 16 + (row / 32) * 4 + (ocol % 64) / 16] = (uint8_t)0;
           }
-          continue;
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        const float v = fmaf(part[t], alpha, bias);
-        if constexpr (sizeof(OutT) == 4) out_tile[t * 128 + wrow] = v;
-        else if constexpr (std::is_same<OutT, __half>::value) out_tile[t * 128 + wrow] = __float2half_rn(v);
-        else out_tile[t * 128 + wrow] = __float2bfloat16_rn(v);
-      }
-      named_barrier_sync(1, 128);
-      constexpr int kSegs = 128 * (int)sizeof(OutT) / 16;   // 16-byte segments per token row
-      constexpr int kSegElems = 16 / (int)sizeof(OutT);
-      for (int sidx = (int)threadIdx.x - 64; sidx < 16 * kSegs; sidx += 128) {
-        const int t = sidx / kSegs, seg = sidx % kSegs;
-        const int token = tok0 + c + t, col = n_tile * 128 + seg * kSegElems;
-        if (token < p.m && col < p.n)
-          *reinterpret_cast<uint4*>(d + (int64_t)token * p.n + col) = *reinterpret_cast<const uint4*>(out_tile + t * 128 + seg * kSegElems);
-      }
-    }
-    // NVFP4 output: the scale rows between the padded token count and 128 are zero in the quantizer's output too
-    if constexpr (sizeof(OutT) == 2) {
-      if (fused && p.out_gs != nullptr && rank == 0) {
-        const int out_cols = p.act ? p.n / 2 : p.n;
-        const int nblk = tile_w / 16, k_tiles = (out_cols + 63) / 64;
-        for (int e = (int)threadIdx.x - 64; e < (128 - sp.nt) * nblk; e += 128) {
-          const int row = sp.nt + e / nblk, ocol = n_tile * tile_w + (e % nblk) * 16;
-          if (ocol / 64 < k_tiles)
-            p.out_sf[(int64_t)(ocol / 64) * 512 + (row % 32) * 16 + (row / 32) * 4 + (ocol % 64) / 16] = (uint8_t)0;
         }
       }
     }
-  }
-  if (epi && sp.persistent) {
-    // this tile's accumulator is in registers or stored: the issuer may overwrite it two tiles on
-    tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar(kAccEmpty + (j & 1)));
-  }
+    if (epi && sp.persistent) {
+      // this tile's accumulator is in registers or stored: the issuer may overwrite it two tiles on
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kAccEmpty + (j & 1)));
+    }
   }  // tiles
   if (sp.split > 1) cluster_wait();
   tc_fence_before_sync();
