@@ -34,6 +34,11 @@ def test_host_only_entry_points():
     assert lib.nvfp_sf_cols_padded(80, 16) == 8 and lib.nvfp_sf_cols_padded(8192, 16) == 512
     assert lib.nvfp_sf_cols_padded(8192, 32) == 256
     assert lib.nvfp_last_error() is not None
+    # workspaces: quantized activation + scales + two scalars; the MLP adds the quantized hidden activation
+    lin = lib.nvfp_linear_workspace_bytes(300, 1024)
+    assert lin == 300 * 512 + 384 * 64 + 256 and lin % 256 == 0
+    assert lib.nvfp_gated_mlp_workspace_bytes(300, 1024, 2048) == lin + 300 * 1024 + 384 * 128
+    assert lib.nvfp_linear_workspace_bytes(-1, 64) == -1 and lib.nvfp_gated_mlp_workspace_bytes(1, 64, -64) == -1
 
 
 def test_argument_validation_needs_no_gpu():
@@ -49,6 +54,12 @@ def test_argument_validation_needs_no_gpu():
     assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"divisible by 32" in lib.nvfp_last_error()
     rc = lib.nvfp_scaled_fp4_mm(p, p, p, p, p, p, 4, 40, 64, _capi.NVFP_DTYPE_BF16, None)
     assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"n to be divisible" in lib.nvfp_last_error()
+    rc = lib.nvfp_gated_mlp_forward(p, p, 4, 64, 64, _capi.NVFP_DTYPE_BF16, p, p, p, 48, p, p, p, p, 64, p, p,
+                                    _capi.NVFP_DTYPE_BF16, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"divisible by 32" in lib.nvfp_last_error()
+    rc = lib.nvfp_gated_mlp_forward(p, p, 4, 64, 64, _capi.NVFP_DTYPE_BF16, p, p, p, 64, p, p, p, p, 64, p, p,
+                                    _capi.NVFP_DTYPE_F32, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"fp16 or bf16" in lib.nvfp_last_error()
     rc = lib.nvfp_mxfp4_quant(p, p, p, 4, 64, 64, _capi.NVFP_DTYPE_BF16, 9, None)
     assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT
     with pytest.raises(_capi.NvfpError):
