@@ -251,9 +251,11 @@ int nvfp_activation_scales(float* gs_out, float* alpha_out, uint32_t* scratch, c
  * Dynamic per-tensor NVFP4 quantization in one pass: gs_out = rcp(max|x|) * 2688 of THIS tensor, the tensor
  * quantized with it exactly as nvfp_scaled_fp4_quant would (same bytes), and, when gs_weight is given,
  * alpha_out = 1 / (gs_out * gs_weight[0]).  Replaces the reference's abs().max() -> division -> quantize chain
- * (speed_test.py:46-48) and reads the tensor once: while the tensor has no more 128 x 128 tiles than two per
- * SM (296 on a B200: 4.8 M elements), one cooperative launch keeps every tile in registers across the
- * reduction of the maximum; larger tensors take the global-scale launch followed by the quantize launch.
+ * (speed_test.py:46-48) and reads the tensor once: decode-sized tensors (up to 128 rows, a few thousand 16-element
+ * blocks) are handled by one cluster of CTAs that exchange their maxima through shared memory; while the tensor has
+ * no more 128 x 128 tiles than two per SM (296 on a B200: 4.8 M elements), one cooperative launch keeps every tile in
+ * registers across the reduction of the maximum; larger tensors take the global-scale launch followed by the
+ * quantize launch.
  *   scratch   as for nvfp_activation_scales (eight uint32 zeroed once; may be the same buffer)
  *   gs_weight device fp32 or NULL; alpha_out may be NULL when gs_weight is
  * A CTA that waits more than two seconds for the others gives up, sets bit 8 of the device status word

@@ -23,6 +23,7 @@
 
 #include "common.h"
 #include "quant_math.cuh"
+#include "ptx_sm100.cuh"
 
 namespace nvfp {
 namespace {
@@ -268,6 +269,105 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
   }
 }
 
+// DYNAMIC quantization of a decode-sized activation (one 128-row scale tile) by ONE CLUSTER of up to eight CTAs,
+// launched like any kernel (nothing cooperative): each CTA owns a range of 64-column scale chunks, keeps its part of
+// the tensor in registers (up to four 16-element blocks per thread), and the CTAs exchange their maxima through each
+// other's shared memory around one cluster barrier (no trip through global memory).  A CTA stages its chunks' scale
+// bytes in shared memory (zero where the tensor has no rows) and stores them 16 bytes at a time.  Same bytes as the
+// tiled kernel.
+constexpr int kSmallThreads = 512;
+constexpr int kSmallBlocksPerThread = 4;
+constexpr int kSmallMaxCluster = 8;
+constexpr int kSmallMaxChunksPerCta = 32;          // 16 KB of staged scale bytes
+
+template <typename T>
+__global__ void __launch_bounds__(kSmallThreads)
+quant_fp4_small_kernel(const T* __restrict__ in, int64_t in_stride, uint8_t* __restrict__ out,
+                       uint8_t* __restrict__ sf_out, int m, int n, int num_k_chunks, int chunks_per_cta, int aligned32,
+                       const DynamicScale dyn) {
+  if (dyn.release_next) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ __align__(16) uint8_t sf_stage_small[kSmallMaxChunksPerCta * 512];   // [chunk][32][4][4]
+  __shared__ float warp_max[kSmallThreads / 32];
+  __shared__ float cta_max[kSmallMaxCluster];      // written by the CTAs of the cluster, one slot each
+  __shared__ float gs_shared;
+  const int tid = threadIdx.x;
+  const uint32_t rank = ptx::cluster_ctarank(), csize = gridDim.x;
+  // every CTA of the cluster is running once all have arrived here; waited for just before the remote stores
+  ptx::cluster_arrive_relaxed();
+  // the other operand's scale is needed only at the end: fetched now, beside the tensor's loads
+  float gs_other = 1.0f;
+  if (tid == 0 && rank == 0 && dyn.gs_other) gs_other = __ldg(dyn.gs_other);
+  const int chunk0 = (int)rank * chunks_per_cta;
+  const int my_chunks = max(0, min(chunks_per_cta, num_k_chunks - chunk0));
+  const int blocks_per_row = n / 16, cols = my_chunks * 4;            // 16-element blocks per row: all, mine
+  const int total = m * cols;
+  Pack16<T> v[kSmallBlocksPerThread];
+#pragma unroll
+  for (int i = 0; i < kSmallBlocksPerThread; ++i) {
+    const int id = tid + i * kSmallThreads;
+    v[i].raw[0] = make_uint4(0u, 0u, 0u, 0u);
+    v[i].raw[1] = make_uint4(0u, 0u, 0u, 0u);
+    if (id < total) {
+      const int row = id / cols, cb = chunk0 * 4 + id % cols;
+      if (cb < blocks_per_row) load16<T>(v[i], in + (int64_t)row * in_stride + cb * 16, aligned32 != 0);
+    }
+  }
+  uint4* stage16 = reinterpret_cast<uint4*>(sf_stage_small);
+  for (int j = tid; j < my_chunks * 32; j += kSmallThreads) stage16[j] = make_uint4(0u, 0u, 0u, 0u);
+  auto mx2 = __habs2(v[0].h2[0]);
+#pragma unroll
+  for (int i = 0; i < kSmallBlocksPerThread; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) mx2 = __hmax2(mx2, __habs2(v[i].h2[e]));
+  float mx = to_float<T>(__hmax(mx2.x, mx2.y));
+#pragma unroll
+  for (int sh = 16; sh > 0; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+  if ((tid & 31) == 0) warp_max[tid >> 5] = mx;
+  __syncthreads();
+  ptx::cluster_wait();
+  if (tid < 32) {
+    float r = tid < kSmallThreads / 32 ? warp_max[tid] : 0.0f;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, sh));
+    // lane l tells CTA l
+    if ((uint32_t)tid < csize)
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ptx::map_to_cta(ptx::smem_u32(&cta_max[rank]), (uint32_t)tid)), "f"(r)
+                   : "memory");
+  }
+  ptx::cluster_arrive();                       // release: the stores above are visible to whoever has waited
+  ptx::cluster_wait();
+  if (tid == 0) {
+    float r = cta_max[0];
+    for (uint32_t c = 1; c < csize; ++c) r = fmaxf(r, cta_max[c]);
+    if (r == 0.0f) r = 1.0f;
+    // same two roundings as amax_kernel: reciprocal(amax) * 2688
+    const float g = __fmul_rn(__frcp_rn(r), 448.0f * 6.0f);
+    gs_shared = g;
+    if (rank == 0) {
+      *dyn.gs_out = g;
+      if (dyn.gs_other) *dyn.alpha_out = __fdiv_rn(1.0f, __fmul_rn(g, gs_other));
+    }
+  }
+  __syncthreads();
+  const float gs = gs_shared, rcp_gs = rcp_approx_ftz(gs), rcp6 = rcp_approx_ftz(6.0f);
+#pragma unroll
+  for (int i = 0; i < kSmallBlocksPerThread; ++i) {
+    const int id = tid + i * kSmallThreads;
+    if (id < total) {
+      const int row = id / cols, cbl = id % cols, cb = chunk0 * 4 + cbl;
+      if (cb < blocks_per_row) {
+        uint8_t sf_byte;
+        const uint2 packed = nvfp4_quantize_block<T>(v[i].h2, gs, rcp_gs, rcp6, sf_byte);
+        *reinterpret_cast<uint2*>(out + (int64_t)row * (n / 2) + cb * 8) = packed;
+        sf_stage_small[(cbl / 4) * 512 + (row % 32) * 16 + (row / 32) * 4 + (cbl % 4)] = sf_byte;
+      }
+    }
+  }
+  __syncthreads();
+  uint4* dst = reinterpret_cast<uint4*>(sf_out + (int64_t)chunk0 * 512);
+  for (int j = tid; j < my_chunks * 32; j += kSmallThreads) dst[j] = stage16[j];
+}
+
 __global__ void rcp_kernel(float* __restrict__ out, const float* __restrict__ in, int64_t count) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < count) out[i] = rcp_approx_ftz(in[i]);
@@ -464,6 +564,32 @@ int launch_dynamic_quant(void* out_fp4, void* out_sf, float* gs_out, float* alph
   const int64_t tiles = m_tiles * col_tiles;
   const bool fits = dynamic_quant_fits<T>(m, n);
   if (one_pass) *one_pass = fits;
+  // decode-sized (one 128-row scale tile, few enough blocks for one cluster's registers): no grid barrier
+  const int64_t k_chunks = ceil_div(n / 16, 4);
+  int cluster = 1;
+  while (cluster < kSmallMaxCluster && cluster * 2 <= k_chunks) cluster *= 2;
+  const int64_t chunks_per_cta = ceil_div(k_chunks, cluster);
+  if (m > 0 && n > 0 && m <= kTileRows && chunks_per_cta <= kSmallMaxChunksPerCta &&
+      m * chunks_per_cta * 4 <= (int64_t)kSmallThreads * kSmallBlocksPerThread) {
+    if (one_pass) *one_pass = true;
+    DynamicScale dyn{scratch, gs_out, gs_other, alpha_out, device_status_word(), release_next ? 1 : 0};
+    const int aligned32 = (reinterpret_cast<uintptr_t>(in) % 32 == 0 && stride % 16 == 0) ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cluster);
+    cfg.blockDim = dim3(kSmallThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NVFP_CUDA(cudaLaunchKernelEx(&cfg, quant_fp4_small_kernel<T>, static_cast<const T*>(in), stride,
+                                 static_cast<uint8_t*>(out_fp4), static_cast<uint8_t*>(out_sf), (int)m, (int)n,
+                                 (int)k_chunks, (int)chunks_per_cta, aligned32, dyn));
+    return NVFP_OK;
+  }
   if (!fits) {
     // too large to keep in registers across the grid: global-scale pass, then quantize pass
     // The quantize launch comes up under the global-scale launch, loads its tiles and waits for the scale.

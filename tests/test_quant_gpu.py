@@ -215,15 +215,16 @@ def test_fused_activation_scales_repeated_calls():
 
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
 def test_one_pass_dynamic_quant_equals_global_scale_then_quantize(dt):
-    """nvfp_dynamic_fp4_quant (maximum, global scale, alpha and quantization in one cooperative launch while the
-    tensor's tiles fit the GPU at once, two launches beyond) must give the bytes of the two-step flow of the
+    """nvfp_dynamic_fp4_quant (maximum, global scale, alpha and quantization by one CTA for decode-sized tensors, in one
+    cooperative launch while the tensor's tiles fit the GPU at once, two launches beyond) must give the bytes of the two-step flow of the
     reference (speed_test.py:46-49): gs = 2688/max|x|, then scaled_fp4_quant(x, gs).  One scratch, zeroed once,
     serves all calls, large and small shapes interleaved."""
     from helpers import capi_dynamic_quant
     scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
     gs_w = torch.tensor([37.25], device="cuda")
     shapes = [(1, 4096), (16, 4096), (128, 14336), (129, 80), (300, 2064), (2368, 4096), (1, 16), (2432, 4096),
-              (4096, 4096), (17, 8192), (8192, 1024)]
+              (4096, 4096), (17, 8192), (8192, 1024), (4, 16384), (3, 16400), (128, 512), (100, 640), (5, 8192),
+              (7, 9360)]
     for i, shape in enumerate(shapes):
         dist = ALL_DISTS[i % len(ALL_DISTS)]
         x = make_input(dist, shape, TORCH_DT[dt], seed=100 + i).cuda()
