@@ -288,6 +288,53 @@ def test_quant_gated_mlp_module():
     assert nv.device_status() == 0
 
 
+def test_model_surgery_replaces_gated_mlp_blocks():
+    """quantize_gated_mlps on a toy Llama-style model: the gate/up/down blocks with a SiLU become QuantGatedMLP with
+    scales calibrated by a run of the unquantized model, other blocks stay, and the model's output stays close."""
+    import torch.nn as nn
+    from nvfp_kernel_b200 import QuantGatedMLP
+    from nvfp_kernel_b200.convert import quantize_gated_mlps
+
+    class MLP(nn.Module):
+        def __init__(self, hidden, inter, act):
+            super().__init__()
+            self.gate_proj = nn.Linear(hidden, inter, bias=False)
+            self.up_proj = nn.Linear(hidden, inter, bias=False)
+            self.down_proj = nn.Linear(inter, hidden, bias=False)
+            self.act_fn = act
+
+        def forward(self, x):
+            return self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))
+
+    class Block(nn.Module):
+        def __init__(self, hidden, inter, act):
+            super().__init__()
+            self.norm = nn.LayerNorm(hidden)
+            self.mlp = MLP(hidden, inter, act)
+
+        def forward(self, x):
+            return x + self.mlp(self.norm(x))
+
+    torch.manual_seed(3)
+    hidden, inter = 256, 704
+    model = nn.Sequential(Block(hidden, inter, nn.SiLU()), Block(hidden, inter, nn.SiLU()), Block(hidden, inter, nn.GELU()))
+    model = model.to(torch.bfloat16).cuda()
+    x = torch.randn(48, hidden).to(torch.bfloat16).cuda()
+    with torch.no_grad():
+        want = model(x)
+    replaced = quantize_gated_mlps(model, lambda: model(x))
+    assert replaced == ["0.mlp", "1.mlp"]
+    assert isinstance(model[0].mlp, QuantGatedMLP) and isinstance(model[1].mlp, QuantGatedMLP)
+    assert not isinstance(model[2].mlp, QuantGatedMLP)            # GELU: left alone
+    assert float(model[0].mlp.act_global_scale) != float(model[1].mlp.act_global_scale)
+    with torch.no_grad():
+        got = model(x)
+    assert got.shape == want.shape
+    assert (got.float() - want.float()).abs().max() < 0.2 * want.float().abs().max()
+    import nvfp_kernel_b200 as nv
+    assert nv.device_status() == 0
+
+
 def test_empty_batches():
     """Zero rows (an empty batch) and zero output columns go through every entry point without a launch that
     touches memory: empty results of the right shape, 2688 as the global scale of an empty activation."""
