@@ -104,13 +104,16 @@ def sweep(batch_size: int, repeats: int):
 
 
 def decode(repeats: int):
-    print(f"{'M':<5} {'K':<7} {'N':<7} {'GEMM (us)':<11} {'GB/s':<9} {'forward (us)':<13} {'graph replay (us)':<13}")
-    print("-" * 76)
+    print(f"{'M':<5} {'K':<7} {'N':<7} {'bf16 mm (us)':<13} {'GEMM (us)':<11} {'GB/s':<9} {'forward (us)':<13} {'graph replay (us)':<13}")
+    print("-" * 90)
     for m in (1, 16, 128):
         for k, n in ((4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096), (8192, 57344)):
             a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
             w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+            wt = w.t()
+            t_bf16 = time_us(lambda: torch.mm(a, wt), repeats)          # the unquantized layer (cuBLAS)
             layer = QuantLinear(k, n, device="cuda").load_weight(w)
+            del wt
             gs = ops.global_scale(a)
             a_fp4, a_sf = ops.scaled_fp4_quant(a, gs)
             alpha = ops.alpha_from_scales(gs, layer.weight_global_scale)
@@ -123,7 +126,7 @@ def decode(repeats: int):
             a_static.copy_(a)
             t_graph = time_us(lambda: layer(a_static), repeats)
             nbytes = n * k * 0.5625 + m * k * 0.5625 + 2.0 * m * n
-            print(f"{m:<5} {k:<7} {n:<7} {t_mm:<11.1f} {nbytes / t_mm / 1e3:<9.0f} {t_fwd:<13.1f} {t_graph:<13.1f}")
+            print(f"{m:<5} {k:<7} {n:<7} {t_bf16:<13.1f} {t_mm:<11.1f} {nbytes / t_mm / 1e3:<9.0f} {t_fwd:<13.1f} {t_graph:<13.1f}")
 
 
 def quant(repeats: int):
