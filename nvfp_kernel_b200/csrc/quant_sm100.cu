@@ -14,6 +14,10 @@
 // and leave as 32 coalesced 16-byte stores instead of the reference's scattered
 // 1-byte stores; every thread keeps four 16-byte loads in flight; padding bytes of
 // the scale tensor are written as zero.
+//
+// Kernels: quant_fp4_kernel<T, BLOCK, DYNAMIC> (the tiled quantizer; DYNAMIC = the global scale is this tensor's own
+// maximum, found in the same cooperative launch), quant_fp4_small_kernel (the same for decode-sized tensors, one
+// cluster), amax_kernel (global scale and alpha of a tensor too large for one pass), rcp_kernel.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
