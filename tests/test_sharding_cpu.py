@@ -143,3 +143,29 @@ def test_gate_up_interleave_layout_and_mlp_shard_granules():
         interleave_gate_up(gate[:24], up[:24])
     with pytest.raises(ValueError):
         shard_range(192, 0, 2, 64, "intermediate_size")      # 96 per rank is not a multiple of 64
+
+
+def test_model_surgery_leaves_models_it_cannot_run_alone():
+    """quantize_gated_mlps / quantize_linear_layers on a CPU model: nothing qualifies (the kernels need CUDA weights),
+    nothing is replaced and the calibration run is not started; SiLU detection by class and by name."""
+    import torch.nn as nn
+    from nvfp_kernel_b200.convert import _is_silu, quantize_gated_mlps, quantize_linear_layers
+
+    class MLP(nn.Module):
+        def __init__(self, act):
+            super().__init__()
+            self.gate_proj = nn.Linear(64, 128, bias=False)
+            self.up_proj = nn.Linear(64, 128, bias=False)
+            self.down_proj = nn.Linear(128, 64, bias=False)
+            self.act_fn = act
+
+    def swish(x):
+        return x * torch.sigmoid(x)
+
+    assert _is_silu(MLP(nn.SiLU())) and _is_silu(MLP(swish)) and not _is_silu(MLP(nn.GELU()))
+    assert not _is_silu(nn.Linear(4, 4))
+    model = nn.Sequential(MLP(nn.SiLU()))
+    called = []
+    assert quantize_gated_mlps(model, lambda: called.append(1)) == [] and not called
+    assert quantize_linear_layers(model) == []
+    assert isinstance(model[0].gate_proj, nn.Linear)
