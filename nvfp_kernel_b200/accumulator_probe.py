@@ -78,22 +78,40 @@ def _split(e: int):
     return pa, e - pa
 
 
+BIG_E = 16                                                  # big term 2^16 = (2^8 scale) * (2^8 scale)
+PLACEMENTS = ("block", "mma", "15 block", "15 mma", "15 neg")
+
+
+def measure(s: int) -> dict:
+    """(result - big) in units of the small term 2^(BIG_E - s), for every placement."""
+    e = BIG_E - s
+    pa, pb = _split(e)
+    big, unit = float(2 ** BIG_E), float(2.0 ** e)
+    return {
+        "block": (_run([(0, 8, 8), (16, pa, pb)]) - big) / unit,
+        "mma": (_run([(0, 8, 8), (64, pa, pb)]) - big) / unit,
+        "15 block": (_run([(0, 8, 8)] + [(16 + i, pa, pb) for i in range(15)]) - big) / unit,
+        "15 mma": (_run([(0, 8, 8)] + [(64 + i, pa, pb) for i in range(15)]) - big) / unit,
+        "15 neg": (-_run([(0, 8, 8)] + [(16 + i, pa, pb) for i in range(15)], negative=True) - big) / unit,
+    }
+
+
+def truncation_model(count: int, s: int) -> int:
+    """What `measure` returns if the `count` small terms are added to the big one EXACTLY and the sum is then
+    truncated toward zero to fp32's 24 significant bits: one fp32 ulp of the big term is 2^(s-23) small units."""
+    if s <= 23:
+        return count
+    step = 1 << (s - 23)
+    return count // step * step
+
+
 def main():
     assert ops.get_active_backend() == "real"
-    big_e = 16                                              # big term 2^16 = (2^8 scale) * (2^8 scale)
-    print(f"big term 2^{big_e}; small term(s) 2^({big_e}-s); entries = (result - big) in units of the small term")
+    print(f"big term 2^{BIG_E}; small term(s) 2^({BIG_E}-s); entries = (result - big) in units of the small term")
     print(f"{'s':>3} {'block':>8} {'mma':>8} {'15 block':>9} {'15 mma':>8} {'15 neg':>8}")
     for s in range(20, 30):
-        e = big_e - s
-        pa, pb = _split(e)
-        big = float(2 ** big_e)
-        unit = float(2.0 ** e)
-        r_block = (_run([(0, 8, 8), (16, pa, pb)]) - big) / unit
-        r_mma = (_run([(0, 8, 8), (64, pa, pb)]) - big) / unit
-        r_many = (_run([(0, 8, 8)] + [(16 + i, pa, pb) for i in range(15)]) - big) / unit
-        r_many_mma = (_run([(0, 8, 8)] + [(64 + i, pa, pb) for i in range(15)]) - big) / unit
-        r_neg = (-_run([(0, 8, 8)] + [(16 + i, pa, pb) for i in range(15)], negative=True) - big) / unit
-        print(f"{s:>3} {r_block:>8.0f} {r_mma:>8.0f} {r_many:>9.0f} {r_many_mma:>8.0f} {r_neg:>8.0f}")
+        r = measure(s)
+        print(f"{s:>3} {r['block']:>8.0f} {r['mma']:>8.0f} {r['15 block']:>9.0f} {r['15 mma']:>8.0f} {r['15 neg']:>8.0f}")
     print("fp32 itself keeps s <= 23 exactly (24-bit significand); s = 24 is the round-to-nearest-even tie.")
 
 

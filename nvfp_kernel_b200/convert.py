@@ -31,7 +31,10 @@ def quantize_linear_layers(model: nn.Module, format: str = "nvfp4", skip: Iterab
                 continue
             if predicate is not None and not predicate(full, child):
                 continue
-            q = QuantLinear.from_linear(child, format=format)
+            # the replacement computes in the model's own 16-bit dtype (an fp16 model keeps fp16 activations; the
+            # reference's logged run is fp16, tmp.log:1-7 there); other dtypes get bf16
+            out_dtype = child.weight.dtype if child.weight.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
+            q = QuantLinear.from_linear(child, format=format, out_dtype=out_dtype)
             if cuda_graph:
                 q.enable_cuda_graph()
             setattr(module, child_name, q)

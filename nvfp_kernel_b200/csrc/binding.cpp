@@ -234,6 +234,21 @@ void scaled_fp4_mm_silu_mul(torch::Tensor& D, c10::optional<torch::Tensor> D_sf,
                                            (int)value_dtype_code, mx ? 1 : 0, current_stream(A)));
 }
 
+// Checks shared by the two entry points that take raw destination addresses (peer GPUs' buffers): a wrong size
+// there is a fault on another GPU, not a Python error, so everything that can be checked on the host is.
+void check_peer_call_operands(torch::Tensor const& A_sf, torch::Tensor const& B_sf, int64_t m, int64_t n, int64_t k, bool mx,
+                              std::vector<int64_t> const& dst_ptrs) {
+  const int block = mx ? 32 : 16;
+  TORCH_CHECK(k % (mx ? 64 : 32) == 0 && n % 32 == 0, "Expected k to be divisible by ", mx ? 64 : 32,
+              " and n by 32, but got k: ", k, ", n: ", n, ".");
+  TORCH_CHECK(A_sf.element_size() * A_sf.numel() == nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, block),
+              "scale_a must be padded and swizzled to ", nvfp_sf_rows_padded(m), "x", nvfp_sf_cols_padded(k, block), " bytes");
+  TORCH_CHECK(B_sf.element_size() * B_sf.numel() == nvfp_sf_rows_padded(n) * nvfp_sf_cols_padded(k, block),
+              "scale_b must be padded and swizzled to ", nvfp_sf_rows_padded(n), "x", nvfp_sf_cols_padded(k, block), " bytes");
+  TORCH_CHECK(!dst_ptrs.empty() && dst_ptrs.size() <= 8, "between 1 and 8 destinations are supported, got ", dst_ptrs.size());
+  for (int64_t p : dst_ptrs) TORCH_CHECK(p != 0 && p % 16 == 0, "destination addresses must be non-null and 16-byte aligned");
+}
+
 // GEMM whose [m, n] result goes to several destinations given as raw device addresses (the local
 // output first, then peer GPUs' buffers): the column-parallel gather fused into the epilogue.
 void scaled_fp4_mm_multi(std::vector<int64_t> const& dst_ptrs, int64_t dst_ld, int64_t out_dtype_code, torch::Tensor const& A,
@@ -246,6 +261,10 @@ void scaled_fp4_mm_multi(std::vector<int64_t> const& dst_ptrs, int64_t dst_ld, i
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.sizes()[1] == B.sizes()[1], "a and b shapes cannot be multiplied");
   TORCH_CHECK(mx || alpha.has_value(), "alpha is required");
   const int64_t m = A.sizes()[0], n = B.sizes()[0], k = A.sizes()[1] * 2;
+  check_peer_call_operands(A_sf, B_sf, m, n, k, mx, dst_ptrs);
+  TORCH_CHECK(out_dtype_code == NVFP_DTYPE_F16 || out_dtype_code == NVFP_DTYPE_BF16 || out_dtype_code == NVFP_DTYPE_F32,
+              "unknown output dtype code ", out_dtype_code);
+  TORCH_CHECK(dst_ld >= n, "destination leading dimension ", dst_ld, " is smaller than n = ", n);
   std::vector<void*> dst;
   for (int64_t p : dst_ptrs) dst.push_back(reinterpret_cast<void*>(p));
   const at::cuda::OptionalCUDAGuard guard(device_of(A));
@@ -267,6 +286,9 @@ void scaled_fp4_mm_scatter_add(std::vector<int64_t> const& dst_ptrs, torch::Tens
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.sizes()[1] == B.sizes()[1], "a and b shapes cannot be multiplied");
   TORCH_CHECK(mx || alpha.has_value(), "alpha is required");
   const int64_t m = A.sizes()[0], n = B.sizes()[0], k = A.sizes()[1] * 2;
+  check_peer_call_operands(A_sf, B_sf, m, n, k, mx, dst_ptrs);
+  TORCH_CHECK(m % (32 * (int64_t)dst_ptrs.size()) == 0, "m = ", m, " must be a multiple of 32 x the number of destinations (",
+              dst_ptrs.size(), ")");
   std::vector<void*> dst;
   for (int64_t p : dst_ptrs) dst.push_back(reinterpret_cast<void*>(p));
   const at::cuda::OptionalCUDAGuard guard(device_of(A));

@@ -23,6 +23,7 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
+#include <mutex>
 #include <type_traits>
 
 #include "common.h"
@@ -152,9 +153,10 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
     gs = gs_ptr ? __ldg(gs_ptr) : 1.0f;
     rcp_gs = rcp_approx_ftz(gs);
   }
-  // NVFP4 uses the hardware reciprocal like the reference; MXFP4 (no reference to
-  // match) uses the correctly rounded constant so that a CPU restatement is exact.
-  const float rcp6 = BLOCK == 16 ? rcp_approx_ftz(6.0f) : __uint_as_float(0x3E2AAAABu);
+  // rcp.approx.ftz(6.0f) like the reference, in both formats (kernel/nvfp4_utils.cuh:192 there; its e8m0 branch,
+  // :196-202, uses the same product).  On sm_100 the instruction returns 0x3E2AAAAB, the correctly rounded 1/6, so a
+  // CPU restatement with that constant is exact (checked on the GPU by the quantizer tests).
+  const float rcp6 = rcp_approx_ftz(6.0f);
 
   Pack16<T> v[kPasses];
 #pragma unroll
@@ -538,16 +540,17 @@ int launch_quant(void* out_fp4, void* out_sf, const void* in, const float* gs, i
 template <typename T>
 int dynamic_quant_capacity(int device, int sm_count) {
   static int cached[64] = {};
+  static std::once_flag once[64];
   if (device < 0 || device >= 64) return 0;
-  if (cached[device] == 0) {
+  std::call_once(once[device], [device, sm_count] {
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_fp4_kernel<T, 16, true>, kThreads, 0) != cudaSuccess)
-      return 0;
+      return;
     // Two tiles per SM at most: measured on B200 inside a layer's forward, 256 tiles (4096 x 1024) take 23.6 us
     // in one pass against 27.6 us in two; at 512 tiles the wait for the slowest CTA costs more than the second
     // read of a tensor that is still in L2 (35.8 against 33.9 us).
     cached[device] = std::max(1, std::min(per_sm, 2) * sm_count);
-  }
+  });
   return cached[device];
 }
 
@@ -744,17 +747,19 @@ static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocScratchWords
 int noalloc_scratch_address(uint32_t** out) {
   constexpr int kMaxDevices = 64;
   static uint32_t* cache[kMaxDevices] = {};
+  static cudaError_t err[kMaxDevices];
+  static std::once_flag once[kMaxDevices];      // two host threads may make the first call on a device together
   int dev = 0;
   NVFP_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail(NVFP_ERR_CUDA, "device index %d out of range", dev);
-  if (!cache[dev]) {
+  std::call_once(once[dev], [dev] {
     uint32_t* ptr = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
-    if (e != cudaSuccess || ptr == nullptr)
-      return fail(NVFP_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed on device %d: %s", dev,
-                  cudaGetErrorString(e));
-    cache[dev] = ptr;
-  }
+    err[dev] = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (err[dev] == cudaSuccess) cache[dev] = ptr;
+  });
+  if (cache[dev] == nullptr)
+    return fail(NVFP_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed on device %d: %s", dev,
+                cudaGetErrorString(err[dev]));
   *out = cache[dev];
   return NVFP_OK;
 }

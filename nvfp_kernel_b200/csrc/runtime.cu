@@ -1,5 +1,6 @@
 // Error reporting, device queries and the device status word of libnvfp_b200.so.
 #include <cstring>
+#include <mutex>
 
 #include "common.h"
 
@@ -20,31 +21,38 @@ int fail(int code, const char* fmt, ...) {
 
 void clear_error() { g_error[0] = '\0'; }
 
+// Per-device caches are filled under std::call_once (one flag per device): two host threads making their first
+// call on a device at the same time both see a complete entry.
 int current_device_info(DeviceInfo* out) {
   static DeviceInfo cache[kMaxDevices];
+  static cudaError_t err[kMaxDevices];
+  static std::once_flag once[kMaxDevices];
   int dev = 0;
   NVFP_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail(NVFP_ERR_CUDA, "device index %d out of range", dev);
-  if (cache[dev].sm_count == 0) {
+  std::call_once(once[dev], [dev] {
     DeviceInfo d;
-    NVFP_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
-    NVFP_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
-    NVFP_CUDA(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+    cudaError_t e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev);
+    err[dev] = e;
     cache[dev] = d;
-  }
+  });
+  if (err[dev] != cudaSuccess)
+    return fail(NVFP_ERR_CUDA, "cudaDeviceGetAttribute failed on device %d: %s", dev, cudaGetErrorString(err[dev]));
   *out = cache[dev];
   return NVFP_OK;
 }
 
 uint32_t* device_status_word() {
   static uint32_t* cache[kMaxDevices] = {};
+  static std::once_flag once[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  if (!cache[dev]) {
+  std::call_once(once[dev], [dev] {
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
-    cache[dev] = static_cast<uint32_t*>(p);
-  }
+    if (cudaGetSymbolAddress(&p, g_status_word) == cudaSuccess) cache[dev] = static_cast<uint32_t*>(p);
+  });
   return cache[dev];
 }
 

@@ -182,7 +182,8 @@ class QuantLinear(nn.Module):
                 if acc_dtype != torch.float32 else self._mm_f32(a_fp4, a_sf, alpha)
         else:
             a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
-            y = ops.mxfp4_scaled_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), acc_dtype, bias=fused_bias)
+            y = ops.mxfp4_scaled_mm(a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), acc_dtype, bias=fused_bias) \
+                if acc_dtype != torch.float32 else self._mm_f32(a_fp4, a_sf, None)
         y = self._combine(y)
         if self.bias is not None and fused_bias is None:
             y = y + (self.bias if y.shape[-1] == self.out_features else self._bias_shard())
@@ -238,10 +239,16 @@ class QuantLinear(nn.Module):
         return y
 
     def _mm_f32(self, a_fp4, a_sf, alpha):
+        """Unrounded fp32 partial product of a K-split layer (the public wrappers only offer fp16 / bf16 outputs,
+        like the reference's); alpha is None for MXFP4."""
         from ._ops_real import _load_scaled_fp4_ops
         out = torch.empty((a_fp4.shape[0], self.weight_fp4.shape[0]), dtype=torch.float32, device=a_fp4.device)
-        _load_scaled_fp4_ops(("cutlass_scaled_fp4_mm",)).cutlass_scaled_fp4_mm(
-            out, a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha)
+        if self.format == "mxfp4":
+            _load_scaled_fp4_ops(("mxfp4_scaled_mm",)).mxfp4_scaled_mm(
+                out, a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha)
+        else:
+            _load_scaled_fp4_ops(("cutlass_scaled_fp4_mm",)).cutlass_scaled_fp4_mm(
+                out, a_fp4, self.weight_fp4, a_sf, self._sf_view(self.weight_sf), alpha)
         return out
 
     def _quantize_activation(self, x2: torch.Tensor):

@@ -49,3 +49,25 @@ def gather_columns_layout(parts: torch.Tensor) -> torch.Tensor:
     """[world, M, N/world] (the layout all_gather_into_tensor produces) -> [M, N]."""
     world, m, n_local = parts.shape
     return parts.permute(1, 0, 2).reshape(m, world * n_local)
+
+
+def zero_scale_padding(sf_swizzled: torch.Tensor, rows: int, k: int, block: int = 16) -> torch.Tensor:
+    """Zeroes, in place, the padding bytes of a swizzled scale tensor [round_up(rows,128), round_up(k/block,4)]: the
+    rows beyond `rows` and the scale columns beyond k/block.  For scale tensors that did not come from this
+    package's quantizers (weights imported from another tool; the reference's own quantizer leaves these bytes
+    uninitialised, nvfp/_ops_real.py:46-54 there).  The GEMM needs it when k is not a multiple of 4*block: the last
+    MMA then covers scale columns past k/block whose operand bytes read as zero, and a non-finite scale byte there
+    (0x7F / 0xFF as ue4m3, 0xFF as ue8m0) would turn 0 * scale into NaN.  Works on CPU and CUDA tensors of any
+    one-byte dtype; returns the tensor."""
+    rows_padded, cols_padded = sf_swizzled.shape
+    if rows_padded % 128 or cols_padded % 4 or rows_padded < rows or cols_padded * block < k:
+        raise ValueError(f"scale tensor {tuple(sf_swizzled.shape)} does not match a padded [{rows}, {k}] operand")
+    raw = sf_swizzled.view(torch.uint8)
+    # [rowTile][kTile][32][4][4] (reference: kernel/nvfp4_utils.cuh:126-153): row = 128*rt + 32*i4 + r32, col = 4*kt + c
+    tiles = raw.reshape(rows_padded // 128, cols_padded // 4, 32, 4, 4)
+    dev = raw.device
+    row = (torch.arange(rows_padded // 128, device=dev).view(-1, 1, 1, 1, 1) * 128 +
+           torch.arange(4, device=dev).view(1, 1, 1, 4, 1) * 32 + torch.arange(32, device=dev).view(1, 1, 32, 1, 1))
+    col = torch.arange(cols_padded // 4, device=dev).view(1, -1, 1, 1, 1) * 4 + torch.arange(4, device=dev).view(1, 1, 1, 1, 4)
+    tiles.masked_fill_((row >= rows) | (col >= k // block), 0)
+    return sf_swizzled

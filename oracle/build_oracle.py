@@ -1,7 +1,10 @@
 """Builds the checkers under oracle/ (test infrastructure; the product never loads them).
 
-  python oracle/build_oracle.py            # C restatement + (if the checkout exists) oracle/_ref
+  python oracle/build_oracle.py            # C restatement + (if a reference checkout is found) oracle/_ref
   python oracle/build_oracle.py --ref /path/to/reference
+
+The reference checkout (huweim/nvfp_kernel) is taken from --ref, else from the environment variable
+NVFP_REFERENCE_ROOT, else from a directory named `reference` beside this repository.
 
   oracle/libnvfp_oracle.so   gcc build of nvfp_oracle.c (CPU restatement, OpenMP)
   oracle/_ref/ref_scaled_fp4_ops.<abi>.so
@@ -25,6 +28,12 @@ C_LIB = os.path.join(HERE, "libnvfp_oracle.so")
 REF_EXT = os.path.join(REF_OUT, "ref_scaled_fp4_ops" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 REF_SOURCES = ["kernel/nvfp4_quant_kernels.cu", "kernel/cuda_utils_kernels.cu", "kernel/reciprocal_kernels.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+
+
+def reference_root() -> str | None:
+    """Where the reference checkout lies: $NVFP_REFERENCE_ROOT, else `reference` beside this repository."""
+    cand = os.environ.get("NVFP_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isfile(os.path.join(cand, "kernel", "nvfp4_utils.cuh")) else None
 
 
 def _digest(paths, extra=()):
@@ -59,10 +68,11 @@ def build_c(force: bool = False) -> str:
     return C_LIB
 
 
-def build_ref(ref_root: str = "/root/reference", force: bool = False) -> str | None:
+def build_ref(ref_root: str | None = None, force: bool = False) -> str | None:
     """Returns the path of the built extension, or None when the checkout is absent
     (the GPU box only has the prebuilt file)."""
-    if not os.path.isdir(os.path.join(ref_root, "kernel")):
+    ref_root = ref_root or reference_root()
+    if ref_root is None or not os.path.isdir(os.path.join(ref_root, "kernel")):
         return REF_EXT if os.path.exists(REF_EXT) else None
     import torch
     from torch.utils.cpp_extension import include_paths, library_paths
@@ -97,7 +107,7 @@ def build_ref(ref_root: str = "/root/reference", force: bool = False) -> str | N
 
 
 if __name__ == "__main__":
-    ref = sys.argv[sys.argv.index("--ref") + 1] if "--ref" in sys.argv else "/root/reference"
+    ref = sys.argv[sys.argv.index("--ref") + 1] if "--ref" in sys.argv else None
     if "--no-c" not in sys.argv:
         print(build_c("--force" in sys.argv))
     print(build_ref(ref, "--force" in sys.argv))

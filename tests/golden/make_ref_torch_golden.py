@@ -53,7 +53,9 @@ def sha(a: np.ndarray) -> str:
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NVFP_REFERENCE_ROOT")
+    if not ref_root:
+        raise SystemExit("usage: make_ref_torch_golden.py /path/to/reference  (or set NVFP_REFERENCE_ROOT)")
     pq = import_reference(ref_root)
     out = {}
 

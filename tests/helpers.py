@@ -2,9 +2,58 @@
 as device buffers, and comparison utilities."""
 from __future__ import annotations
 
+import importlib.util
+import os
+
 import torch
 
 from nvfp_kernel_b200 import _capi
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_REF = []
+
+
+def load_ref_quantizer():
+    """The reference's own CUDA quantizer built for sm_100a (oracle/_ref, recipe oracle/build_oracle.py), or None
+    when it has not been built.  Test infrastructure only."""
+    if not _REF:
+        mod = None
+        d = os.path.join(_ROOT, "oracle", "_ref")
+        names = [f for f in os.listdir(d) if f.startswith("ref_scaled_fp4_ops") and f.endswith(".so")] if os.path.isdir(d) else []
+        if names and torch.cuda.is_available():
+            spec = importlib.util.spec_from_file_location("ref_scaled_fp4_ops", os.path.join(d, names[0]))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+        _REF.append(mod)
+    return _REF[0]
+
+
+def ref_quant(x: torch.Tensor, gs: torch.Tensor):
+    """NVFP4 bytes of the reference kernel: (packed [m, n/2], swizzled scale bytes with 0x55 where it writes nothing)."""
+    ref = load_ref_quantizer()
+    m, n = x.shape
+    out = torch.empty((m, n // 2), dtype=torch.uint8, device="cuda")
+    rm, rn = sf_shape(m, n, 16)
+    sf = torch.full((rm, rn // 4), 0x55555555, dtype=torch.int32, device="cuda")
+    ref.scaled_fp4_quant_sm1xxa(out, x.contiguous(), sf, gs)
+    return out, sf.view(torch.uint8).reshape(rm, rn)
+
+
+def ref_quant_ue8m0(x: torch.Tensor):
+    """The reference's e8m0 branch (16-element blocks, no global scale): (packed, swizzled ue8m0 scale bytes)."""
+    ref = load_ref_quantizer()
+    m, n = x.shape
+    out = torch.empty((m, n // 2), dtype=torch.uint8, device="cuda")
+    rm, rn = sf_shape(m, n, 16)
+    sf = torch.full((rm, rn // 4), 0x55555555, dtype=torch.int32, device="cuda")
+    ref.scaled_fp4_quant_ue8m0(out, x.contiguous(), sf)
+    return out, sf.view(torch.uint8).reshape(rm, rn)
+
+
+def unswizzle_gpu(sf_swz: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    """[rowTile][kTile][32][4][4] bytes -> the valid [rows, cols] scale bytes."""
+    rp, cp = sf_swz.shape
+    return sf_swz.reshape(rp // 128, cp // 4, 32, 4, 4).transpose(1, 3).reshape(rp, cp)[:rows, :cols]
 
 
 def _stream():

@@ -90,3 +90,24 @@ def test_extension_exports_reference_symbols():
     with pytest.raises(RuntimeError, match="missing required"):
         _load_scaled_fp4_ops(("no_such_symbol",))
     assert ext.__name__ == "scaled_fp4_ops"
+
+
+def test_root_ops_shim_and_build_profile():
+    """`import ops` from the repository root resolves the four names the reference's scripts use (ops.py:2-7 and
+    speed_test.py:5 there); setup.py takes NVFP_BUILD_PROFILE like the reference's (setup.py:7-15 there)."""
+    import subprocess
+    import sys
+    import ops
+    import nvfp_kernel_b200.ops as real
+    for name in ("scaled_fp4_quant", "cutlass_scaled_fp4_mm", "get_active_backend", "reciprocal_approximate_ftz_tensor"):
+        assert getattr(ops, name) is getattr(real, name)
+    assert ops.get_active_backend() == "real"
+
+    def run(profile):
+        env = dict(os.environ, NVFP_BUILD_PROFILE=profile)
+        return subprocess.run([sys.executable, "setup.py", "--name"], cwd=ROOT, env=env, capture_output=True, text=True)
+    ok = run("real")
+    assert ok.returncode == 0 and ok.stdout.strip().splitlines()[-1] == "nvfp_kernel_b200", ok.stderr
+    assert run("emulation").returncode == 0                     # accepted, builds the real kernels
+    bad = run("bogus")
+    assert bad.returncode != 0 and "Invalid NVFP_BUILD_PROFILE" in bad.stderr

@@ -83,7 +83,8 @@ def test_cuda_graph_replay_matches_eager_and_handles_several_shapes():
     assert nv.device_status() == 0
 
 
-def test_quantize_linear_layers_of_a_model():
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_quantize_linear_layers_of_a_model(dt):
     import torch.nn as nn
     from nvfp_kernel_b200 import QuantLinear
     from nvfp_kernel_b200.convert import quantize_linear_layers
@@ -93,13 +94,15 @@ def test_quantize_linear_layers_of_a_model():
     model.add_module("act", nn.SiLU())
     model.add_module("down", nn.Linear(512, 256, bias=True))
     model.add_module("lm_head", nn.Linear(256, 96, bias=False))
-    model = model.cuda().to(torch.bfloat16)
-    x = torch.randn(40, 256, device="cuda", dtype=torch.bfloat16)
+    model = model.cuda().to(dt)
+    x = torch.randn(40, 256, device="cuda", dtype=dt)
     dense = model(x)
     names = quantize_linear_layers(model)
     assert names == ["up", "down"] and isinstance(model.up, QuantLinear) and isinstance(model.lm_head, nn.Linear)
+    # the replaced layers keep the model's dtype (an fp16 model must not turn bf16 half-way through)
+    assert model.up.out_dtype == dt and model.down.bias.dtype == dt
     y = model(x)
-    assert y.shape == dense.shape
+    assert y.shape == dense.shape and y.dtype == dt
     assert (y.float() - dense.float()).abs().max() < 0.35 * dense.float().abs().max()
 
 

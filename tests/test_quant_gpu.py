@@ -4,14 +4,13 @@ Bit-exactness authorities, in order: (1) the reference's own CUDA quantizer buil
 sm_100a (oracle/_ref, run live here), (2) its committed outputs (tests/golden/
 ref_kernel_sm100.npz), (3) the CPU oracle replaying the hardware reciprocal.
 """
-import importlib.util
 import os
 
 import numpy as np
 import pytest
 import torch
 
-from helpers import capi_global_scale, capi_mx_quant, capi_quant, capi_rcp, gpu_rcp_table
+from helpers import capi_global_scale, capi_mx_quant, capi_quant, capi_rcp, gpu_rcp_table, load_ref_quantizer
 from inputs import DISTRIBUTIONS, make_input
 from oracle import c_oracle, nvfp_oracle as O
 
@@ -21,20 +20,7 @@ TORCH_DT = {"bf16": torch.bfloat16, "fp16": torch.float16}
 ALL_DISTS = DISTRIBUTIONS + ("zeros_mixed",)
 
 
-def _load_ref():
-    d = os.path.join(ROOT, "oracle", "_ref")
-    if not os.path.isdir(d):
-        return None
-    names = [f for f in os.listdir(d) if f.startswith("ref_scaled_fp4_ops") and f.endswith(".so")]
-    if not names:
-        return None
-    spec = importlib.util.spec_from_file_location("ref_scaled_fp4_ops", os.path.join(d, names[0]))
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    return mod
-
-
-REF = _load_ref() if torch.cuda.is_available() else None
+REF = load_ref_quantizer()
 needs_ref = pytest.mark.skipif(REF is None, reason="oracle/_ref (reference quantizer for sm_100a) not built")
 
 

@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from inputs import make_input
-from nvfp_kernel_b200.sharding import gather_columns_layout, shard_columns, shard_range, shard_rows
+from nvfp_kernel_b200.sharding import gather_columns_layout, shard_columns, shard_range, shard_rows, zero_scale_padding
 from oracle import nvfp_oracle as O
 
 
@@ -30,6 +30,25 @@ def test_shard_range_rejects_ragged_splits():
         shard_range(384, 0, 2, 128, "n")
     with pytest.raises(ValueError):
         shard_range(500, 0, 2, 4, "n")
+
+
+@pytest.mark.parametrize("rows,k,block", [(129, 80, 16), (300, 96, 16), (128, 64, 16), (17, 320, 32), (1, 32, 16)])
+def test_zero_scale_padding_clears_exactly_the_padding(rows, k, block):
+    """A foreign scale tensor with garbage (here: NaN patterns) in its padding: after the helper the valid region
+    is untouched and every padding byte is zero, judged through the oracle's de-swizzle."""
+    rp, cp = (rows + 127) // 128 * 128, (k // block + 3) // 4 * 4
+    rng = np.random.default_rng(5)
+    lin = rng.integers(1, 0x7E, size=(rp, cp), dtype=np.uint8)
+    lin[rows:, :] = 0xFF
+    lin[:, k // block:] = 0x7F
+    swz = torch.from_numpy(O.swizzle_128x4(lin[:rows, :k // block]).copy())
+    # the oracle's swizzle pads with zeros; put the garbage back in through the inverse view
+    full = torch.from_numpy(lin).reshape(rp // 128, 4, 32, cp // 4, 4).permute(0, 3, 2, 1, 4).reshape(rp, cp).contiguous()
+    assert np.array_equal(O.unswizzle_128x4(full.numpy(), rows, k // block), lin[:rows, :k // block])
+    out = zero_scale_padding(full.clone(), rows, k, block)
+    assert np.array_equal(out.numpy(), swz.numpy())
+    with pytest.raises(ValueError):
+        zero_scale_padding(torch.zeros((rp, cp + 1), dtype=torch.uint8), rows, k, block)
 
 
 def test_column_shards_are_slices_of_the_full_quantization():
