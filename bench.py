@@ -243,6 +243,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     peaks = load_peaks()
     n_total = N_PER_GPU * world
     fused = args.gather != "nccl"
+    fp4_gather = args.gather == "fused-fp4" and world > 1
     own_launches = [0]          # this package's kernels launched inside timed regions (counted per call below)
 
     def barrier():
@@ -307,12 +308,19 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     gathered = torch.empty((world * M, N_PER_GPU), dtype=torch.bfloat16, device=dev) if world > 1 else None
     layer.gather_output = fused
 
-    def step(x):
+    fp4_out_gs = [None]                  # calibrated global scale of the gathered output (NVFP4 gather only)
+
+    def step_bf16(x):
         y = layer(x)                     # fused gather: already the full [M, n_total] matrix
         if world > 1 and not fused:
             dist.all_gather_into_tensor(gathered, y)     # layout [world, M, N/world]
             return gathered
         return y
+
+    def step(x):
+        if fp4_gather and fp4_out_gs[0] is not None:
+            return layer.forward_gather_fp4(x, fp4_out_gs[0])[0]      # gathered NVFP4 operand (packed bytes)
+        return step_bf16(x)
 
     sampler = ClockSampler(local_rank)
     launches_per_step = 3 if world == 1 or fused else 4   # amax(+scales), quantize, gemm (+ all-gather)
@@ -326,7 +334,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     parity = None
     if world > 1:
         parity = {}
-        y_gathered = step(a)
+        y_gathered = step_bf16(a)
         if not fused:
             y_gathered = y_gathered.view(world, M, N_PER_GPU).permute(1, 0, 2).reshape(M, n_total)
         y_gathered = y_gathered.clone()
@@ -344,8 +352,20 @@ def main_ours(args, rank: int, world: int, local_rank: int):
         slab_ok, slab_rel = gemm_tolerance(y_gathered[:, rank * N_PER_GPU:(rank + 1) * N_PER_GPU], ref)
         parity["own_slab_max_rel"] = max_over_ranks(slab_rel)
         slab_ok = all_ranks(slab_ok)
-        del ref, y_gathered, a_fp4, a_sf
+        # (c) the gather of the NVFP4 form of the output (quantized in the GEMM epilogue, 0.5625 B per element over
+        # NVLink): bytes and scales of the gathered operand equal the quantizer's on the gathered bf16 matrix
+        out_gs = (2688.0 / y_gathered.abs().max().float()).reshape(1)
+        want_fp4, want_sf = nv.scaled_fp4_quant(y_gathered, out_gs)
+        got_fp4, got_sf = layer.forward_gather_fp4(a, out_gs)
+        fp4_ok = all_ranks(bool(torch.equal(got_fp4, want_fp4)) and
+                           bool(torch.equal(got_sf.view(torch.uint8), want_sf.view(torch.uint8))))
+        parity["fp4_gather_vs_quantizer_on_bf16_gather"] = "bitwise" if fp4_ok else "MISMATCH"
+        fp4_out_gs[0] = out_gs
+        del ref, y_gathered, a_fp4, a_sf, want_fp4, want_sf, got_fp4, got_sf
         torch.cuda.empty_cache()
+        for _ in range(3):
+            layer.forward_gather_fp4(a, out_gs)
+        ms_fp4_gather = timed(lambda: layer.forward_gather_fp4(a, out_gs), args.steps, own_kernels_per_step)
 
     # ---- region 1: whole hot path, activation resident in HBM, exactly --steps steps (burst) -------------------
     with sampler:
@@ -353,11 +373,13 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     flops_step = 2.0 * M * n_total * K
     value = flops_step / (ms_step * 1e-3) / 1e12
 
-    # ---- region 1b: the same step for at least a second: the power cap engages, the clock settles -------------
-    sustained_sampler = sampler.fork()
-    sustained_steps = int(min(20000, max(args.steps, 1.2 / (ms_step * 1e-3))))
-    with sustained_sampler:
-        ms_sustained = timed(lambda: step(a), sustained_steps, own_kernels_per_step)
+    if args.profile_mode:
+        # for profiler captures: the warm-up and the burst region only, so that a capture ends quickly
+        if rank == 0:
+            print(json.dumps({"profile_mode": True, "ms_per_step": ms_step, "value": value, "n_gpus": world}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- region 2: the same steps with an event pair around ONE of the kernels (kernel breakdown) ---
     # calls the same ops QuantLinear.forward makes, one by one; three passes, each timing one kernel of every step
@@ -391,6 +413,12 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     ks = min(args.steps, 200)
     with sampler:
         t_amax, t_quant, t_gemm = timed_pass(0, ks), timed_pass(1, ks), timed_pass(2, ks)
+    # ---- region 2b: the same step for at least a second: the power cap engages, the clock settles -------------
+    sustained_sampler = sampler.fork()
+    sustained_steps = int(min(20000, max(args.steps, 1.2 / (ms_step * 1e-3))))
+    with sustained_sampler:
+        ms_sustained = timed(lambda: step(a), sustained_steps, own_kernels_per_step)
+
     # the GEMM inside a run of at least a second (sustained clock)
     with sustained_sampler:
         t_gemm_sustained = timed_pass(2, int(min(8000, max(ks, 1.2 / (ms_step * 1e-3)))))
@@ -418,7 +446,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
             x = a_full
         else:
             x = x_part
-        y = step(x)
+        y = step_bf16(x)                                         # the host receives bf16 in every mode
         if world == 1:
             return y
         if not fused:
@@ -463,6 +491,13 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     del layer, gathered
     torch.cuda.empty_cache()
     extra = {}
+    if world > 1:
+        extra["fp4_gather"] = {
+            "what": "the same step with the output gathered as NVFP4 (packed nibbles + block scales written by the GEMM "
+                    "epilogue into every rank's operand buffer) instead of bf16",
+            "ms_per_step": ms_fp4_gather, "value": 2.0 * M * n_total * K / (ms_fp4_gather * 1e-3) / 1e12,
+            "gather_bytes_out_per_rank": (world - 1) * M * N_PER_GPU * 9 // 16,
+            "gather_gbs_per_rank": (world - 1) * M * N_PER_GPU * 0.5625 / (ms_fp4_gather * 1e-3) / 1e9}
     x_gu = randn_bf16((M, K), 2)
     cols = torch.randperm(K, generator=torch.Generator().manual_seed(2))[:K // 100].to(dev)
     x_gu[:, cols] *= 50
@@ -505,7 +540,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
         row_ok, row_rel = gemm_tolerance(dn(x_dn), ref)
         parity["row_fused_max_rel" if fused else "row_nccl_max_rel"] = max_over_ranks(row_rel)
         row_ok = all_ranks(row_ok)
-        parity["ok"] = bool(column_ok and slab_ok and row_ok)
+        parity["ok"] = bool(column_ok and slab_ok and row_ok and fp4_ok)
         parity["what"] = ("column: gathered [M, N_total] of this run's gather against the other gather (fused <-> NCCL) "
                           "of the same layer, torch.equal on every rank; own_slab: each rank's columns against the fp32 "
                           "product of the dequantized bytes the kernel consumed; row: Llama-3-70B down projection "
@@ -603,8 +638,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="N>1 only: how the column-parallel outputs are gathered")
+    ap.add_argument("--profile-mode", action="store_true",
+                    help="run only the warm-up and the burst region (for ncu captures of the step's kernels)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "fused-fp4"],
+                    help="N>1 only: how the column-parallel outputs are gathered (fused-fp4: as NVFP4, for a next "
+                         "quantized layer)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -216,6 +216,91 @@ int nvfp_scaled_fp4_mm_scatter_add(void* const* dst, int n_dst, const void* a, c
                                    int mxfp4, void* stream);
 
 /*
+ * Tensor-parallel layers with the ranks synchronised INSIDE the GEMM kernel.  The two entry points above leave it to
+ * the caller to synchronise the ranks before and after the call (two collectives or barrier kernels per layer); the
+ * ones below need nothing around them.  The reference has no distributed code; there is no counterpart.
+ *
+ * A peer group describes the ranks (one process per GPU, 2..8 GPUs of one node) as THIS rank sees them:
+ *   dst[r]    rank r's destination matrix, mapped into this process (peer-mapped for r != rank)
+ *   flags[r]  rank r's flag block: NVFP_PEER_FLAG_WORDS uint32, 128-byte aligned, peer-mapped like dst, zeroed ONCE
+ *             (with all ranks synchronised on the host afterwards) and then owned by the library: ready / done
+ *             announcements and a call counter.  Each destination buffer has its own flag block.  All NULL: no
+ *             in-kernel synchronisation, the caller synchronises as for the entry points above.
+ *   wait_limit_ns  bound of every in-kernel wait on a peer's flag; 0 = two seconds.
+ * Protocol: the kernel announces "ready" to every peer when it starts (nothing on this rank reads this rank's
+ * destination any more: every earlier reader precedes the call in stream order); it writes into a peer's destination
+ * only after that peer's ready; when its last store has been performed it announces "done" and waits for every
+ * peer's done, so that when the kernel has finished, this rank's destination holds every rank's contribution.  All
+ * ranks must make the same sequence of calls on a flag block.  A wait that exceeds the limit (a peer that is late
+ * or gone) sets bit 5 (0x20) of the device status word; the kernel then skips its stores to peers (if it was a
+ * ready wait) and returns: the call's result is incomplete, nothing hangs, and the next call works again once
+ * the peer is back.
+ */
+#define NVFP_MAX_RANKS 8
+#define NVFP_PEER_FLAG_WORDS 32
+typedef struct {
+  int world;
+  int rank;
+  void* dst[NVFP_MAX_RANKS];
+  uint32_t* flags[NVFP_MAX_RANKS];
+  uint64_t wait_limit_ns;
+} nvfp_peer_group_t;
+
+/*
+ * Column-parallel layer, all-gather fused into the GEMM: this rank's [m, n] product is stored into every rank's
+ * gathered matrix.  group->dst[r]: where this rank's slab starts in rank r's [m, dst_ld] row-major matrix (that is,
+ * base + rank * n elements), 16-byte aligned; dst_ld >= n, a multiple of 8.  Otherwise as nvfp_scaled_fp4_mm_multi.
+ */
+int nvfp_scaled_fp4_mm_gather(const nvfp_peer_group_t* group, int64_t dst_ld, const void* a, const void* b,
+                              const void* sfa, const void* sfb, const float* alpha, int64_t m, int64_t n, int64_t k,
+                              int out_dtype, int mxfp4, void* stream);
+
+/*
+ * Row-parallel (K-split) layer, reduce-scatter fused into the GEMM: group->dst[r] is rank r's [m / world, n] fp32
+ * matrix, which owns rows [r*m/world, (r+1)*m/world) of the sum and must be zero when rank r's call starts (zero it
+ * on the same stream before the call: the kernel announces ready after that).  Otherwise as
+ * nvfp_scaled_fp4_mm_scatter_add.
+ */
+int nvfp_scaled_fp4_mm_reduce_scatter(const nvfp_peer_group_t* group, const void* a, const void* b, const void* sfa,
+                                      const void* sfb, const float* alpha, int64_t m, int64_t n, int64_t k, int mxfp4,
+                                      void* stream);
+
+/*
+ * nvfp_linear_forward for a column-parallel layer with the fused gather: quantizer and GEMM chained in one call, the
+ * GEMM's tiles stored into every rank's gathered matrix (group->dst as for nvfp_scaled_fp4_mm_gather).  workspace and
+ * scratch as for nvfp_linear_forward.
+ */
+int nvfp_linear_forward_gather(const nvfp_peer_group_t* group, int64_t dst_ld, const void* x, int64_t m, int64_t k,
+                               int64_t x_row_stride, int x_dtype, const void* w_fp4, const void* w_sf,
+                               const float* w_global_scale, int64_t n, void* workspace, uint32_t* scratch,
+                               int out_dtype, void* stream);
+
+/*
+ * Column-parallel layer whose gathered output is the NEXT layer's NVFP4 activation operand: every tile is quantized in
+ * the epilogue (as nvfp_scaled_fp4_mm_fp4out does, same bytes) and its packed nibbles and scale bytes are stored into
+ * every rank's gathered operand: 0.5625 bytes per element cross NVLink instead of 2.
+ *   group->dst[r]  BASE of rank r's packed matrix, [m, n_total / 2] bytes, 16-byte aligned
+ *   dst_sf[r]      base of rank r's scale tensor, nvfp_sf_rows_padded(m) x (n_total / 16) bytes in the swizzled layout
+ *                  of an [m, n_total] tensor; rows between m and the padded row count receive zeros
+ *   n_offset       first column of this rank's [m, n] slab in the gathered matrix; n, n_offset and n_total are
+ *                  multiples of 64 (whole 512-byte scale chunks per rank)
+ *   out_global_scale  device fp32: the (calibrated) global scale of the gathered tensor, the same on every rank
+ *   bias           n values of value_dtype (fp16 / bf16) or NULL
+ * Synchronisation of the ranks as for nvfp_scaled_fp4_mm_gather.  No counterpart in the reference.
+ */
+int nvfp_scaled_fp4_mm_gather_fp4(const nvfp_peer_group_t* group, void* const* dst_sf, int64_t n_total, int64_t n_offset,
+                                  const void* a, const void* b, const void* sfa, const void* sfb, const float* alpha,
+                                  const void* bias, const float* out_global_scale, int64_t m, int64_t n, int64_t k,
+                                  int value_dtype, int mxfp4, void* stream);
+
+/* The same behind the online activation quantizer, chained in one call (cf. nvfp_linear_forward_gather). */
+int nvfp_linear_forward_gather_fp4(const nvfp_peer_group_t* group, void* const* dst_sf, int64_t n_total, int64_t n_offset,
+                                   const void* x, int64_t m, int64_t k, int64_t x_row_stride, int x_dtype,
+                                   const void* w_fp4, const void* w_sf, const float* w_global_scale, int64_t n,
+                                   const void* bias, const float* out_global_scale, void* workspace, uint32_t* scratch,
+                                   int value_dtype, void* stream);
+
+/*
  * y[i] = rcp.approx.ftz.f32(x[i]).  Replaces reciprocal_approximate_ftz_tensor
  * (kernel/reciprocal_kernels.h:4-5, kernel/reciprocal_kernels.cu:91-121); fp32 only,
  * the one dtype reachable through the reference's Python wrapper (nvfp/ops.py:87-92).

@@ -35,6 +35,12 @@ PROTOTYPES = {
     "nvfp_mxfp4_mm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_scaled_fp4_mm_multi": (_int, [ctypes.POINTER(ctypes.c_void_p), _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp]),
     "nvfp_scaled_fp4_mm_scatter_add": (_int, [ctypes.POINTER(ctypes.c_void_p), _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "nvfp_scaled_fp4_mm_gather": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "nvfp_scaled_fp4_mm_reduce_scatter": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "nvfp_linear_forward_gather": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp]),
+    "nvfp_scaled_fp4_mm_gather_fp4": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "nvfp_linear_forward_gather_fp4": (_int, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _i64, _vp, _vp,
+                                              _vp, _vp, _int, _vp]),
     "nvfp_reciprocal_approximate_ftz": (_int, [_vp, _vp, _i64, _vp]),
     "nvfp_global_scale": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nvfp_activation_scales": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
@@ -52,6 +58,16 @@ PROTOTYPES = {
     "nvfp_device_status": (_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "nvfp_selftest_wait_timeout": (_int, [ctypes.c_uint64, _vp]),
 }
+
+NVFP_MAX_RANKS = 8
+NVFP_PEER_FLAG_WORDS = 32
+
+
+class PeerGroup(ctypes.Structure):
+    """nvfp_peer_group_t of include/nvfp_b200.h."""
+    _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("dst", ctypes.c_void_p * NVFP_MAX_RANKS),
+                ("flags", ctypes.c_void_p * NVFP_MAX_RANKS), ("wait_limit_ns", ctypes.c_uint64)]
+
 
 _lib = None
 

@@ -297,6 +297,141 @@ void scaled_fp4_mm_scatter_add(std::vector<int64_t> const& dst_ptrs, torch::Tens
                                               B_sf.data_ptr(), alpha_ptr, m, n, k, mx ? 1 : 0, current_stream(A)));
 }
 
+// nvfp_peer_group_t from Python: destination and flag-block addresses per rank (raw device addresses, rank order).
+nvfp_peer_group_t make_peer_group(std::vector<int64_t> const& dst_ptrs, std::vector<int64_t> const& flag_ptrs, int64_t rank,
+                                  int64_t wait_limit_ns) {
+  TORCH_CHECK(!dst_ptrs.empty() && dst_ptrs.size() <= NVFP_MAX_RANKS, "between 1 and 8 ranks are supported, got ", dst_ptrs.size());
+  TORCH_CHECK(flag_ptrs.empty() || flag_ptrs.size() == dst_ptrs.size(), "one flag block per rank, or none");
+  TORCH_CHECK(rank >= 0 && rank < (int64_t)dst_ptrs.size(), "rank ", rank, " out of range");
+  TORCH_CHECK(wait_limit_ns >= 0, "negative wait limit");
+  nvfp_peer_group_t g = {};
+  g.world = (int)dst_ptrs.size();
+  g.rank = (int)rank;
+  g.wait_limit_ns = (uint64_t)wait_limit_ns;
+  for (size_t r = 0; r < dst_ptrs.size(); ++r) {
+    TORCH_CHECK(dst_ptrs[r] != 0 && dst_ptrs[r] % 16 == 0, "destination addresses must be non-null and 16-byte aligned");
+    g.dst[r] = reinterpret_cast<void*>(dst_ptrs[r]);
+    if (!flag_ptrs.empty()) {
+      TORCH_CHECK(flag_ptrs[r] != 0 && flag_ptrs[r] % 128 == 0, "flag blocks must be non-null and 128-byte aligned");
+      g.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+    }
+  }
+  return g;
+}
+
+// Column-parallel GEMM with the gather fused in and the ranks synchronised inside the kernel (nvfp_scaled_fp4_mm_gather).
+void scaled_fp4_mm_gather(std::vector<int64_t> const& dst_ptrs, std::vector<int64_t> const& flag_ptrs, int64_t rank,
+                          int64_t wait_limit_ns, int64_t dst_ld, int64_t out_dtype_code, torch::Tensor const& A,
+                          torch::Tensor const& B, torch::Tensor const& A_sf, torch::Tensor const& B_sf,
+                          c10::optional<torch::Tensor> const& alpha, bool mx) {
+  CHECK_OPERAND(A, at::ScalarType::Byte, "a");
+  CHECK_OPERAND(B, at::ScalarType::Byte, "b");
+  TORCH_CHECK(A_sf.is_cuda() && A_sf.is_contiguous() && B_sf.is_cuda() && B_sf.is_contiguous(),
+              "scales must be contiguous CUDA tensors");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.sizes()[1] == B.sizes()[1], "a and b shapes cannot be multiplied");
+  TORCH_CHECK(mx || alpha.has_value(), "alpha is required");
+  const int64_t m = A.sizes()[0], n = B.sizes()[0], k = A.sizes()[1] * 2;
+  check_peer_call_operands(A_sf, B_sf, m, n, k, mx, dst_ptrs);
+  TORCH_CHECK(out_dtype_code == NVFP_DTYPE_F16 || out_dtype_code == NVFP_DTYPE_BF16 || out_dtype_code == NVFP_DTYPE_F32,
+              "unknown output dtype code ", out_dtype_code);
+  TORCH_CHECK(dst_ld >= n, "destination leading dimension ", dst_ld, " is smaller than n = ", n);
+  const nvfp_peer_group_t g = make_peer_group(dst_ptrs, flag_ptrs, rank, wait_limit_ns);
+  const at::cuda::OptionalCUDAGuard guard(device_of(A));
+  const float* alpha_ptr = alpha.has_value() ? static_cast<const float*>(alpha->data_ptr()) : nullptr;
+  check_status(nvfp_scaled_fp4_mm_gather(&g, dst_ld, A.data_ptr(), B.data_ptr(), A_sf.data_ptr(), B_sf.data_ptr(), alpha_ptr,
+                                         m, n, k, (int)out_dtype_code, mx ? 1 : 0, current_stream(A)));
+}
+
+// Row-parallel GEMM with the reduce-scatter fused in, ranks synchronised inside the kernel.
+void scaled_fp4_mm_reduce_scatter(std::vector<int64_t> const& dst_ptrs, std::vector<int64_t> const& flag_ptrs, int64_t rank,
+                                  int64_t wait_limit_ns, torch::Tensor const& A, torch::Tensor const& B,
+                                  torch::Tensor const& A_sf, torch::Tensor const& B_sf,
+                                  c10::optional<torch::Tensor> const& alpha, bool mx) {
+  CHECK_OPERAND(A, at::ScalarType::Byte, "a");
+  CHECK_OPERAND(B, at::ScalarType::Byte, "b");
+  TORCH_CHECK(A_sf.is_cuda() && A_sf.is_contiguous() && B_sf.is_cuda() && B_sf.is_contiguous(),
+              "scales must be contiguous CUDA tensors");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.sizes()[1] == B.sizes()[1], "a and b shapes cannot be multiplied");
+  TORCH_CHECK(mx || alpha.has_value(), "alpha is required");
+  const int64_t m = A.sizes()[0], n = B.sizes()[0], k = A.sizes()[1] * 2;
+  check_peer_call_operands(A_sf, B_sf, m, n, k, mx, dst_ptrs);
+  TORCH_CHECK(m % (32 * (int64_t)dst_ptrs.size()) == 0, "m = ", m, " must be a multiple of 32 x the number of ranks (",
+              dst_ptrs.size(), ")");
+  const nvfp_peer_group_t g = make_peer_group(dst_ptrs, flag_ptrs, rank, wait_limit_ns);
+  const at::cuda::OptionalCUDAGuard guard(device_of(A));
+  const float* alpha_ptr = alpha.has_value() ? static_cast<const float*>(alpha->data_ptr()) : nullptr;
+  check_status(nvfp_scaled_fp4_mm_reduce_scatter(&g, A.data_ptr(), B.data_ptr(), A_sf.data_ptr(), B_sf.data_ptr(), alpha_ptr,
+                                                 m, n, k, mx ? 1 : 0, current_stream(A)));
+}
+
+// Whole forward of a column-parallel NVFP4 layer with the fused gather in one call (nvfp_linear_forward_gather).
+void linear_forward_gather(std::vector<int64_t> const& dst_ptrs, std::vector<int64_t> const& flag_ptrs, int64_t rank,
+                           int64_t wait_limit_ns, int64_t dst_ld, int64_t out_dtype_code, torch::Tensor const& X,
+                           torch::Tensor const& W, torch::Tensor const& W_sf, torch::Tensor const& gs_w,
+                           torch::Tensor& workspace, torch::Tensor& scratch) {
+  TORCH_CHECK(X.dim() == 2 && X.stride(1) == 1, "input must be a matrix with dense rows");
+  CHECK_OPERAND(W, at::ScalarType::Byte, "weight");
+  TORCH_CHECK(W_sf.is_cuda() && W_sf.is_contiguous(), "weight scales must be a contiguous CUDA tensor");
+  TORCH_CHECK(X.is_cuda() && gs_w.is_cuda() && workspace.is_cuda() && scratch.is_cuda(), "all tensors must be CUDA tensors");
+  TORCH_CHECK(gs_w.scalar_type() == at::ScalarType::Float, "weight global scale must be fp32");
+  const int64_t m = X.size(0), k = X.size(1), n = W.size(0);
+  TORCH_CHECK(W.dim() == 2 && W.size(1) * 2 == k, "a and b shapes cannot be multiplied (", m, "x", k, " and ", n, "x",
+              W.size(1) * 2, ")");
+  TORCH_CHECK(k % 32 == 0 && n % 32 == 0, "Expected k and n to be divisible by 32, but got k: ", k, ", n: ", n, ".");
+  TORCH_CHECK(W_sf.element_size() * W_sf.numel() == nvfp_sf_rows_padded(n) * nvfp_sf_cols_padded(k, 16),
+              "scale_b must be padded and swizzled to a shape (", nvfp_sf_rows_padded(n), "x", nvfp_sf_cols_padded(k, 16), ")");
+  TORCH_CHECK(out_dtype_code == NVFP_DTYPE_F16 || out_dtype_code == NVFP_DTYPE_BF16 || out_dtype_code == NVFP_DTYPE_F32,
+              "unknown output dtype code ", out_dtype_code);
+  TORCH_CHECK(dst_ld >= n, "destination leading dimension ", dst_ld, " is smaller than n = ", n);
+  TORCH_CHECK(workspace.element_size() * workspace.numel() >= nvfp_linear_workspace_bytes(m, k), "workspace too small");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 32, "scratch must hold 32 bytes");
+  const nvfp_peer_group_t g = make_peer_group(dst_ptrs, flag_ptrs, rank, wait_limit_ns);
+  const int xdt = dtype_code(X, "Unsupported input data type for quantize_to_fp4.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(X));
+  check_status(nvfp_linear_forward_gather(&g, dst_ld, X.data_ptr(), m, k, m > 1 ? X.stride(0) : k, xdt, W.data_ptr(),
+                                          W_sf.data_ptr(), static_cast<const float*>(gs_w.data_ptr()), n, workspace.data_ptr(),
+                                          static_cast<uint32_t*>(scratch.data_ptr()), (int)out_dtype_code, current_stream(X)));
+}
+
+// Whole forward of a column-parallel NVFP4 layer whose gathered output is NVFP4 (nvfp_linear_forward_gather_fp4).
+// packed_ptrs / sf_ptrs: BASE addresses of every rank's gathered packed matrix and scale tensor, rank order.
+void linear_forward_gather_fp4(std::vector<int64_t> const& packed_ptrs, std::vector<int64_t> const& sf_ptrs,
+                               std::vector<int64_t> const& flag_ptrs, int64_t rank, int64_t wait_limit_ns, int64_t n_total,
+                               int64_t n_offset, int64_t value_dtype_code, torch::Tensor const& X, torch::Tensor const& W,
+                               torch::Tensor const& W_sf, torch::Tensor const& gs_w, c10::optional<torch::Tensor> const& bias,
+                               torch::Tensor const& out_gs, torch::Tensor& workspace, torch::Tensor& scratch) {
+  TORCH_CHECK(X.dim() == 2 && X.stride(1) == 1, "input must be a matrix with dense rows");
+  CHECK_OPERAND(W, at::ScalarType::Byte, "weight");
+  TORCH_CHECK(W_sf.is_cuda() && W_sf.is_contiguous(), "weight scales must be a contiguous CUDA tensor");
+  TORCH_CHECK(X.is_cuda() && gs_w.is_cuda() && out_gs.is_cuda() && workspace.is_cuda() && scratch.is_cuda(),
+              "all tensors must be CUDA tensors");
+  TORCH_CHECK(gs_w.scalar_type() == at::ScalarType::Float && out_gs.scalar_type() == at::ScalarType::Float, "scales must be fp32");
+  const int64_t m = X.size(0), k = X.size(1), n = W.size(0);
+  TORCH_CHECK(W.dim() == 2 && W.size(1) * 2 == k, "a and b shapes cannot be multiplied (", m, "x", k, " and ", n, "x",
+              W.size(1) * 2, ")");
+  TORCH_CHECK(W_sf.element_size() * W_sf.numel() == nvfp_sf_rows_padded(n) * nvfp_sf_cols_padded(k, 16),
+              "scale_b must be padded and swizzled to a shape (", nvfp_sf_rows_padded(n), "x", nvfp_sf_cols_padded(k, 16), ")");
+  TORCH_CHECK(sf_ptrs.size() == packed_ptrs.size(), "one scale tensor per rank");
+  TORCH_CHECK(workspace.element_size() * workspace.numel() >= nvfp_linear_workspace_bytes(m, k), "workspace too small");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 32, "scratch must hold 32 bytes");
+  const void* bias_ptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->dim() == 1 && bias->size(0) == n, "bias must be a contiguous CUDA vector of ", n, " elements");
+    TORCH_CHECK((value_dtype_code == NVFP_DTYPE_BF16 && bias->scalar_type() == at::ScalarType::BFloat16) ||
+                    (value_dtype_code == NVFP_DTYPE_F16 && bias->scalar_type() == at::ScalarType::Half), "bias must have the value dtype");
+    bias_ptr = bias->data_ptr();
+  }
+  const nvfp_peer_group_t g = make_peer_group(packed_ptrs, flag_ptrs, rank, wait_limit_ns);
+  void* sf[NVFP_MAX_RANKS] = {};
+  for (size_t r = 0; r < sf_ptrs.size(); ++r) sf[r] = reinterpret_cast<void*>(sf_ptrs[r]);
+  const int xdt = dtype_code(X, "Unsupported input data type for quantize_to_fp4.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(X));
+  check_status(nvfp_linear_forward_gather_fp4(&g, sf, n_total, n_offset, X.data_ptr(), m, k, m > 1 ? X.stride(0) : k, xdt,
+                                              W.data_ptr(), W_sf.data_ptr(), static_cast<const float*>(gs_w.data_ptr()), n,
+                                              bias_ptr, static_cast<const float*>(out_gs.data_ptr()), workspace.data_ptr(),
+                                              static_cast<uint32_t*>(scratch.data_ptr()), (int)value_dtype_code, current_stream(X)));
+}
+
 // kernel/reciprocal_kernels.cu:91-121 of the reference (fp32, the only reachable dtype).
 void reciprocal_approximate_ftz_tensor(torch::Tensor const& input, torch::Tensor& output) {
   TORCH_CHECK(input.scalar_type() == at::ScalarType::Float, "Input tensor must be float");
@@ -482,6 +617,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scaled_fp4_mm_silu_mul", &scaled_fp4_mm_silu_mul);
   m.def("scaled_fp4_mm_multi", &scaled_fp4_mm_multi);
   m.def("scaled_fp4_mm_scatter_add", &scaled_fp4_mm_scatter_add);
+  m.def("scaled_fp4_mm_gather", &scaled_fp4_mm_gather);
+  m.def("scaled_fp4_mm_reduce_scatter", &scaled_fp4_mm_reduce_scatter);
+  m.def("linear_forward_gather", &linear_forward_gather);
+  m.def("linear_forward_gather_fp4", &linear_forward_gather_fp4);
   m.def("global_scale", &global_scale);
   m.def("activation_scales", &activation_scales);
   m.def("dynamic_scaled_fp4_quant", &dynamic_scaled_fp4_quant);

@@ -32,8 +32,11 @@ struct PairCfg {
   // epilogue staging: per epilogue warp two buffers of 32 rows x 128 bytes (128-byte swizzle)
   static constexpr uint32_t kStoreBufBytes = 32 * 128;
   static constexpr uint32_t kStagingBytes = 4 * 2 * kStoreBufBytes;
-  static constexpr int kStages = (kSmemLimit - 2048 - kStagingBytes) / kStageBytes;
-  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + 2048;
+  // NVFP4-gather epilogue: the scale bytes of one 128-row x 256-column tile (four 512-byte chunks), staged by the four
+  // epilogue warps together
+  static constexpr uint32_t kSfStagingBytes = 4 * 512;
+  static constexpr int kStages = (kSmemLimit - 2048 - kStagingBytes - kSfStagingBytes) / kStageBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kStagingBytes + kSfStagingBytes + 2048;
   // Tensor-memory columns.  Two 256-column accumulators do not fit beside the scale columns, so they
   // OVERLAP: even tiles accumulate in [0,256), odd tiles in [208,464), scales live in [464,512).  The
   // epilogue drains the shared columns [208,256) first and releases the accumulator barrier right
@@ -61,20 +64,52 @@ struct OutMaps {
 //                   into its owner's buffer -- the reduce-scatter fused into the epilogue
 //   kOutFused       the epilogue applies the gated activation (p.act) and / or quantizes to NVFP4 (p.out_gs) and
 //                   stores from registers (finish_row_chunk); no output maps
-constexpr int kOutStoreAll = 0, kOutScatterAdd = 1, kOutFused = 2;
+//   kOutFp4Gather   the tile is quantized to NVFP4 in the epilogue (p.out_gs) and its packed bytes and scale bytes are
+//                   stored to all n_out destinations: the column-parallel gather of the NEXT layer's activation
+//                   operand, 0.5625 bytes per element over NVLink instead of 2
+constexpr int kOutStoreAll = 0, kOutScatterAdd = 1, kOutFused = 2, kOutFp4Gather = 3;
+
+// Scale destinations of kOutFp4Gather, in the order of the output maps: base of each destination's swizzled scale
+// tensor ([rowTile][kTile][512 bytes] of the GATHERED [m, n_total] matrix), and where this rank's columns sit in it.
+struct GatherFp4 {
+  uint8_t* sf[kMaxOutputs];
+  int k_tiles_total;    // 64-column scale tiles per row tile of the gathered matrix
+  int k_tile0;          // first scale tile of this rank's slab
+  int k_tiles_slab;     // scale tiles of this rank's slab (n / 64)
+};
+
+// Synchronisation of the ranks of a tensor-parallel layer INSIDE the GEMM kernel, through flag words in peer-visible
+// memory (plain system-scope stores and loads over NVLink; no collective, no extra launch).  Every rank owns a block of
+// kPeerFlagWords uint32, zeroed once:
+//   [0, 8)   ready[r]   rank r has reached call number ready[r]: nobody on r reads r's destination buffer any more
+//   [8, 16)  done[r]    everything rank r writes into THIS rank's buffer in call number done[r] has arrived
+//   [16]     epilogue warps of this GPU that have finished the current call (reset by the last one)
+//   [17]     number of completed calls (the sequence number; kept on the device so that a replayed launch still counts)
+// At its start a kernel announces ready on every peer; an epilogue warp waits for a peer's ready before its first
+// store to that peer; the last epilogue warp to finish announces done on every peer and waits for every peer's done,
+// so the gathered (or reduced) result is complete when the kernel ends.  Every wait is bounded: on expiry the warp
+// records kErrPeerWait in the device status word and goes on -- without its remote stores, if the wait was for ready.
+constexpr int kPeerFlagWords = 32;
+constexpr uint32_t kErrPeerWait = 32u;
+struct PeerSync {
+  uint32_t* flags[kMaxOutputs];   // rank r's flag block (peer-mapped for r != rank)
+  int world;                      // 0: the caller synchronises the ranks around the call
+  int rank;
+  uint64_t limit_ns;              // bound of each wait
+};
 
 template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                      const __grid_constant__ OutMaps out_maps, const int n_out, const int rows_per_owner,
-                     const GemmParams p) {
+                     const GemmParams p, const PeerSync sync, const GatherFp4 gq) {
   using C = PairCfg<MX>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kStagingBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kStagingBytes + C::kSfStagingBytes);
   constexpr int kFull = 0, kEmpty = C::kStages, kAccFull = 2 * C::kStages, kAccEmpty = kAccFull + 1,
-                kDrain = kAccEmpty + 1, kNumBars = kDrain + 1;
+                kDrain = kAccEmpty + 1, kEpiStart = kDrain + 1, kEpiEnd = kEpiStart + 1, kNumBars = kEpiEnd + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* never_set = tmem_slot + 2;
@@ -85,6 +120,16 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t smem_base = smem_u32(smem);
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
+  // number of this call among the calls that share the flag blocks (read by every thread before any epilogue warp of
+  // this grid can finish, hence before the last one advances the stored count)
+  uint32_t peer_seq = 0;
+  if (sync.world > 1) {
+    peer_seq = ld_acquire_sys(sync.flags[sync.rank] + 17) + 1u;
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+      for (int r = 0; r < sync.world; ++r)
+        if (r != sync.rank) st_release_sys(sync.flags[r] + sync.rank, peer_seq);     // ready[rank] on rank r
+  }
+
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(bar(kFull + i), 1);     // armed by the leader's producer for the bytes of BOTH CTAs
@@ -93,6 +138,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     mbar_init(bar(kAccFull), 1);        // one commit from the leader's issuer
     mbar_init(bar(kAccEmpty), 8);       // 4 epilogue warps x 2 CTAs (used in the leader)
     mbar_init(bar(kDrain), 1);
+    mbar_init(bar(kEpiStart), 4);       // the four epilogue warps of this CTA, once per tile (kOutFp4Gather)
+    mbar_init(bar(kEpiEnd), 4);
     *abort_flag = 0;
     *never_set = 0;
     fence_mbar_init();
@@ -276,12 +323,15 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (p.after_producer) griddep_wait();   // alpha comes from the kernel before this one
     const float alpha = p.alpha ? *reinterpret_cast<const volatile float*>(p.alpha) : 1.0f;
     const OutT* bias = static_cast<const OutT*>(p.bias);
-    const float out_gs = (OUT_MODE == kOutFused && p.out_gs) ? __ldg(p.out_gs) : 1.0f;
+    const float out_gs = ((OUT_MODE == kOutFused || OUT_MODE == kOutFp4Gather) && p.out_gs) ? __ldg(p.out_gs) : 1.0f;
     const float rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
     const uint32_t acc_empty_leader = map_to_cta(bar(kAccEmpty), 0);
     const uint32_t staging = smem_base + C::kStages * C::kStageBytes + (uint32_t)(warp - 2) * 2 * C::kStoreBufBytes;
     uint32_t store_count = 0;
     int it = 0;
+    // destinations in other GPUs' memory are written only once their owners have announced ready (lane 0 decides:
+    // it issues the stores)
+    bool peers_asked = sync.world <= 1, remote_ok = true;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull), (uint32_t)it & 1u, abort_flag))) {
@@ -293,6 +343,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int row0 = tm * kPairBM + (int)rank * 128 + q * 32;
       const bool odd = (it & 1) != 0;
       const uint32_t t_row = tmem_base + (odd ? C::kOddAccCol : 0u) + ((uint32_t)(q * 32) << 16);
+      bool bail = false;
 #pragma unroll 1
       for (int i = 0; i < kSteps; ++i) {
         // Even tiles drain from the last columns down, odd tiles from the first up: either way the
@@ -314,6 +365,75 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           else finish_row_chunk<OutT, 64, false>(p, r, alpha, bias, row0 + lane, tn * kPairBN + c * kCols, out_gs, rcp_out_gs, rcp6);
           continue;
         }
+        if constexpr (OUT_MODE == kOutFp4Gather) {
+          // A warp's 32 rows x 256 columns of a tile are 32 x 128 bytes of packed nibbles: ONE 128-byte-swizzled box,
+          // filled 32 bytes per row and step and stored once per destination when the tile is done (two boxes per
+          // warp, alternating by tile).  The tile's scale bytes -- 128 rows x 16, four 512-byte chunks of the
+          // swizzled layout, contiguous in memory -- are staged by the four warps together and leave as one bulk
+          // copy per destination, issued by the first epilogue warp.
+          static_assert(kCols == 64, "16-bit value type");
+          const uint32_t fp4_buf = staging + (uint32_t)(it & 1) * C::kStoreBufBytes;
+          const uint32_t sf_buf = smem_base + C::kStages * C::kStageBytes + C::kStagingBytes;
+          if (i == 0) {
+            // this warp's box of two tiles ago, and (first epilogue warp) the previous tile's scale copies, have
+            // been read out of shared memory; all four warps know before anyone overwrites the scale chunks
+            if (lane == 0) {
+              bulk_wait_group_read<1>();
+              mbar_arrive(bar(kEpiStart));
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(kEpiStart), (uint32_t)it & 1u, abort_flag))) {
+              *abort_flag = 1;
+              if (lane == 0) atomicOr(p.status, kErrEpilogue);
+              bail = true;
+              break;
+            }
+          }
+          uint2 qv[4];
+          uint32_t sf_word;
+          quantize_row_chunk_to_regs<OutT, 64>(p, r, alpha, bias, row0 + lane, tn * kPairBN + c * kCols, out_gs, rcp_out_gs,
+                                               rcp6, qv, sf_word);
+          st_shared_v4(fp4_buf + (uint32_t)lane * 128u + (uint32_t)(((2 * c) ^ (lane & 7)) << 4),
+                       make_uint4(qv[0].x, qv[0].y, qv[1].x, qv[1].y));
+          st_shared_v4(fp4_buf + (uint32_t)lane * 128u + (uint32_t)(((2 * c + 1) ^ (lane & 7)) << 4),
+                       make_uint4(qv[2].x, qv[2].y, qv[3].x, qv[3].y));
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(sf_buf + (uint32_t)c * 512u + (uint32_t)lane * 16u + (uint32_t)q * 4u),
+                       "r"(sf_word) : "memory");
+          if (i == kSteps - 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kEpiEnd));
+            bool chunks_staged = true;
+            if (warp == 2) chunks_staged = __all_sync(0xffffffffu, mbar_wait_bounded(bar(kEpiEnd), (uint32_t)it & 1u, abort_flag));
+            if (lane == 0) {
+              if (!peers_asked) {
+                peers_asked = true;
+                for (int rr = 0; rr < sync.world; ++rr)
+                  if (rr != sync.rank && !wait_flag_reached(sync.flags[sync.rank] + rr, peer_seq, sync.limit_ns)) remote_ok = false;
+                if (!remote_ok) atomicOr(p.status, kErrPeerWait);
+              }
+              const int n_store = remote_ok ? n_out : 1;
+              if (warp == 2 && chunks_staged) {
+                const int row_tile = tm * 2 + (int)rank, chunks = min(4, gq.k_tiles_slab - tn * 4);
+                if (row_tile * 128 < p.m && chunks > 0) {
+                  const int64_t off = ((int64_t)row_tile * gq.k_tiles_total + gq.k_tile0 + tn * 4) * 512;
+                  for (int o = 0; o < n_store; ++o)
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(gq.sf[o] + off), "r"(sf_buf), "r"((uint32_t)chunks * 512u) : "memory");
+                }
+                bulk_commit_group();      // committed BEFORE this warp's box: the wait at the next tile's start covers it
+              }
+              for (int o = 0; o < n_store; ++o)
+                tma_store_2d(&out_maps.map[o], fp4_buf, tn * (kPairBN / 2), row0);
+              bulk_commit_group();
+            }
+            if (!chunks_staged) {
+              *abort_flag = 1;
+              if (lane == 0) atomicOr(p.status, kErrEpilogue);
+              bail = true;
+            }
+          }
+          continue;
+        }
         // the buffer used two steps ago must have been read out by its TMA store
         const uint32_t buf = staging + (store_count & 1u) * C::kStoreBufBytes;
         if (lane == 0) bulk_wait_group_read<1>();
@@ -328,20 +448,45 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
+          if (!peers_asked) {
+            peers_asked = true;
+            for (int r = 0; r < sync.world; ++r)
+              if (r != sync.rank && !wait_flag_reached(sync.flags[sync.rank] + r, peer_seq, sync.limit_ns)) remote_ok = false;
+            if (!remote_ok) atomicOr(p.status, kErrPeerWait);
+          }
           if constexpr (OUT_MODE == kOutScatterAdd) {
-            const int owner = row0 / rows_per_owner;
-            if (owner < n_out)
+            const int owner = row0 / rows_per_owner;     // destinations are in rank order here
+            if (owner < n_out && (remote_ok || sync.world <= 1 || owner == sync.rank))
               tma_reduce_add_2d(&out_maps.map[owner], buf, tn * kPairBN + c * kCols, row0 - owner * rows_per_owner);
           } else {
-            for (int o = 0; o < n_out; ++o)
+            // destination 0 is this GPU's own buffer, the others are the peers'
+            const int n_store = remote_ok ? n_out : 1;
+            for (int o = 0; o < n_store; ++o)
               tma_store_2d(&out_maps.map[o], buf, tn * kPairBN + c * kCols, row0);
           }
           bulk_commit_group();
         }
         ++store_count;
       }
+      if (bail) break;
     }
     if (lane == 0) bulk_wait_group<0>();    // all stores performed before the CTA may exit
+    if (sync.world > 1 && lane == 0) {
+      // this warp's stores have been performed; the last warp of the grid to get here tells the peers and waits for them
+      __threadfence_system();
+      uint32_t* mine = sync.flags[sync.rank];
+      if (atomicAdd(mine + 16, 1u) == gridDim.x * 4u - 1u) {
+        __threadfence_system();
+        mine[16] = 0u;
+        mine[17] = peer_seq;
+        for (int r = 0; r < sync.world; ++r)
+          if (r != sync.rank) st_release_sys(sync.flags[r] + 8 + sync.rank, peer_seq);   // done[rank] on rank r
+        bool all = true;
+        for (int r = 0; r < sync.world; ++r)
+          if (r != sync.rank && !wait_flag_reached(mine + 8 + r, peer_seq, sync.limit_ns)) all = false;
+        if (!all) atomicOr(p.status, kErrPeerWait);
+      }
+    }
     __syncwarp();
   }
 
@@ -388,11 +533,27 @@ int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, in
   return NVFP_OK;
 }
 
+// Row-major [rows, bytes_per_row] packed NVFP4 output (one rank's slab inside a wider matrix with row pitch ld_bytes);
+// box = 128 bytes x 32 rows, 128-byte swizzle.
+inline int make_packed_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t bytes_per_row, int64_t ld_bytes) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)bytes_per_row, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+  const cuuint32_t box[2] = {128, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled (packed output) failed with code %d", (int)r);
+  return NVFP_OK;
+}
+
 // `outputs`: n_out destination matrices with leading dimension ld: [m, n] each (kOutStoreAll; outputs[0]
 // is normally p.d) or [m / n_out, n] each (kOutScatterAdd).
 template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 int launch_pair(const GemmParams& base, const void* a, const void* b, void* const* outputs, int n_out,
-                int64_t ld, int sm_count, cudaStream_t stream) {
+                int64_t ld, int sm_count, cudaStream_t stream, const PeerSync* peer_sync = nullptr,
+                const GatherFp4* gather_fp4 = nullptr) {
   using C = PairCfg<MX>;
   GemmParams p = base;
   p.tiles_m = (int)ceil_div(p.m, kPairBM);
@@ -405,9 +566,14 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   OutMaps out_maps;
   memset(&out_maps, 0, sizeof(out_maps));
   const int rows_per_owner = OUT_MODE == kOutScatterAdd ? p.m / n_out : p.m;
-  if constexpr (OUT_MODE != kOutFused)
+  if constexpr (OUT_MODE == kOutFp4Gather) {
+    // outputs[o]: where this rank's packed slab starts in destination o's [m, ld / 2]-byte matrix
+    for (int o = 0; o < n_out; ++o)
+      if (int rc = make_packed_output_map(&out_maps.map[o], outputs[o], p.m, p.n / 2, ld / 2)) return rc;
+  } else if constexpr (OUT_MODE != kOutFused) {
     for (int o = 0; o < n_out; ++o)
       if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], rows_per_owner, p.n, ld)) return rc;
+  }
   auto kernel = fp4_gemm_pair_kernel<MX, OutT, OUT_MODE>;
   NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
@@ -426,6 +592,12 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.after_producer ? 2 : 1;
-  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, out_maps, n_out, rows_per_owner, p));
+  PeerSync sync;
+  memset(&sync, 0, sizeof(sync));
+  if (peer_sync) sync = *peer_sync;
+  GatherFp4 gq;
+  memset(&gq, 0, sizeof(gq));
+  if (gather_fp4) gq = *gather_fp4;
+  NVFP_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_sfa, map_sfb, out_maps, n_out, rows_per_owner, p, sync, gq));
   return NVFP_OK;
 }

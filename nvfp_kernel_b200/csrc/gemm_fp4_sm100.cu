@@ -157,6 +157,35 @@ __device__ __forceinline__ float silu_mul_16bit(float g, float u) {
   else return __bfloat162float(__float2bfloat16_rn(s)) * u;
 }
 
+// NCOLS consecutive accumulators of one row -> alpha * acc (+ bias) rounded to OutT -> NVFP4: NCOLS / 16 blocks of
+// 8 bytes and their scale bytes (block b in bits [8b, 8b+8) of sf_word), exactly as the quantizer kernel would
+// quantize that OutT tensor.  Rows at or beyond p.m get zero scale bytes (padding of the scale tensor).
+template <typename OutT, int NCOLS>
+__device__ __forceinline__ void quantize_row_chunk_to_regs(const GemmParams& p, const uint32_t* r, float alpha, const OutT* bias,
+                                                           int row, int col0, float gs, float rcp_gs, float rcp6,
+                                                           uint2 (&q)[NCOLS / 16], uint32_t& sf_word) {
+  static_assert(sizeof(OutT) == 2, "16-bit values only");
+  using V2 = typename Vec2<OutT>::type;
+  uint32_t w[NCOLS / 2];
+#pragma unroll
+  for (int piece = 0; piece < NCOLS / 8; ++piece) {
+    const int colj = col0 + 8 * piece;
+    const uint4 o = scale_bias_pack<OutT>(&r[8 * piece], alpha, (bias && colj < p.n) ? bias + colj : nullptr);
+    w[4 * piece + 0] = o.x; w[4 * piece + 1] = o.y; w[4 * piece + 2] = o.z; w[4 * piece + 3] = o.w;
+  }
+  sf_word = 0;
+#pragma unroll
+  for (int b = 0; b < NCOLS / 16; ++b) {
+    V2 h2[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h2[i] = *reinterpret_cast<const V2*>(&w[8 * b + i]);
+    uint8_t sf;
+    q[b] = nvfp4_quantize_block<OutT>(h2, gs, rcp_gs, rcp6, sf);
+    sf_word |= (uint32_t)sf << (8 * b);
+  }
+  if (row >= p.m) sf_word = 0;
+}
+
 // Everything the epilogue can do to NCOLS (64 or 32) consecutive columns of one row beyond a plain store.
 //   values   alpha * acc (+ bias), rounded to OutT (fp16 / bf16)
 //   ACT      gated activation: the columns come in groups of 32, 16 "gate" columns followed by their 16 "up" columns
@@ -544,7 +573,7 @@ template <bool MX>
 int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream,
               const void* bias = nullptr, bool after_producer = false, const float* out_gs = nullptr,
-              void* out_sf = nullptr, int act = 0, bool release_next = false) {
+              void* out_sf = nullptr, int act = 0, bool release_next = false, const PeerSync* peer_sync = nullptr) {
   NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
   const bool fused = out_gs != nullptr || act != 0;
   if (fused) {
@@ -606,7 +635,9 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
       default: return launch_skinny<MX, float>(p, a, b, info.sm_count, stream, after_producer);
     }
   }
-  p.after_producer = (after_producer && n_out == 1) ? 1 : 0;   // the kernels below fetch only B before they wait
+  // the kernels below fetch only B before they wait; several destinations only when the ranks are synchronised inside
+  // the kernel (a caller that synchronises them around the call does so with launches of its own in between)
+  p.after_producer = (after_producer && (n_out == 1 || peer_sync != nullptr)) ? 1 : 0;
   // Large problems: CTA pairs on 256 x 256 tiles (least operand traffic per flop).
   const int64_t pair_tiles = ceil_div(m, kPairBM) * ceil_div(n, kPairBN);
   if (n_out > 1 || ld != n || (m > 128 && n >= 256 && pair_tiles >= info.sm_count / 2)) {
@@ -615,9 +646,9 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
                  ? launch_pair<MX, __nv_bfloat16, kOutFused>(p, a, b, outputs, n_out, ld, info.sm_count, stream)
                  : launch_pair<MX, __half, kOutFused>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
     switch (out_dtype) {
-      case NVFP_DTYPE_BF16: return launch_pair<MX, __nv_bfloat16>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
-      case NVFP_DTYPE_F16: return launch_pair<MX, __half>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
-      default: return launch_pair<MX, float>(p, a, b, outputs, n_out, ld, info.sm_count, stream);
+      case NVFP_DTYPE_BF16: return launch_pair<MX, __nv_bfloat16>(p, a, b, outputs, n_out, ld, info.sm_count, stream, peer_sync);
+      case NVFP_DTYPE_F16: return launch_pair<MX, __half>(p, a, b, outputs, n_out, ld, info.sm_count, stream, peer_sync);
+      default: return launch_pair<MX, float>(p, a, b, outputs, n_out, ld, info.sm_count, stream, peer_sync);
     }
   }
   // Tile-width choice: 256-wide tiles halve the shared-memory traffic per flop but have a single accumulator
@@ -804,10 +835,11 @@ extern "C" int nvfp_scaled_fp4_mm_multi(void* const* dst, int n_dst, const void*
                : scaled_mm<false>(dst, n_dst, dst_ld, a, b, sfa, sfb, alpha, m, n, k, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int nvfp_scaled_fp4_mm_scatter_add(void* const* dst, int n_dst, const void* a, const void* b,
-                                              const void* sfa, const void* sfb, const float* alpha, int64_t m,
-                                              int64_t n, int64_t k, int mxfp4, void* stream) {
-  clear_error();
+namespace nvfp {
+namespace {
+
+int scatter_add(void* const* dst, int n_dst, const void* a, const void* b, const void* sfa, const void* sfb,
+                const float* alpha, int64_t m, int64_t n, int64_t k, int mxfp4, cudaStream_t st, const PeerSync* peer_sync) {
   NVFP_REQUIRE(dst != nullptr && n_dst >= 1 && n_dst <= kMaxOutputs, "between 1 and %d destinations are supported, got %d",
                kMaxOutputs, n_dst);
   NVFP_REQUIRE(m > 0 && n > 0 && k > 0 && m % (32 * n_dst) == 0,
@@ -833,7 +865,199 @@ extern "C" int nvfp_scaled_fp4_mm_scatter_add(void* const* dst, int n_dst, const
   p.sfb_row_tiles = (int)ceil_div(n, 128);
   p.status = device_status_word();
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
+  return mxfp4 ? launch_pair<true, float, kOutScatterAdd>(p, a, b, dst, n_dst, n, info.sm_count, st, peer_sync)
+               : launch_pair<false, float, kOutScatterAdd>(p, a, b, dst, n_dst, n, info.sm_count, st, peer_sync);
+}
+
+// Checks a peer group and turns it into the kernel's view: `rotated` receives the destinations starting with this
+// rank's own (the order in which an epilogue warp walks them, so that at any moment the ranks write to different
+// peers), `sync` the flag blocks (world = 0 when the group has none: the caller synchronises).
+int unpack_peer_group(const nvfp_peer_group_t* g, void** rotated, PeerSync* sync) {
+  NVFP_REQUIRE(g != nullptr, "peer group is null");
+  NVFP_REQUIRE(g->world >= 1 && g->world <= kMaxOutputs && g->rank >= 0 && g->rank < g->world,
+               "peer group: world %d (1..%d) / rank %d out of range", g->world, kMaxOutputs, g->rank);
+  memset(sync, 0, sizeof(*sync));
+  bool any = false, all = true;
+  for (int r = 0; r < g->world; ++r) {
+    NVFP_REQUIRE(g->dst[r] != nullptr, "peer group: destination of rank %d is null", r);
+    any = any || g->flags[r] != nullptr;
+    all = all && g->flags[r] != nullptr && (reinterpret_cast<uintptr_t>(g->flags[r]) & 127) == 0;
+    rotated[r] = g->dst[(g->rank + r) % g->world];
+  }
+  NVFP_REQUIRE(!any || all, "peer group: flag blocks must be given for every rank (128-byte aligned) or for none");
+  if (any && g->world > 1) {
+    for (int r = 0; r < g->world; ++r) sync->flags[r] = g->flags[r];
+    sync->world = g->world;
+    sync->rank = g->rank;
+    sync->limit_ns = g->wait_limit_ns ? g->wait_limit_ns : 2000000000ull;
+    NVFP_REQUIRE(sync->limit_ns <= 10000000000ull, "peer group: wait limit above 10 s");
+  }
+  return NVFP_OK;
+}
+
+}  // namespace
+}  // namespace nvfp
+
+namespace nvfp {
+namespace {
+// Column-parallel GEMM whose result leaves as NVFP4 into every rank's gathered operand (packed bytes + scales).
+int gather_fp4(const nvfp_peer_group_t* g, void* const* dst_sf, int64_t n_total, int64_t n_offset, const void* a,
+               const void* b, const void* sfa, const void* sfb, const float* alpha, const void* bias, const float* out_gs,
+               int64_t m, int64_t n, int64_t k, int value_dtype, int mxfp4, cudaStream_t stream, bool after_producer) {
+  void* rotated[kMaxOutputs];
+  PeerSync sync;
+  if (int rc = unpack_peer_group(g, rotated, &sync)) return rc;
+  NVFP_REQUIRE(dst_sf != nullptr && out_gs != nullptr, "scale destinations or output global scale are null");
+  NVFP_REQUIRE(value_dtype == NVFP_DTYPE_F16 || value_dtype == NVFP_DTYPE_BF16,
+               "the product is rounded to fp16 or bf16 before it is quantized (dtype code %d)", value_dtype);
+  NVFP_REQUIRE(m > 0 && n > 0 && k > 0 && m < (1ll << 31) && n_total < (1ll << 31) && k < (1ll << 31), "bad shape");
+  NVFP_REQUIRE(k % (mxfp4 ? 64 : 32) == 0, "Expected k to be divisible by %d, but got k: %lld.", mxfp4 ? 64 : 32, (long long)k);
+  NVFP_REQUIRE(n % 64 == 0 && n_offset % 64 == 0 && n_total % 64 == 0 && n_offset >= 0 && n_offset + n <= n_total,
+               "slab [%lld, %lld) of %lld columns: offsets and widths must be multiples of 64 (whole scale chunks)",
+               (long long)n_offset, (long long)(n_offset + n), (long long)n_total);
+  NVFP_REQUIRE(mxfp4 || alpha != nullptr, "alpha pointer is null");
+  NVFP_REQUIRE(a && b && sfa && sfb, "null pointer");
+  NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
+  GatherFp4 gq;
+  memset(&gq, 0, sizeof(gq));
+  for (int o = 0; o < g->world; ++o) {
+    const int r = (g->rank + o) % g->world;
+    NVFP_REQUIRE(dst_sf[r] != nullptr && (reinterpret_cast<uintptr_t>(dst_sf[r]) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(g->dst[r]) & 15) == 0,
+                 "destination %d: packed matrix and scale tensor must be non-null and 16-byte aligned", r);
+    gq.sf[o] = static_cast<uint8_t*>(dst_sf[r]);
+    rotated[o] = static_cast<uint8_t*>(g->dst[r]) + n_offset / 2;
+  }
+  gq.k_tiles_total = (int)(n_total / 64);
+  gq.k_tile0 = (int)(n_offset / 64);
+  gq.k_tiles_slab = (int)(n / 64);
+  DeviceInfo info;
+  if (int rc = current_device_info(&info)) return rc;
+  if (info.cc_major != 10)
+    return fail(NVFP_ERR_UNSUPPORTED, "No compiled nvfp4 mm kernel for compute capability %d.%d (needs sm_100)",
+                info.cc_major, info.cc_minor);
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.alpha = alpha;
+  p.bias = bias;
+  p.out_gs = out_gs;
+  p.d = rotated[0];
+  p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.sf_k_chunks = (int)ceil_div(k / (mxfp4 ? 32 : 16), 4);
+  p.sfb_row_tiles = (int)ceil_div(n, 128);
+  p.after_producer = after_producer ? 1 : 0;
+  p.status = device_status_word();
+  NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
+  const PeerSync* ps = sync.world > 1 ? &sync : nullptr;
+  if (value_dtype == NVFP_DTYPE_BF16)
+    return mxfp4 ? launch_pair<true, __nv_bfloat16, kOutFp4Gather>(p, a, b, rotated, g->world, n_total, info.sm_count, stream, ps, &gq)
+                 : launch_pair<false, __nv_bfloat16, kOutFp4Gather>(p, a, b, rotated, g->world, n_total, info.sm_count, stream, ps, &gq);
+  return mxfp4 ? launch_pair<true, __half, kOutFp4Gather>(p, a, b, rotated, g->world, n_total, info.sm_count, stream, ps, &gq)
+               : launch_pair<false, __half, kOutFp4Gather>(p, a, b, rotated, g->world, n_total, info.sm_count, stream, ps, &gq);
+}
+}  // namespace
+}  // namespace nvfp
+
+extern "C" int nvfp_scaled_fp4_mm_gather_fp4(const nvfp_peer_group_t* group, void* const* dst_sf, int64_t n_total,
+                                             int64_t n_offset, const void* a, const void* b, const void* sfa,
+                                             const void* sfb, const float* alpha, const void* bias,
+                                             const float* out_global_scale, int64_t m, int64_t n, int64_t k,
+                                             int value_dtype, int mxfp4, void* stream) {
+  clear_error();
+  return gather_fp4(group, dst_sf, n_total, n_offset, a, b, sfa, sfb, alpha, bias, out_global_scale, m, n, k, value_dtype,
+                    mxfp4, static_cast<cudaStream_t>(stream), false);
+}
+
+extern "C" int nvfp_linear_forward_gather_fp4(const nvfp_peer_group_t* group, void* const* dst_sf, int64_t n_total,
+                                              int64_t n_offset, const void* x, int64_t m, int64_t k, int64_t x_row_stride,
+                                              int x_dtype, const void* w_fp4, const void* w_sf,
+                                              const float* w_global_scale, int64_t n, const void* bias,
+                                              const float* out_global_scale, void* workspace, uint32_t* scratch,
+                                              int value_dtype, void* stream_) {
+  clear_error();
+  NVFP_REQUIRE(m > 0 && n > 0 && k > 0, "empty shape");
+  NVFP_REQUIRE(k % 32 == 0, "Expected k to be divisible by 32, but got k: %lld.", (long long)k);
+  NVFP_REQUIRE(x != nullptr && workspace != nullptr && scratch != nullptr && w_global_scale != nullptr, "null pointer");
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  NVFP_REQUIRE(x_dtype == NVFP_DTYPE_F16 || x_dtype == NVFP_DTYPE_BF16,
+               "Unsupported input data type for quantize_to_fp4 (dtype code %d).", x_dtype);
+  NVFP_REQUIRE(x_row_stride >= k && x_row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0,
+               "activation must be 16-byte aligned with a row stride that is >= k and a multiple of 8 elements");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* a_fp4 = ws;
+  uint8_t* a_sf = a_fp4 + round_up(m * (k / 2), 256);
+  float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
+  float* alpha = gs + 1;
+  if (int rc = dynamic_fp4_quant_launch(a_fp4, a_sf, gs, alpha, scratch, x, m, k, x_row_stride, x_dtype, w_global_scale,
+                                        /*release_next=*/true, nullptr, stream))
+    return rc;
+  return gather_fp4(group, dst_sf, n_total, n_offset, a_fp4, w_fp4, a_sf, w_sf, alpha, bias, out_global_scale, m, n, k,
+                    value_dtype, 0, stream, /*after_producer=*/true);
+}
+
+extern "C" int nvfp_scaled_fp4_mm_scatter_add(void* const* dst, int n_dst, const void* a, const void* b,
+                                              const void* sfa, const void* sfb, const float* alpha, int64_t m,
+                                              int64_t n, int64_t k, int mxfp4, void* stream) {
+  clear_error();
+  return scatter_add(dst, n_dst, a, b, sfa, sfb, alpha, m, n, k, mxfp4, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+extern "C" int nvfp_scaled_fp4_mm_gather(const nvfp_peer_group_t* group, int64_t dst_ld, const void* a, const void* b,
+                                         const void* sfa, const void* sfb, const float* alpha, int64_t m, int64_t n,
+                                         int64_t k, int out_dtype, int mxfp4, void* stream) {
+  clear_error();
+  void* rotated[kMaxOutputs];
+  PeerSync sync;
+  if (int rc = unpack_peer_group(group, rotated, &sync)) return rc;
+  const PeerSync* ps = sync.world > 1 ? &sync : nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return mxfp4 ? launch_pair<true, float, kOutScatterAdd>(p, a, b, dst, n_dst, n, info.sm_count, st)
-               : launch_pair<false, float, kOutScatterAdd>(p, a, b, dst, n_dst, n, info.sm_count, st);
+  return mxfp4 ? scaled_mm<true>(rotated, group->world, dst_ld, a, b, sfa, sfb, alpha, m, n, k, out_dtype, st, nullptr, false,
+                                 nullptr, nullptr, 0, false, ps)
+               : scaled_mm<false>(rotated, group->world, dst_ld, a, b, sfa, sfb, alpha, m, n, k, out_dtype, st, nullptr, false,
+                                  nullptr, nullptr, 0, false, ps);
+}
+
+extern "C" int nvfp_scaled_fp4_mm_reduce_scatter(const nvfp_peer_group_t* group, const void* a, const void* b,
+                                                 const void* sfa, const void* sfb, const float* alpha, int64_t m,
+                                                 int64_t n, int64_t k, int mxfp4, void* stream) {
+  clear_error();
+  void* rotated[kMaxOutputs];
+  PeerSync sync;
+  if (int rc = unpack_peer_group(group, rotated, &sync)) return rc;
+  return scatter_add(group->dst, group->world, a, b, sfa, sfb, alpha, m, n, k, mxfp4, static_cast<cudaStream_t>(stream),
+                     sync.world > 1 ? &sync : nullptr);
+}
+
+extern "C" int nvfp_linear_forward_gather(const nvfp_peer_group_t* group, int64_t dst_ld, const void* x, int64_t m,
+                                          int64_t k, int64_t x_row_stride, int x_dtype, const void* w_fp4,
+                                          const void* w_sf, const float* w_global_scale, int64_t n, void* workspace,
+                                          uint32_t* scratch, int out_dtype, void* stream_) {
+  clear_error();
+  void* rotated[kMaxOutputs];
+  PeerSync sync;
+  if (int rc = unpack_peer_group(group, rotated, &sync)) return rc;
+  NVFP_REQUIRE(m >= 0 && n >= 0 && k >= 0, "negative shape");
+  NVFP_REQUIRE(k % 32 == 0, "Expected k to be divisible by 32, but got k: %lld.", (long long)k);
+  if (m == 0 || n == 0) return NVFP_OK;
+  NVFP_REQUIRE(x != nullptr && workspace != nullptr && scratch != nullptr && w_global_scale != nullptr, "null pointer");
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  NVFP_REQUIRE(x_dtype == NVFP_DTYPE_F16 || x_dtype == NVFP_DTYPE_BF16,
+               "Unsupported input data type for quantize_to_fp4 (dtype code %d).", x_dtype);
+  NVFP_REQUIRE(x_row_stride >= k && x_row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0,
+               "activation must be 16-byte aligned with a row stride that is >= k and a multiple of 8 elements");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* a_fp4 = ws;
+  uint8_t* a_sf = a_fp4 + round_up(m * (k / 2), 256);
+  float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
+  float* alpha = gs + 1;
+  // same chain as nvfp_linear_forward: the GEMM comes up under the quantizer, fetches weights, announces ready to the
+  // peers, and touches the activation operand only after the quantizer has finished
+  if (int rc = dynamic_fp4_quant_launch(a_fp4, a_sf, gs, alpha, scratch, x, m, k, x_row_stride, x_dtype, w_global_scale,
+                                        /*release_next=*/true, nullptr, stream))
+    return rc;
+  return scaled_mm<false>(rotated, group->world, dst_ld, a_fp4, w_fp4, a_sf, w_sf, alpha, m, n, k, out_dtype, stream, nullptr,
+                          /*after_producer=*/true, nullptr, nullptr, 0, false, sync.world > 1 ? &sync : nullptr);
 }

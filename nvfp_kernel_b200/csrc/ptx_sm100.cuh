@@ -83,6 +83,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// ------------------------------------------------- flags shared between GPUs ---
+// System-scope release store / acquire load of one word in global memory (this GPU's or a peer's).
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits until *flag has reached `target` (sequence numbers: compared modulo 2^32), for at most limit_ns.
+__device__ __forceinline__ bool wait_flag_reached(const uint32_t* flag, uint32_t target, uint64_t limit_ns) {
+  if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
+    if ((spin & 31u) == 31u && global_timer_ns() - t0 > limit_ns) return false;
+  }
+}
+
 // ------------------------------------------------ programmatic dependent launch ---
 // In a kernel launched with the programmatic-stream-serialization attribute: blocks until the kernels before
 // it in the stream have completed and their writes are visible.  A no-op otherwise.

@@ -45,6 +45,8 @@ class QuantLinear(nn.Module):
         # GEMM epilogue (TMA reduce over NVLink) instead of an NCCL reduce-scatter afterwards
         self.fused_reduce_scatter = fused_reduce_scatter and parallel == "row"
         self._reduce_buffers = {}
+        # bound (ns) of each in-kernel wait on a peer rank in the fused collectives; 0 = the library's two seconds
+        self.peer_wait_limit_ns = 0
         self.world, self.rank = 1, 0
         if parallel is not None:
             import torch.distributed as dist
@@ -191,28 +193,62 @@ class QuantLinear(nn.Module):
 
     def _forward_fused_gather(self, x2: torch.Tensor, lead) -> torch.Tensor:
         """Column-parallel forward whose result is the gathered [M, N] matrix; the returned tensor
-        aliases a peer-visible buffer that the next call with the same M overwrites."""
+        aliases a peer-visible buffer that the next call with the same M overwrites.  One extension call: quantizer
+        and GEMM chained, the GEMM storing its tiles into every rank's buffer and synchronising the ranks itself
+        (no barrier or collective around it)."""
         from ._ops_real import _load_scaled_fp4_ops
         from .peer import GatherBuffer
         m = x2.shape[0]
         gb = self._gather_buffers.get(m)
         if gb is None:
             gb = self._gather_buffers[m] = GatherBuffer(m, self.n_local, self.out_dtype, x2.device, self.process_group)
-        ext = _load_scaled_fp4_ops(("scaled_fp4_mm_multi",))
+        gb.wait_limit_ns = self.peer_wait_limit_ns
         code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[self.out_dtype]
         if self.format == "nvfp4":
-            a_fp4, a_sf, alpha = self._quantize_activation(x2)
+            ext = _load_scaled_fp4_ops(("linear_forward_gather", "linear_workspace_bytes"))
+            if x2.stride(-1) != 1 or (m > 1 and x2.stride(0) % 8 != 0) or x2.data_ptr() % 16 != 0:
+                x2 = x2.contiguous()
+            workspace = torch.empty(ext.linear_workspace_bytes(m, x2.shape[1]), dtype=torch.uint8, device=x2.device)
+            ext.linear_forward_gather(gb.dst_ptrs, gb.flag_ptrs, gb.rank, gb.wait_limit_ns, gb.ld, code, x2, self.weight_fp4,
+                                      self.weight_sf, self.weight_global_scale, workspace, self._scale_scratch)
         else:
+            ext = _load_scaled_fp4_ops(("scaled_fp4_mm_gather",))
             a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
-            alpha = None
-        gb.barrier()          # every rank has finished reading the previous contents
-        ext.scaled_fp4_mm_multi(gb.dst_ptrs, gb.ld, code, a_fp4, self.weight_fp4, a_sf.view(torch.uint8), self.weight_sf,
-                                alpha, self.format == "mxfp4")
-        gb.barrier()          # every rank's slab has arrived
+            ext.scaled_fp4_mm_gather(gb.dst_ptrs, gb.flag_ptrs, gb.rank, gb.wait_limit_ns, gb.ld, code, a_fp4, self.weight_fp4,
+                                     a_sf.view(torch.uint8), self.weight_sf, None, True)
         y = gb.gathered()
         if self.bias is not None:
             y = y + self.bias
         return y.reshape(*lead, y.shape[-1])
+
+    def forward_gather_fp4(self, x: torch.Tensor, out_global_scale: torch.Tensor):
+        """Column-parallel NVFP4 layer whose gathered output is the next layer's NVFP4 activation operand: returns
+        (packed uint8 [M, N / 2], float8_e4m3fn scales [round_up(M,128), N / 16]) of the whole [M, N] product, the
+        bytes scaled_fp4_quant(layer(x), out_global_scale) would give, on every rank.  Each tile is quantized in the
+        GEMM epilogue and 0.5625 bytes per element cross NVLink instead of 2.  `out_global_scale`: fp32 [1] on the
+        device, the same (calibrated) value on every rank.  The result aliases a peer-visible buffer that the next
+        call with the same M overwrites."""
+        from ._ops_real import _load_scaled_fp4_ops
+        from .peer import Fp4GatherBuffer
+        assert self.parallel == "column" and self.format == "nvfp4", "column-parallel NVFP4 layers only"
+        assert self.out_dtype in (torch.float16, torch.bfloat16)
+        x2 = x.reshape(-1, x.shape[-1])
+        m = x2.shape[0]
+        if x2.stride(-1) != 1 or (m > 1 and x2.stride(0) % 8 != 0) or x2.data_ptr() % 16 != 0:
+            x2 = x2.contiguous()
+        key = ("fp4", m)
+        gb = self._gather_buffers.get(key)
+        if gb is None:
+            gb = self._gather_buffers[key] = Fp4GatherBuffer(m, self.n_local, x2.device, self.process_group)
+        gb.wait_limit_ns = self.peer_wait_limit_ns
+        ext = _load_scaled_fp4_ops(("linear_forward_gather_fp4", "linear_workspace_bytes"))
+        workspace = torch.empty(ext.linear_workspace_bytes(m, x2.shape[1]), dtype=torch.uint8, device=x2.device)
+        bias = self._bias_shard().detach() if self.bias is not None and self.world > 1 else \
+            (self.bias.detach() if self.bias is not None else None)
+        ext.linear_forward_gather_fp4(gb.packed_ptrs, gb.sf_ptrs, gb.flag_ptrs, gb.rank, gb.wait_limit_ns, gb.n, gb.n_offset,
+                                      1 if self.out_dtype == torch.bfloat16 else 0, x2, self.weight_fp4, self.weight_sf,
+                                      self.weight_global_scale, bias, out_global_scale, workspace, self._scale_scratch)
+        return gb.packed, gb.scales.view(torch.float8_e4m3fn)
 
     def _forward_fused_reduce_scatter(self, x2: torch.Tensor) -> torch.Tensor:
         """Row-parallel forward: returns this rank's [M / world, N] rows of the sum over ranks."""
@@ -222,17 +258,18 @@ class QuantLinear(nn.Module):
         rb = self._reduce_buffers.get(m)
         if rb is None:
             rb = self._reduce_buffers[m] = ReduceBuffer(m, self.out_features, x2.device, self.process_group)
-        ext = _load_scaled_fp4_ops(("scaled_fp4_mm_scatter_add",))
+        rb.wait_limit_ns = self.peer_wait_limit_ns
+        ext = _load_scaled_fp4_ops(("scaled_fp4_mm_reduce_scatter",))
         if self.format == "nvfp4":
             a_fp4, a_sf, alpha = self._quantize_activation(x2)
         else:
             a_fp4, a_sf = ops.scaled_mxfp4_quant(x2, self.mx_rounding)
             alpha = None
+        # the kernel announces "ready" to the peers when it starts, i.e. after this zeroing in stream order, and
+        # returns only when every rank's contributions have arrived
         rb.buf.zero_()
-        rb.barrier()          # every rank's buffer is zero and nobody reads the previous result any more
-        ext.scaled_fp4_mm_scatter_add(rb.dst_ptrs, a_fp4, self.weight_fp4, a_sf.view(torch.uint8), self.weight_sf,
-                                      alpha, self.format == "mxfp4")
-        rb.barrier()          # every rank's contributions have arrived
+        ext.scaled_fp4_mm_reduce_scatter(rb.dst_ptrs, rb.flag_ptrs, rb.rank, rb.wait_limit_ns, a_fp4, self.weight_fp4,
+                                         a_sf.view(torch.uint8), self.weight_sf, alpha, self.format == "mxfp4")
         y = rb.buf.to(self.out_dtype)
         if self.bias is not None:
             y = y + self.bias

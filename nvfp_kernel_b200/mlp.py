@@ -136,11 +136,12 @@ class QuantGatedMLP(nn.Module):
             rb = self._reduce_buffers.get(m)
             if rb is None:
                 rb = self._reduce_buffers[m] = ReduceBuffer(m, self.hidden_size, h_fp4.device, self.process_group)
+            # the kernel synchronises the ranks itself: it announces "ready" when it starts (after this zeroing, in
+            # stream order) and ends when every rank's contributions have arrived
             rb.buf.zero_()
-            rb.barrier()          # every rank's buffer is zero and nobody reads the previous result any more
-            _load_scaled_fp4_ops(("scaled_fp4_mm_scatter_add",)).scaled_fp4_mm_scatter_add(
-                rb.dst_ptrs, h_fp4, self.down_fp4, h_sf.view(torch.uint8), self.down_sf, self.down_alpha, False)
-            rb.barrier()          # every rank's contributions have arrived
+            _load_scaled_fp4_ops(("scaled_fp4_mm_reduce_scatter",)).scaled_fp4_mm_reduce_scatter(
+                rb.dst_ptrs, rb.flag_ptrs, rb.rank, rb.wait_limit_ns, h_fp4, self.down_fp4, h_sf.view(torch.uint8),
+                self.down_sf, self.down_alpha, False)
             return rb.buf.to(self.out_dtype)
         part = torch.empty((m, self.hidden_size), dtype=torch.float32, device=h_fp4.device)
         _load_scaled_fp4_ops(("cutlass_scaled_fp4_mm",)).cutlass_scaled_fp4_mm(

@@ -231,3 +231,24 @@ def check_gemm(out: torch.Tensor, ref: torch.Tensor, rel: float = 1e-2):
     bad = err > rel * ref.abs() + rms * 2.0 ** -8 + 1e-30
     assert not bad.any(), f"{int(bad.sum())} elements outside tolerance; worst {err.max().item():.4g}"
     return float(err.max()), float(mx)
+
+
+def capi_mm_gather_fp4(a, b, sfa, sfb, alpha, out_gs, packed_bases, sf_bases, n_total, n_offset, rank=0, flags=None,
+                       value_dtype=torch.bfloat16, bias=None, wait_limit_ns=0):
+    """nvfp_scaled_fp4_mm_gather_fp4: this rank's [m, n] product quantized in the epilogue and stored at columns
+    [n_offset, n_offset + n) of every destination (device tensors: packed [m, n_total / 2], scales swizzled)."""
+    import ctypes
+    lib = _capi.load()
+    m, n, k = a.shape[0], b.shape[0], a.shape[1] * 2
+    g = _capi.PeerGroup()
+    g.world, g.rank, g.wait_limit_ns = len(packed_bases), rank, wait_limit_ns
+    sf_arr = (ctypes.c_void_p * _capi.NVFP_MAX_RANKS)()
+    for r, (pk, sf) in enumerate(zip(packed_bases, sf_bases)):
+        g.dst[r] = pk.data_ptr() if hasattr(pk, "data_ptr") else pk
+        sf_arr[r] = sf.data_ptr() if hasattr(sf, "data_ptr") else sf
+        if flags is not None:
+            g.flags[r] = flags[r].data_ptr() if hasattr(flags[r], "data_ptr") else flags[r]
+    _capi.check(lib.nvfp_scaled_fp4_mm_gather_fp4(ctypes.byref(g), sf_arr, n_total, n_offset, a.data_ptr(), b.data_ptr(),
+                                                  sfa.data_ptr(), sfb.data_ptr(), alpha.data_ptr() if alpha is not None else None,
+                                                  bias.data_ptr() if bias is not None else None, out_gs.data_ptr(), m, n, k,
+                                                  _dt(value_dtype), 0, _stream()))

@@ -319,3 +319,43 @@ def test_accumulator_sums_products_exactly_and_truncates_toward_zero():
     assert [P.truncation_model(15, s) for s in (23, 24, 25, 26, 27)] == [15, 14, 12, 8, 0]
     import nvfp_kernel_b200 as nv
     assert nv.device_status() == 0
+
+
+@pytest.mark.parametrize("m,n_local,k,world", [(300, 256, 512, 2), (128, 128, 256, 4), (2048, 1024, 1024, 2), (40, 64, 128, 3),
+                                               (512, 320, 256, 2)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_nvfp4_gather_epilogue_fills_a_gathered_operand(m, n_local, k, world, dt):
+    """The column-parallel gather of the NVFP4 form of the output, with the `world` ranks' slabs computed one after the
+    other on this GPU into one gathered operand (each call: a group of one rank, no flags): packed bytes and scale bytes
+    of the whole [m, world * n_local] matrix equal the quantizer's on the concatenated 16-bit products, padding rows
+    of the scale tensor are zero, and nothing outside the operand is written."""
+    from helpers import capi_mm_gather_fp4, capi_quant
+    n_total = world * n_local
+    a, _ = gemm_inputs(m, n_local, k, seed=m + k, w_std=0.05)
+    a = a.to(dt).cuda()
+    ga = capi_global_scale(a)
+    a_fp4, a_sf = capi_quant(a, ga)
+    rp = (m + 127) // 128 * 128
+    packed = torch.full((m * (n_total // 2) + 512,), 0xAA, dtype=torch.uint8, device="cuda")
+    scales = torch.full((rp * (n_total // 16) + 512,), 0xAA, dtype=torch.uint8, device="cuda")
+    pk, sc = packed[256:256 + m * (n_total // 2)].view(m, n_total // 2), scales[256:256 + rp * (n_total // 16)].view(rp, n_total // 16)
+    slabs, operands = [], []
+    for r in range(world):
+        _, w = gemm_inputs(m, n_local, k, seed=100 + r, w_std=0.05)
+        w = w.to(dt).cuda()
+        gw = capi_global_scale(w)
+        w_fp4, w_sf = capi_quant(w, gw)
+        alpha = (1.0 / (ga * gw)).to(torch.float32)
+        operands.append((w_fp4, w_sf, alpha))
+        slabs.append(capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, dt))
+    full = torch.cat(slabs, dim=1).contiguous()
+    out_gs = ((448.0 * 6.0) / full.float().abs().max()).reshape(1)
+    want_fp4, want_sf = capi_quant(full, out_gs)
+    for r, (w_fp4, w_sf, alpha) in enumerate(operands):
+        capi_mm_gather_fp4(a_fp4, w_fp4, a_sf, w_sf, alpha, out_gs, [pk], [sc], n_total, r * n_local, value_dtype=dt)
+    import nvfp_kernel_b200 as nv
+    assert nv.device_status() == 0
+    assert torch.equal(pk, want_fp4), f"{(pk != want_fp4).sum().item()} packed bytes differ"
+    assert torch.equal(sc, want_sf), f"{(sc != want_sf).sum().item()} scale bytes differ"
+    assert (packed[:256] == 0xAA).all() and (packed[256 + pk.numel():] == 0xAA).all(), "packed: out-of-bounds write"
+    assert (scales[:256] == 0xAA).all() and (scales[256 + sc.numel():] == 0xAA).all(), "scales: out-of-bounds write"

@@ -48,6 +48,43 @@ def _worker(rank, world, port, ret):
             y_rf = row_fused(a * scale)
             ref = QuantLinear(k, n, device="cuda").load_weight(w)(a * scale)
             check_gemm(y_rf, ref[lo:hi].double(), rel=2e-2)
+        # A peer that is late: rank 1 reaches the call half a second after rank 0, whose in-kernel waits are limited
+        # to 20 ms.  Rank 0's kernel gives up on rank 1 (status bit 0x20), skips its stores to it and returns; rank 1
+        # finds rank 0's announcements already there and completes normally.  Nothing hangs, the context stays
+        # usable, and the next call (default limit again) is bit-exact on both ranks.
+        import time
+        import nvfp_kernel_b200 as nv
+        torch.cuda.synchronize()
+        assert nv.device_status() == 0
+        dist.barrier()
+        fused.peer_wait_limit_ns = 20_000_000
+        if rank == 1:
+            time.sleep(0.5)
+        t0 = time.perf_counter()
+        fused(a)
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        late_status = nv.device_status()
+        dist.barrier()
+        fused.peer_wait_limit_ns = 0
+        y_after = fused(a).clone()
+        torch.cuda.synchronize()
+        late_ok = (late_status == (0x20 if rank == 0 else 0)) and waited < 0.4 and bool(torch.equal(y_after, single)) \
+            and nv.device_status() == 0
+        # gather of the NVFP4 form of the output: the gathered operand equals the quantizer's bytes on the 1-GPU result
+        out_gs = (2688.0 / single.abs().max().float()).reshape(1)
+        want_fp4, want_sf = nv.scaled_fp4_quant(single, out_gs)
+        fp4_ok = True
+        for _ in range(2):
+            g_fp4, g_sf = fused.forward_gather_fp4(a, out_gs)
+            fp4_ok = fp4_ok and bool(torch.equal(g_fp4, want_fp4)) and bool(torch.equal(g_sf.view(torch.uint8), want_sf.view(torch.uint8)))
+        late_ok = late_ok and fp4_ok
+        # MXFP4 row-parallel: fp32 partial products through NCCL, and through the fused reduce-scatter
+        single_mx = QuantLinear(k, n, format="mxfp4", device="cuda").load_weight(w)(a)
+        for fused_rs in (False, True):
+            row_mx = QuantLinear(k, n, format="mxfp4", parallel="row", fused_reduce_scatter=fused_rs, device="cuda").load_weight(w)
+            for _ in range(2):
+                check_gemm(row_mx(a), single_mx[lo:hi].double(), rel=2e-2)
         # tensor-parallel gated MLP: intermediate dimension split, hidden activation quantized in the gate/up epilogue
         # with one calibrated scale on every rank, partial sums of the down projection reduce-scattered over the rows
         from nvfp_kernel_b200 import QuantGatedMLP
@@ -69,7 +106,8 @@ def _worker(rank, world, port, ret):
                 check_gemm(y_tp, one(xm * scale)[lo:hi].double(), rel=2e-2)
         torch.cuda.synchronize()
         ret[rank] = (bool(torch.equal(y_nccl, single)), bool(torch.equal(y_fused, single)),
-                     bool(torch.equal(y_fused2, single2)), tuple(y_row.shape), tuple(mlp_ok), tuple(y_one.shape))
+                     bool(torch.equal(y_fused2, single2)), tuple(y_row.shape), tuple(mlp_ok), tuple(y_one.shape),
+                     late_ok or (late_status, waited))
     finally:
         dist.destroy_process_group()
 
@@ -80,4 +118,4 @@ def test_column_and_row_parallel_two_gpus():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     for rank in range(world):
-        assert ret[rank] == (True, True, True, (256, 1024), (True, True), (512, 512)), (rank, ret[rank])
+        assert ret[rank] == (True, True, True, (256, 1024), (True, True), (512, 512), True), (rank, ret[rank])
