@@ -488,9 +488,32 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     # gate_up [57344, 8192] column-parallel (N split, outputs gathered), down [8192, 28672] row-parallel (K split,
     # partial products reduce-scattered over the rows); activations ~N(0,1) with 1 % of the K channels x50, weights
     # ~N(0, 0.02^2).  Weak-scaling layer `layer` and its buffers are released first.
+    extra = {}
+    if world == 1:
+        # two such layers in a row: layer 1's GEMM forms the global scale of its output in its epilogue, so layer 2
+        # skips its pass over the activation for the maximum (quantize -> GEMM only)
+        layer2 = install_weight(QuantLinear(N_PER_GPU, N_PER_GPU, device=dev), randn_bf16((N_PER_GPU, N_PER_GPU), 1001))
+
+        def two_plain():
+            return layer2(layer(a))
+
+        def two_chained():
+            y, y_gs = layer(a, return_output_scale=True, next_layer=layer2)
+            return layer2(y, x_global_scale=y_gs)
+
+        for _ in range(3):
+            two_plain(), two_chained()
+        chain_steps = max(3, min(args.steps, 50))
+        ms_two_plain = timed(two_plain, chain_steps, 6)
+        ms_two_chained = timed(two_chained, chain_steps, 5)
+        extra["two_layers_chained"] = {
+            "what": "layer(a) -> layer2(.) at M=N=K=8192 each: every layer finds its activation's maximum itself, against "
+                    "the first layer's GEMM epilogue handing the second its global scale",
+            "ms_unchained": ms_two_plain, "ms_chained": ms_two_chained,
+            "tflops_chained": 2 * 2.0 * M * N_PER_GPU * K / (ms_two_chained * 1e-3) / 1e12}
+        del layer2
     del layer, gathered
     torch.cuda.empty_cache()
-    extra = {}
     if world > 1:
         extra["fp4_gather"] = {
             "what": "the same step with the output gathered as NVFP4 (packed nibbles + block scales written by the GEMM "

@@ -162,6 +162,35 @@ int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k, int64_t x_
                         const void* bias, void* workspace, uint32_t* scratch, int out_dtype, void* stream);
 
 /*
+ * Chains of layers: the global scale a layer's quantizer needs (2688 / max|x|) is the global scale of the tensor the
+ * layer BEFORE it wrote, so that layer's GEMM can form it in its epilogue and the consumer skips its pass over x
+ * (the reference spends abs().max() and a division per layer on it, speed_test.py:46-47).
+ *
+ * nvfp_scaled_fp4_mm_amax: nvfp_scaled_fp4_mm_bias that also writes
+ *   d_global_scale_out[0] = rcp(max|d|) * 2688 over the [m, n] fp16 / bf16 values it stored (the value
+ *                           nvfp_global_scale(d) would give; NaNs are ignored by the maximum), and, when
+ *   next_weight_global_scale is given, next_alpha_out[0] = 1 / (d_global_scale_out[0] * next_weight_global_scale[0]).
+ *   scratch  eight uint32 zeroed once, self-cleaning, as for nvfp_activation_scales; NOT the buffer a quantizer
+ *            launched before this GEMM in the same call chain uses
+ *
+ * nvfp_linear_forward_chained: nvfp_linear_forward with both ends of the chain open:
+ *   x_global_scale  device fp32 or NULL.  Given: x is quantized with it (no pass for the maximum) and the GEMM forms
+ *                   alpha = 1 / (x_global_scale * w_global_scale) itself.  NULL: dynamic, as nvfp_linear_forward
+ *                   (scratch needed).
+ *   d_global_scale_out / d_scale_scratch / next_weight_global_scale / next_alpha_out  as above, or NULL: not wanted.
+ * Same bytes as the separate calls nvfp_global_scale -> nvfp_scaled_fp4_quant -> nvfp_scaled_fp4_mm_bias.
+ */
+int nvfp_scaled_fp4_mm_amax(void* d, const void* a, const void* b, const void* sfa, const void* sfb, const float* alpha,
+                            const void* bias, int64_t m, int64_t n, int64_t k, int out_dtype, int mxfp4,
+                            float* d_global_scale_out, uint32_t* scratch, const float* next_weight_global_scale,
+                            float* next_alpha_out, void* stream);
+int nvfp_linear_forward_chained(void* d, const void* x, int64_t m, int64_t k, int64_t x_row_stride, int x_dtype,
+                                const float* x_global_scale, const void* w_fp4, const void* w_sf,
+                                const float* w_global_scale, int64_t n, const void* bias, void* workspace,
+                                uint32_t* scratch, int out_dtype, float* d_global_scale_out, uint32_t* d_scale_scratch,
+                                const float* next_weight_global_scale, float* next_alpha_out, void* stream);
+
+/*
  * One call for a gated MLP with NVFP4 weights, y = down(silu(gate(x)) * up(x)): the quantizer of x, the gate/up GEMM
  * with the activation and the NVFP4 quantization of its result in the epilogue (nvfp_scaled_fp4_mm_silu_mul), and
  * the down GEMM, chained with programmatic dependent launch: each GEMM comes up while the kernel before it still

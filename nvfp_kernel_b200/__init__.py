@@ -9,6 +9,7 @@ from .ops import (
     get_active_backend,
     global_scale,
     linear_forward,
+    linear_forward_chained,
     gated_mlp_forward,
     mxfp4_scaled_mm,
     reciprocal_approximate_ftz_tensor,
@@ -35,6 +36,7 @@ __all__ = [
     "device_status",
     "dynamic_scaled_fp4_quant",
     "linear_forward",
+    "linear_forward_chained",
     "gated_mlp_forward",
     "scaled_fp4_mm_fp4out",
     "scaled_fp4_mm_silu_mul",

@@ -49,6 +49,9 @@ PROTOTYPES = {
     "nvfp_scaled_fp4_mm_silu_mul": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "nvfp_linear_workspace_bytes": (_i64, [_i64, _i64]),
     "nvfp_linear_forward": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _int, _vp]),
+    "nvfp_scaled_fp4_mm_amax": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp]),
+    "nvfp_linear_forward_chained": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _int,
+                                           _vp, _vp, _vp, _vp, _vp]),
     "nvfp_gated_mlp_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "nvfp_gated_mlp_forward": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
                                       _vp, _vp, _int, _vp]),

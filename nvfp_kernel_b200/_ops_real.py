@@ -259,6 +259,44 @@ def linear_forward(input: torch.Tensor, weight_fp4: torch.Tensor, weight_sf: tor
     return out
 
 
+def linear_forward_chained(input: torch.Tensor, weight_fp4: torch.Tensor, weight_sf: torch.Tensor,
+                           weight_global_scale: torch.Tensor, scratch: torch.Tensor, out_dtype: torch.dtype,
+                           bias: torch.Tensor | None = None, input_global_scale: torch.Tensor | None = None,
+                           output_scale_scratch: torch.Tensor | None = None,
+                           next_weight_global_scale: torch.Tensor | None = None):
+    """linear_forward for a layer inside a chain of quantized layers.
+
+    input_global_scale: fp32 [1] on the device, the NVFP4 global scale of `input` when the caller already has it (the
+        layer before returned it): the pass over `input` for its maximum is skipped.  None: dynamic, as linear_forward.
+    output_scale_scratch: 8 int32 on the device, zeroed once (a buffer of its own, not `scratch`).  Given: the GEMM's
+        epilogue also forms the global scale of the OUTPUT, 2688 / max|out|, bit for bit global_scale(out), and, with
+        next_weight_global_scale, the next layer's alpha = 1 / (that scale * next_weight_global_scale).
+    Returns out, or (out, out_global_scale, next_alpha or None) when output_scale_scratch is given."""
+    assert input.is_cuda and input.ndim == 2, "input must be a CUDA matrix"
+    assert input.dtype in (torch.float16, torch.bfloat16), f"input.dtype needs to be fp16 or bf16 but got {input.dtype}."
+    assert out_dtype in (torch.float16, torch.bfloat16), f"out_dtype needs to be fp16 or bf16 but got {out_dtype}."
+    m, k = input.shape
+    assert k % 32 == 0, f"last dim has to be multiple of 32, but got {k}."
+    if input.stride(-1) != 1 or (m > 1 and input.stride(0) % 8 != 0) or input.data_ptr() % 16 != 0:
+        input = input.contiguous()
+    n = weight_fp4.shape[0]
+    ext = _load_scaled_fp4_ops(("linear_forward_chained", "linear_workspace_bytes"))
+    out = torch.empty((m, n), dtype=out_dtype, device=input.device)
+    workspace = torch.empty(ext.linear_workspace_bytes(m, k), dtype=torch.uint8, device=input.device)
+    if bias is not None:
+        bias = _check_bias(bias, n, out_dtype)
+    scales = next_alpha = None
+    if output_scale_scratch is not None:
+        scales = torch.empty(2, dtype=torch.float32, device=input.device)
+        next_alpha = scales[1:] if next_weight_global_scale is not None else None
+    ext.linear_forward_chained(out, input, input_global_scale, weight_fp4, weight_sf, weight_global_scale, bias, workspace,
+                               scratch, scales[:1] if scales is not None else None, output_scale_scratch,
+                               next_weight_global_scale, next_alpha)
+    if output_scale_scratch is None:
+        return out
+    return out, scales[:1], next_alpha
+
+
 def gated_mlp_forward(input: torch.Tensor, gate_up_fp4: torch.Tensor, gate_up_sf: torch.Tensor,
                       gate_up_global_scale: torch.Tensor, down_fp4: torch.Tensor, down_sf: torch.Tensor,
                       act_global_scale: torch.Tensor, down_alpha: torch.Tensor, scratch: torch.Tensor,

@@ -2,6 +2,7 @@
 
     python -m nvfp_kernel_b200.build            # library + torch extension
     python -m nvfp_kernel_b200.build --lib      # only libnvfp_b200.so
+    python -m nvfp_kernel_b200.build --trace    # libnvfp_b200_trace.so, the instrumented build for pair_trace.py
 
 Outputs, both inside this package directory:
   libnvfp_b200.so                 CUDA kernels + C ABI (include/nvfp_b200.h); no torch dependency
@@ -78,6 +79,27 @@ def build_lib(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+TRACE_LIB_PATH = os.path.join(PKG_DIR, "libnvfp_b200_trace.so")
+
+
+def build_trace_lib(force: bool = False) -> str:
+    """libnvfp_b200_trace.so: the same library compiled with -DNVFP_PAIR_TRACE (the CTA-pair GEMM counts where its
+    roles wait; read with nvfp_debug_pair_trace).  Used by nvfp_kernel_b200.pair_trace only; never the product path."""
+    srcs = [os.path.join(CSRC, s) for s in CU_SOURCES]
+    digest = _digest(srcs + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))], NVCC_FLAGS + ["trace"])
+    if not force and _up_to_date(TRACE_LIB_PATH, digest):
+        return TRACE_LIB_PATH
+    objs = []
+    for s in srcs:
+        o = os.path.join(PKG_DIR, "build", "trace_" + os.path.basename(s) + ".o")
+        os.makedirs(os.path.dirname(o), exist_ok=True)
+        _run([NVCC, *NVCC_FLAGS, "-DNVFP_PAIR_TRACE", "-c", s, "-o", o])
+        objs.append(o)
+    _run([NVCC, "-shared", "-o", TRACE_LIB_PATH, *objs, "-cudart", "shared"])
+    _write_stamp(TRACE_LIB_PATH, digest)
+    return TRACE_LIB_PATH
+
+
 def build_torch_ext(force: bool = False) -> str:
     """g++ only: the extension holds no device code, it forwards to libnvfp_b200.so."""
     import torch
@@ -111,7 +133,9 @@ def build_all(force: bool = False) -> None:
 
 if __name__ == "__main__":
     force = "--force" in sys.argv
-    if "--lib" in sys.argv:
+    if "--trace" in sys.argv:
+        print(build_trace_lib(force))
+    elif "--lib" in sys.argv:
         print(build_lib(force, verbose="-v" in sys.argv))
     else:
         build_all(force)

@@ -544,6 +544,58 @@ void linear_forward(torch::Tensor& D, torch::Tensor const& X, torch::Tensor cons
                                    workspace.data_ptr(), static_cast<uint32_t*>(scratch.data_ptr()), dt, current_stream(X)));
 }
 
+// linear_forward with the chain open at both ends (nvfp_linear_forward_chained): x_gs = known global scale of X or
+// nullopt (dynamic); out_gs = where the OUTPUT's global scale goes (with out_scratch) or nullopt; next_gs_w / next_alpha:
+// the next layer's weight scale and where its alpha goes, or nullopt.
+void linear_forward_chained(torch::Tensor& D, torch::Tensor const& X, std::optional<torch::Tensor> const& x_gs,
+                            torch::Tensor const& W, torch::Tensor const& W_sf, torch::Tensor const& gs_w,
+                            std::optional<torch::Tensor> const& bias, torch::Tensor& workspace, torch::Tensor& scratch,
+                            std::optional<torch::Tensor> const& out_gs, std::optional<torch::Tensor> const& out_scratch,
+                            std::optional<torch::Tensor> const& next_gs_w, std::optional<torch::Tensor> const& next_alpha) {
+  TORCH_CHECK(X.dim() == 2 && X.stride(1) == 1, "input must be a matrix with dense rows");
+  CHECK_OPERAND(W, at::ScalarType::Byte, "weight");
+  TORCH_CHECK(W_sf.is_cuda() && W_sf.is_contiguous(), "weight scales must be a contiguous CUDA tensor");
+  TORCH_CHECK(D.is_cuda() && D.is_contiguous() && X.is_cuda() && gs_w.is_cuda() && workspace.is_cuda() && scratch.is_cuda(),
+              "all tensors must be CUDA tensors");
+  TORCH_CHECK(gs_w.scalar_type() == at::ScalarType::Float, "weight global scale must be fp32");
+  const int64_t m = X.size(0), k = X.size(1), n = W.size(0);
+  TORCH_CHECK(W.dim() == 2 && W.size(1) * 2 == k, "a and b shapes cannot be multiplied (", m, "x", k, " and ", n, "x",
+              W.size(1) * 2, ")");
+  TORCH_CHECK(n % 32 == 0, "Expected n to be divisible by 32, but got b shape: (", W.sizes()[0], "x", W.sizes()[1], ").");
+  TORCH_CHECK(W_sf.element_size() * W_sf.numel() == nvfp_sf_rows_padded(n) * nvfp_sf_cols_padded(k, 16),
+              "scale_b must be padded and swizzled to a shape (", nvfp_sf_rows_padded(n), "x", nvfp_sf_cols_padded(k, 16), ")");
+  TORCH_CHECK(D.dim() == 2 && D.size(0) == m && D.size(1) == n, "out must have shape (", m, "x", n, ")");
+  TORCH_CHECK(workspace.element_size() * workspace.numel() >= nvfp_linear_workspace_bytes(m, k), "workspace too small");
+  TORCH_CHECK(scratch.element_size() * scratch.numel() >= 32, "scratch must hold 32 bytes");
+  int dt;
+  if (D.scalar_type() == at::ScalarType::BFloat16) dt = NVFP_DTYPE_BF16;
+  else if (D.scalar_type() == at::ScalarType::Half) dt = NVFP_DTYPE_F16;
+  else TORCH_CHECK(false, "chained layers write fp16 or bf16 (", D.scalar_type(), ")");
+  auto f32 = [](std::optional<torch::Tensor> const& t, const char* what) -> float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::ScalarType::Float && t->numel() >= 1, what, " must be a CUDA fp32 tensor");
+    return static_cast<float*>(t->data_ptr());
+  };
+  uint32_t* out_scratch_ptr = nullptr;
+  if (out_scratch.has_value() && out_scratch->defined()) {
+    TORCH_CHECK(out_scratch->is_cuda() && out_scratch->element_size() * out_scratch->numel() >= 32, "output scratch must hold 32 bytes");
+    out_scratch_ptr = static_cast<uint32_t*>(out_scratch->data_ptr());
+  }
+  const void* bias_ptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->dim() == 1 && bias->size(0) == n &&
+                    bias->scalar_type() == D.scalar_type(), "bias must be a contiguous CUDA vector of ", n, " elements of the output's dtype");
+    bias_ptr = bias->data_ptr();
+  }
+  const int xdt = dtype_code(X, "Unsupported input data type for quantize_to_fp4.");
+  const at::cuda::OptionalCUDAGuard guard(device_of(X));
+  check_status(nvfp_linear_forward_chained(D.data_ptr(), X.data_ptr(), m, k, m > 1 ? X.stride(0) : k, xdt, f32(x_gs, "x_gs"),
+                                           W.data_ptr(), W_sf.data_ptr(), static_cast<const float*>(gs_w.data_ptr()), n, bias_ptr,
+                                           workspace.data_ptr(), static_cast<uint32_t*>(scratch.data_ptr()), dt,
+                                           f32(out_gs, "out_gs"), out_scratch_ptr, f32(next_gs_w, "next_gs_w"),
+                                           f32(next_alpha, "next_alpha"), current_stream(X)));
+}
+
 // Gated MLP in one call: Y = down(silu(gate(X)) * up(X)); see nvfp_gated_mlp_forward.
 int64_t gated_mlp_workspace_bytes(int64_t m, int64_t hidden, int64_t inter) {
   return nvfp_gated_mlp_workspace_bytes(m, hidden, inter);
@@ -626,6 +678,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dynamic_scaled_fp4_quant", &dynamic_scaled_fp4_quant);
   m.def("linear_workspace_bytes", &linear_workspace_bytes);
   m.def("linear_forward", &linear_forward);
+  m.def("linear_forward_chained", &linear_forward_chained);
   m.def("gated_mlp_workspace_bytes", &gated_mlp_workspace_bytes);
   m.def("gated_mlp_forward", &gated_mlp_forward);
   m.def("alpha_from_scales", &alpha_from_scales);

@@ -37,6 +37,13 @@ uint32_t* device_status_word();
 int dynamic_fp4_quant_launch(void* out_fp4, void* out_sf, float* gs_out, float* alpha_out, uint32_t* scratch,
                              const void* in, int64_t m, int64_t n, int64_t stride, int in_dtype,
                              const float* gs_weight, bool release_next, bool* one_pass, cudaStream_t stream);
+// gs_out = rcp(max|in|) * 2688 and, when gs_other is given, alpha_out = 1 / (gs_out * gs_other[0]), with the
+// self-cleaning eight-word scratch of nvfp_activation_scales (no argument checks).
+int activation_scales_launch(float* gs_out, float* alpha_out, uint32_t* scratch, const void* in, int64_t m, int64_t n,
+                             int64_t stride, int in_dtype, const float* gs_other, cudaStream_t stream);
+// nvfp_scaled_fp4_quant without the public wrapper: release_next as above.
+int scaled_fp4_quant_launch(void* out_fp4, void* out_sf, const void* in, const float* gs, int64_t m, int64_t n,
+                            int64_t stride, int in_dtype, bool release_next, cudaStream_t stream);
 // Whether that call would take the one-pass path for an [m, n] tensor on the current device.
 bool dynamic_fp4_quant_is_one_pass(int64_t m, int64_t n, int in_dtype);
 

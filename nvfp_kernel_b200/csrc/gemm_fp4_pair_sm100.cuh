@@ -98,6 +98,20 @@ struct PeerSync {
   uint64_t limit_ns;              // bound of each wait
 };
 
+#ifdef NVFP_PAIR_TRACE
+// Instrumented build (python -m nvfp_kernel_b200.build --trace): where do the roles of a CTA pair spend their clocks?
+// Per cluster: [0] issuer, clocks from its first to its last instruction  [1] issuer waiting for operands (full
+// barriers)  [2] issuer waiting for an accumulator (epilogue not done)  [3] K stages issued  [4] leader's producer
+// waiting for a free stage  [5] first epilogue warp of the leader waiting for a finished accumulator  [6] the same
+// warp waiting for its staging buffers (output stores not yet read out of shared memory)  [7] tiles.
+constexpr int kTraceClusters = 128;
+__device__ unsigned long long g_pair_trace[kTraceClusters][8];
+__device__ __forceinline__ long long trace_clock() { return clock64(); }
+#define NVFP_TRACE(...) __VA_ARGS__
+#else
+#define NVFP_TRACE(...)
+#endif
+
 template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 __global__ void __launch_bounds__(kThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -170,6 +184,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t kc = 0;
       int ks0 = 0;
       bool ok = true;
+      NVFP_TRACE(long long trace_producer_wait = 0;)
       if (p.after_producer && first_tile < num_tiles) {
         // Launched under the kernel that writes A, its scales and alpha: the ring's first fill fetches the B side
         // (which that kernel does not touch) at once and the A side after griddepcontrol.wait.
@@ -198,12 +213,14 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
         for (int ks = ks0; ks < k_stages; ++ks, ++kc) {
           const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
+          NVFP_TRACE(const long long tw0 = trace_clock();)
           if (!mbar_wait_bounded(bar(kEmpty + s), ph ^ 1u, abort_flag)) {
             *abort_flag = 1;
             atomicOr(p.status, kErrProducer);
             ok = false;
             break;
           }
+          NVFP_TRACE(trace_producer_wait += trace_clock() - tw0;)
           const uint32_t st = smem_base + s * C::kStageBytes;
           const uint32_t full = map_to_cta(bar(kFull + s), 0);
           // Only the leader arms the barrier (CTA-local, no cluster-scope release on the hot path).  The
@@ -218,6 +235,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                            ks * C::kChunksPerStage, tn * 2);
         }
       }
+      NVFP_TRACE(if (rank == 0 && cluster_id_x() < kTraceClusters) g_pair_trace[cluster_id_x()][4] = (unsigned long long)trace_producer_wait;)
       if (!ok || *abort_flag) {
         // The loads already issued report to the leader's barriers, which this thread cannot wait
         // on from the peer CTA: give them a fixed, bounded time to land before the CTA may exit.
@@ -245,21 +263,26 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const uint64_t sfb_desc0 = make_smem_desc(smem_base + C::kABytes + C::kBBytes + C::kSfaBytes, 0, 128, 0);
       const uint32_t sfa_tmem = tmem_base + C::kSfColBase, sfb_tmem = sfa_tmem + C::kSfaCols;
       const int tail_mmas = (p.k - (k_stages - 1) * kStageK + kMmaK - 1) / kMmaK;   // MMAs in the last stage
+      NVFP_TRACE(long long trace_full = 0, trace_acc = 0, trace_stages = 0; const long long trace_t0 = trace_clock();)
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++it) {
+        NVFP_TRACE(const long long ta0 = trace_clock();)
         if (!mbar_wait_bounded(bar(kAccEmpty), ((uint32_t)it & 1u) ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicOr(p.status, kErrIssuer);
           break;
         }
+        NVFP_TRACE(trace_acc += trace_clock() - ta0;)
         const uint32_t d_tmem = tmem_base + ((it & 1) ? C::kOddAccCol : 0u);
         const bool more_tiles = tile + tile_step < num_tiles;
         for (int ks = 0; ks < k_stages; ++ks) {
+          NVFP_TRACE(const long long tf0 = trace_clock();)
           if (!next_ready && !mbar_wait_bounded(bar(kFull + s), ph, abort_flag)) {
             *abort_flag = 1;
             atomicOr(p.status, kErrIssuer);
             ok = false;
             break;
           }
+          NVFP_TRACE(if (!next_ready) trace_full += trace_clock() - tf0; ++trace_stages;)
           tc_fence_after_sync();
           const int mmas = ks == k_stages - 1 ? tail_mmas : kStageK / kMmaK;
           const uint64_t stage_off = (uint64_t)((s * C::kStageBytes) >> 4);
@@ -306,6 +329,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           tc_commit_pair(acc_full_1);
         }
       }
+      NVFP_TRACE(if (cluster_id_x() < kTraceClusters) {
+        unsigned long long* t = g_pair_trace[cluster_id_x()];
+        t[0] = (unsigned long long)(trace_clock() - trace_t0); t[1] = (unsigned long long)trace_full;
+        t[2] = (unsigned long long)trace_acc; t[3] = (unsigned long long)trace_stages; t[7] = (unsigned long long)it;
+      })
       if (*abort_flag) {
         tc_commit_pair(map_to_cta(bar(kDrain), 0));
         mbar_wait_bounded(bar(kDrain), 0, never_set, 200000000ull);
@@ -321,8 +349,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     constexpr int kEarlySteps = 64 / kCols;                  // steps that cover the 48 shared columns
     const int q = warp & 3;
     if (p.after_producer) griddep_wait();   // alpha comes from the kernel before this one
-    const float alpha = p.alpha ? *reinterpret_cast<const volatile float*>(p.alpha) : 1.0f;
+    const float alpha = load_alpha(p);
     const OutT* bias = static_cast<const OutT*>(p.bias);
+    uint32_t mx2_bits = 0;                       // running max |value stored| of this lane (pair of OutT)
+    const bool track_amax = OUT_MODE == kOutStoreAll && sizeof(OutT) == 2 && p.amax_scratch != nullptr;
     const float out_gs = ((OUT_MODE == kOutFused || OUT_MODE == kOutFp4Gather) && p.out_gs) ? __ldg(p.out_gs) : 1.0f;
     const float rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
     const uint32_t acc_empty_leader = map_to_cta(bar(kAccEmpty), 0);
@@ -332,13 +362,16 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // destinations in other GPUs' memory are written only once their owners have announced ready (lane 0 decides:
     // it issues the stores)
     bool peers_asked = sync.world <= 1, remote_ok = true;
+    NVFP_TRACE(long long trace_accfull = 0, trace_store = 0;)
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      NVFP_TRACE(const long long te0 = trace_clock();)
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull), (uint32_t)it & 1u, abort_flag))) {
         *abort_flag = 1;
         if (lane == 0) atomicOr(p.status, kErrEpilogue);
         break;
       }
+      NVFP_TRACE(trace_accfull += trace_clock() - te0;)
       tc_fence_after_sync();
       const int row0 = tm * kPairBM + (int)rank * 128 + q * 32;
       const bool odd = (it & 1) != 0;
@@ -436,14 +469,17 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
         // the buffer used two steps ago must have been read out by its TMA store
         const uint32_t buf = staging + (store_count & 1u) * C::kStoreBufBytes;
+        NVFP_TRACE(const long long ts0 = trace_clock();)
         if (lane == 0) bulk_wait_group_read<1>();
         __syncwarp();
+        NVFP_TRACE(trace_store += trace_clock() - ts0;)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {     // eight 16-byte pieces of this thread's 128-byte row
           constexpr int kPer = 16 / (int)sizeof(OutT);
           const int colj = tn * kPairBN + c * kCols + j * kPer;
           const uint4 o = scale_bias_pack<OutT>(&r[kPer * j], alpha, (bias && colj < p.n) ? bias + colj : nullptr);
           st_shared_v4(buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4), o);
+          if (track_amax && row0 + lane < p.m) absmax_fold<OutT>(mx2_bits, o);     // rows past m hold only the bias
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -470,6 +506,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
       if (bail) break;
     }
+    NVFP_TRACE(if (rank == 0 && warp == 2 && lane == 0 && cluster_id_x() < kTraceClusters) {
+      g_pair_trace[cluster_id_x()][5] = (unsigned long long)trace_accfull;
+      g_pair_trace[cluster_id_x()][6] = (unsigned long long)trace_store;
+    })
+    if (track_amax) absmax_finish<OutT>(p, mx2_bits, gridDim.x * 4u);
     if (lane == 0) bulk_wait_group<0>();    // all stores performed before the CTA may exit
     if (sync.world > 1 && lane == 0) {
       // this warp's stores have been performed; the last warp of the grid to get here tells the peers and waits for them
@@ -502,15 +543,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 // Scale tensor as a 3-D map: 512-byte chunk (128 x u32) | chunk index along K | 128-row tile.
 inline int make_scale_map(CUtensorMap* map, const void* base, int64_t k_chunks, int64_t row_tiles,
                           int box_chunks, int box_tiles) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[3] = {128, (cuuint64_t)k_chunks, (cuuint64_t)row_tiles};
   const cuuint64_t strides[2] = {512, (cuuint64_t)k_chunks * 512};
   const cuuint32_t box[3] = {128, (cuuint32_t)box_chunks, (cuuint32_t)box_tiles};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled_cached(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with code %d", (int)r);
   return NVFP_OK;
 }
@@ -518,17 +555,13 @@ inline int make_scale_map(CUtensorMap* map, const void* base, int64_t k_chunks, 
 // Row-major [rows, cols] output of OutT; box = 128 bytes x 32 rows, 128-byte swizzle.
 template <typename OutT>
 int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ld) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(OutT)};
   const cuuint32_t box[2] = {(cuuint32_t)(128 / sizeof(OutT)), 32};
-  const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = sizeof(OutT) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : std::is_same<OutT, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  CUresult r = enc(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled_cached(map, dt, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
   if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
   return NVFP_OK;
 }
@@ -536,14 +569,11 @@ int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, in
 // Row-major [rows, bytes_per_row] packed NVFP4 output (one rank's slab inside a wider matrix with row pitch ld_bytes);
 // box = 128 bytes x 32 rows, 128-byte swizzle.
 inline int make_packed_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t bytes_per_row, int64_t ld_bytes) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {(cuuint64_t)bytes_per_row, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
   const cuuint32_t box[2] = {128, 32};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled_cached(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_NONE);
   if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled (packed output) failed with code %d", (int)r);
   return NVFP_OK;
 }
@@ -575,7 +605,7 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
       if (int rc = make_output_map<OutT>(&out_maps.map[o], outputs[o], rows_per_owner, p.n, ld)) return rc;
   }
   auto kernel = fp4_gemm_pair_kernel<MX, OutT, OUT_MODE>;
-  NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+  if (int rc = ensure_dynamic_smem(kernel, (int)C::kSmemBytes)) return rc;
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const unsigned pairs = (unsigned)std::min<int64_t>(tiles, sm_count / 2);
   cudaLaunchConfig_t cfg = {};

@@ -273,7 +273,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   float alpha = 1.0f;
   if (epi) {
     if (sp.after_producer) griddep_wait();         // alpha comes from the kernel before this one
-    if (owner && p.alpha) alpha = *reinterpret_cast<const volatile float*>(p.alpha);
+    if (owner) alpha = load_alpha(p);
   }
   bool have_peers = true;
   for (int j = 0; j < my_tiles; ++j) {             // one pass unless persistent
@@ -508,7 +508,7 @@ template <bool MX, typename OutT, int BOXES>
 int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
                         bool after_producer) {
   using C = SkinnyCfg<MX, BOXES>;
-  constexpr int kMaxTokens = BOXES == 4 ? 64 : 128;
+  constexpr int kMaxTokens = BOXES == 4 ? 64 : 128;   // (one-box stages: experiment only)
   SkinnyParams sp{};
   sp.g = base;
   sp.after_producer = after_producer ? 1 : 0;
@@ -585,7 +585,7 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
   if (int rc = make_operand_map(&map_w, b, n, k, 128)) return rc;
   if (int rc = make_operand_map(&map_x, a, m, k, sp.nt)) return rc;
   auto kernel = fp4_gemm_skinny_kernel<MX, OutT, BOXES>;
-  NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+  if (int rc = ensure_dynamic_smem(kernel, (int)smem_bytes)) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(persistent ? grid : (unsigned)(n_tiles * sp.split));
   cfg.blockDim = dim3(kThreads);
@@ -616,6 +616,9 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
 template <bool MX, typename OutT>
 int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
                   bool after_producer = false) {
+  static const char* forced = getenv("NVFP_SKINNY_BOXES");      // experiment switch: stage size in 256-element boxes
+  if (forced && forced[0] == '1') return launch_skinny_boxes<MX, OutT, 1>(base, a, b, sm_count, stream, after_producer);
+  if (forced && forced[0] == '2') return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer);
   if (base.m <= 64) return launch_skinny_boxes<MX, OutT, 4>(base, a, b, sm_count, stream, after_producer);
   return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer);
 }

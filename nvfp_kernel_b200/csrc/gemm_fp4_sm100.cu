@@ -26,6 +26,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <type_traits>
@@ -93,7 +94,26 @@ struct GemmParams {
                         // scales and alpha: B and its scales may be fetched before that kernel has finished
   int release_next;     // the next kernel in the stream is launched the same way behind this one and reads nothing
                         // this kernel writes before its own griddepcontrol.wait: let it come up as CTAs retire
+  // alpha formed in the epilogue from two global scales, 1 / (alpha[0] * alpha_gs_b[0]) with the roundings of
+  // nvfp_alpha_from_scales, when alpha_gs_b is set (alpha then points at the activation's global scale)
+  const float* alpha_gs_b;
+  // Global scale of the OUTPUT for the next layer's quantizer, from the epilogue: every epilogue warp folds
+  // max |value written| into amax_scratch (eight words, zeroed once, self-cleaning: two (max, arrivals) pairs and a
+  // toggle, the protocol of nvfp_activation_scales); the last warp of the grid writes amax_gs_out = rcp(max) * 2688
+  // and, when amax_gs_other is set, amax_alpha_out = 1 / (amax_gs_out * amax_gs_other[0]).  16-bit outputs only.
+  uint32_t* amax_scratch;
+  float* amax_gs_out;
+  const float* amax_gs_other;
+  float* amax_alpha_out;
 };
+
+// alpha of the epilogue: read after the kernel that produces it has finished.
+__device__ __forceinline__ float load_alpha(const GemmParams& p) {
+  if (p.alpha == nullptr) return 1.0f;
+  const float a = *reinterpret_cast<const volatile float*>(p.alpha);
+  if (p.alpha_gs_b == nullptr) return a;
+  return __fdiv_rn(1.0f, __fmul_rn(a, *reinterpret_cast<const volatile float*>(p.alpha_gs_b)));
+}
 
 template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
@@ -136,14 +156,69 @@ __device__ __forceinline__ uint4 scale_bias_pack(const uint32_t* r, float alpha,
   return o;
 }
 
+// Running max |value| over packed 16-bit outputs (eight per uint4), kept as a pair of OutT.
+template <typename OutT>
+__device__ __forceinline__ void absmax_fold(uint32_t& mx2_bits, const uint4& o) {
+  if constexpr (sizeof(OutT) == 2) {
+    using V2 = typename Vec2<OutT>::type;
+    V2 mx2 = *reinterpret_cast<V2*>(&mx2_bits);
+    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.x)));
+    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.y)));
+    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.z)));
+    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.w)));
+    mx2_bits = *reinterpret_cast<uint32_t*>(&mx2);
+  }
+}
+
+// End of an epilogue warp's work when the output's global scale is wanted (GemmParams::amax_scratch): the warp's
+// maximum goes into the scratch pair the toggle points at; the last of `total_warps` warps forms the scale (and alpha),
+// cleans the OTHER pair for the next launch and flips the toggle.  Whole warp; mx2_bits: this lane's running maximum.
+template <typename OutT>
+__device__ __forceinline__ void absmax_finish(const GemmParams& p, uint32_t mx2_bits, uint32_t total_warps) {
+  if constexpr (sizeof(OutT) == 2) {
+    using V2 = typename Vec2<OutT>::type;
+    const V2 mx2 = *reinterpret_cast<V2*>(&mx2_bits);
+    float mx = to_float<OutT>(__hmax(mx2.x, mx2.y));
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+    if ((threadIdx.x & 31) == 0) {
+      uint32_t* toggle = p.amax_scratch + 4;
+      const uint32_t t = *reinterpret_cast<volatile uint32_t*>(toggle) & 1u;   // read before this warp arrives
+      uint32_t* pair = p.amax_scratch + 2u * t;
+      atomicMax(&pair[0], __float_as_uint(mx));
+      __threadfence();
+      if (atomicAdd(&pair[1], 1u) == total_warps - 1u) {
+        __threadfence();
+        float amax = __uint_as_float(*reinterpret_cast<volatile uint32_t*>(&pair[0]));
+        if (amax == 0.0f) amax = 1.0f;
+        const float g = __fmul_rn(__frcp_rn(amax), 448.0f * 6.0f);      // the roundings of nvfp_global_scale
+        *p.amax_gs_out = g;
+        if (p.amax_gs_other) *p.amax_alpha_out = __fdiv_rn(1.0f, __fmul_rn(g, *p.amax_gs_other));
+        pair[0] = 0u;                 // every warp has contributed: this pair is clean again as well
+        pair[1] = 0u;
+        uint32_t* other = p.amax_scratch + 2u * (t ^ 1u);
+        other[0] = 0u;
+        other[1] = 0u;
+        __threadfence();
+        *toggle = t ^ 1u;
+      }
+    }
+  }
+}
+
 // 32 consecutive fp32 accumulators of one row -> 32 outputs, 16-byte stores.  `bias` points at the bias of the
 // first column or is null.
 template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t (&r)[32], float alpha, const OutT* bias) {
+__device__ __forceinline__ void store_row_chunk(OutT* dst_elems, const uint32_t (&r)[32], float alpha, const OutT* bias,
+                                                uint32_t* mx2_bits = nullptr) {
   uint4* dst = reinterpret_cast<uint4*>(dst_elems);
   constexpr int kPer = 16 / (int)sizeof(OutT);
 #pragma unroll
-  for (int v = 0; v < 32 / kPer; ++v) dst[v] = scale_bias_pack<OutT>(&r[kPer * v], alpha, bias ? bias + kPer * v : nullptr);
+  for (int v = 0; v < 32 / kPer; ++v) {
+    const uint4 o = scale_bias_pack<OutT>(&r[kPer * v], alpha, bias ? bias + kPer * v : nullptr);
+    dst[v] = o;
+    if (mx2_bits) absmax_fold<OutT>(*mx2_bits, o);
+  }
 }
 
 // silu(g) * u the way a framework evaluates it on 16-bit tensors: silu in fp32, rounded to T, times u in fp32,
@@ -454,10 +529,12 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------------------------------------ epilogue ---
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
     if (p.after_producer) griddep_wait();   // alpha comes from the kernel before this one
-    const float alpha = p.alpha ? *reinterpret_cast<const volatile float*>(p.alpha) : 1.0f;
+    const float alpha = load_alpha(p);
     OutT* d = static_cast<OutT*>(p.d);
     const OutT* bias = static_cast<const OutT*>(p.bias);
     const float out_gs = p.out_gs ? __ldg(p.out_gs) : 1.0f, rcp_out_gs = rcp_approx_ftz(out_gs), rcp6 = rcp_approx_ftz(6.0f);
+    uint32_t mx2_bits = 0;                       // running max |value stored| of this lane (pair of OutT)
+    const bool track_amax = sizeof(OutT) == 2 && p.amax_scratch != nullptr;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
@@ -486,12 +563,14 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
         }
         if (row < p.m && col < p.n)
-          store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha, bias ? bias + col : nullptr);
+          store_row_chunk<OutT>(d + (int64_t)row * p.n + col, r, alpha, bias ? bias + col : nullptr,
+                                track_amax ? &mx2_bits : nullptr);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kAccEmpty + as));
     }
+    if (track_amax) absmax_finish<OutT>(p, mx2_bits, gridDim.x * 4u);
   }
 
   // -------------------------------------------------------------- common exit ---
@@ -520,18 +599,73 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled behind a small per-thread cache.  A descriptor is a pure function of its arguments, a layer
+// calls with the same weight (and usually the same workspace) addresses every time, and an encode costs about a
+// microsecond of host time -- four or five of them per launch are not small beside a 9 us decode kernel.
+struct TensorMapKey {
+  uintptr_t base;
+  uint64_t dims[3], strides[2];
+  uint32_t box[3];
+  int32_t dtype, rank, swizzle, promotion;
+};
+CUresult encode_tiled_cached(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base, const cuuint64_t* dims,
+                             const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
+                             CUtensorMapL2promotion promotion) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return CUDA_ERROR_NOT_SUPPORTED;
+  constexpr int kSlots = 256;
+  struct Slot { TensorMapKey key; CUtensorMap map; bool used; };
+  thread_local Slot* table = nullptr;
+  if (!table) table = new Slot[kSlots]();
+  TensorMapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = reinterpret_cast<uintptr_t>(base);
+  for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+  key.dtype = (int32_t)dtype; key.rank = rank; key.swizzle = (int32_t)swizzle; key.promotion = (int32_t)promotion;
+  uint64_t h = key.base * 0x9E3779B97F4A7C15ull;
+  h ^= (key.dims[0] + 0x632BE59BD9B4E019ull * key.dims[1] + key.box[1] * 1315423911ull + (uint64_t)key.rank) * 0xD6E8FEB86659FD93ull;
+  Slot& slot = table[(h >> 40) % kSlots];
+  static const bool cache_off = getenv("NVFP_NO_DESCRIPTOR_CACHE") != nullptr;     // for measuring what the cache saves
+  if (!cache_off && slot.used && memcmp(&slot.key, &key, sizeof(key)) == 0) {
+    *map = slot.map;
+    return CUDA_SUCCESS;
+  }
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, dtype, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle, promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) {
+    slot.key = key;
+    slot.map = *map;
+    slot.used = true;
+  }
+  return r;
+}
+
+// cudaFuncSetAttribute(max dynamic shared memory) once per kernel and device instead of once per launch.
+template <typename Kernel>
+int ensure_dynamic_smem(Kernel kernel, int bytes) {
+  struct Done { const void* fn; int dev; int bytes; };
+  thread_local Done done[64];
+  thread_local int count = 0;
+  int dev = 0;
+  NVFP_CUDA(cudaGetDevice(&dev));
+  const void* fn = reinterpret_cast<const void*>(kernel);
+  for (int i = 0; i < count; ++i)
+    if (done[i].fn == fn && done[i].dev == dev && done[i].bytes >= bytes) return NVFP_OK;
+  NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (count < 64) done[count++] = Done{fn, dev, bytes};
+  return NVFP_OK;
+}
+
 // Row-major [rows, k/2] bytes of packed e2m1; box = 128 bytes of K x box_rows rows,
 // 128-byte swizzle; out-of-range rows / bytes read as zero.
 int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {(cuuint64_t)(k / 2), (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)(k / 2)};
   const cuuint32_t box[2] = {(cuuint32_t)kStageKBytes, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = encode_tiled_cached(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (r != CUDA_SUCCESS) return fail(NVFP_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return NVFP_OK;
 }
@@ -547,7 +681,7 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
   if (int rc = make_operand_map(&map_a, a, p.m, p.k, kBM)) return rc;
   if (int rc = make_operand_map(&map_b, b, p.n, p.k, BN)) return rc;
   auto kernel = fp4_gemm_kernel<BN, MX, OutT>;
-  NVFP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+  if (int rc = ensure_dynamic_smem(kernel, (int)C::kSmemBytes)) return rc;
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count);
   cudaLaunchConfig_t cfg = {};
@@ -567,13 +701,24 @@ int launch_config(const GemmParams& base, const void* a, const void* b, int sm_c
 #include "gemm_fp4_pair_sm100.cuh"
 #include "gemm_fp4_skinny_sm100.cuh"
 
+// Scale plumbing between chained layers (see GemmParams): alpha formed in the epilogue from two global scales, and / or
+// the output's own global scale (and the next layer's alpha) produced by the epilogue.
+struct ChainOpts {
+  const float* alpha_gs_b = nullptr;
+  uint32_t* amax_scratch = nullptr;
+  float* amax_gs_out = nullptr;
+  const float* amax_gs_other = nullptr;
+  float* amax_alpha_out = nullptr;
+};
+
 // `outputs`: n_out destination matrices [m, n] (row-major, out_dtype); more than one only for the
 // column-parallel gather, where the extra ones are peer GPUs' buffers.
 template <bool MX>
 int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const void* b, const void* sfa, const void* sfb,
               const float* alpha, int64_t m, int64_t n, int64_t k, int out_dtype, cudaStream_t stream,
               const void* bias = nullptr, bool after_producer = false, const float* out_gs = nullptr,
-              void* out_sf = nullptr, int act = 0, bool release_next = false, const PeerSync* peer_sync = nullptr) {
+              void* out_sf = nullptr, int act = 0, bool release_next = false, const PeerSync* peer_sync = nullptr,
+              const ChainOpts* chain = nullptr) {
   NVFP_REQUIRE(bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "bias must be 16-byte aligned");
   const bool fused = out_gs != nullptr || act != 0;
   if (fused) {
@@ -627,13 +772,35 @@ int scaled_mm(void* const* outputs, int n_out, int64_t ld, const void* a, const 
   p.sfb_row_tiles = (int)ceil_div(n, 128);
   p.status = device_status_word();
   NVFP_REQUIRE(p.status != nullptr, "cannot locate the device status word");
+  bool amax_after = false;       // the output's global scale by a pass over the (small) output instead of the epilogue
+  if (chain) {
+    p.alpha_gs_b = chain->alpha_gs_b;
+    if (chain->amax_scratch) {
+      NVFP_REQUIRE(!fused && n_out == 1 && ld == n && out_dtype != NVFP_DTYPE_F32 && chain->amax_gs_out != nullptr &&
+                       (chain->amax_gs_other == nullptr || chain->amax_alpha_out != nullptr),
+                   "the output's global scale is formed for one dense fp16 / bf16 output (and needs its result pointers)");
+      p.amax_scratch = chain->amax_scratch;
+      p.amax_gs_out = chain->amax_gs_out;
+      p.amax_gs_other = chain->amax_gs_other;
+      p.amax_alpha_out = chain->amax_alpha_out;
+    }
+  }
   // Few activation rows (decode): weights are streamed once; swap the operands and split K over a cluster.
   if (n_out == 1 && ld == n && skinny_preferred(m, n, info.sm_count)) {
+    // the few-rows kernel does not fold the output's maximum into its epilogue: its output is a few hundred KB, which
+    // the global-scale kernel sweeps in a couple of microseconds right after
+    amax_after = p.amax_scratch != nullptr;
+    p.amax_scratch = nullptr;
+    int rc;
     switch (out_dtype) {
-      case NVFP_DTYPE_BF16: return launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream, after_producer);
-      case NVFP_DTYPE_F16: return launch_skinny<MX, __half>(p, a, b, info.sm_count, stream, after_producer);
-      default: return launch_skinny<MX, float>(p, a, b, info.sm_count, stream, after_producer);
+      case NVFP_DTYPE_BF16: rc = launch_skinny<MX, __nv_bfloat16>(p, a, b, info.sm_count, stream, after_producer); break;
+      case NVFP_DTYPE_F16: rc = launch_skinny<MX, __half>(p, a, b, info.sm_count, stream, after_producer); break;
+      default: rc = launch_skinny<MX, float>(p, a, b, info.sm_count, stream, after_producer); break;
     }
+    if (rc == NVFP_OK && amax_after)
+      rc = activation_scales_launch(chain->amax_gs_out, chain->amax_alpha_out, chain->amax_scratch, d, m, n, n, out_dtype,
+                                    chain->amax_gs_other, stream);
+    return rc;
   }
   // the kernels below fetch only B before they wait; several destinations only when the ranks are synchronised inside
   // the kernel (a caller that synchronises them around the call does so with launches of its own in between)
@@ -779,6 +946,78 @@ extern "C" int nvfp_linear_forward(void* d, const void* x, int64_t m, int64_t k,
     return rc;
   return scaled_mm<false>(&d, 1, n, a_fp4, w_fp4, a_sf, w_sf, alpha, m, n, k, out_dtype, stream, bias,
                           /*after_producer=*/true);
+}
+
+extern "C" int nvfp_scaled_fp4_mm_amax(void* d, const void* a, const void* b, const void* sfa, const void* sfb,
+                                       const float* alpha, const void* bias, int64_t m, int64_t n, int64_t k, int out_dtype,
+                                       int mxfp4, float* d_global_scale_out, uint32_t* scratch,
+                                       const float* next_weight_global_scale, float* next_alpha_out, void* stream) {
+  clear_error();
+  NVFP_REQUIRE(d_global_scale_out != nullptr && scratch != nullptr, "global-scale output or scratch is null");
+  NVFP_REQUIRE(next_weight_global_scale == nullptr || next_alpha_out != nullptr,
+               "alpha output is null although the next weight's scale is given");
+  if (m == 0 || n == 0) return NVFP_OK;
+  ChainOpts chain;
+  chain.amax_scratch = scratch;
+  chain.amax_gs_out = d_global_scale_out;
+  chain.amax_gs_other = next_weight_global_scale;
+  chain.amax_alpha_out = next_alpha_out;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return mxfp4 ? scaled_mm<true>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, st, bias, false, nullptr, nullptr, 0, false,
+                                 nullptr, &chain)
+               : scaled_mm<false>(&d, 1, n, a, b, sfa, sfb, alpha, m, n, k, out_dtype, st, bias, false, nullptr, nullptr, 0, false,
+                                  nullptr, &chain);
+}
+
+extern "C" int nvfp_linear_forward_chained(void* d, const void* x, int64_t m, int64_t k, int64_t x_row_stride, int x_dtype,
+                                           const float* x_global_scale, const void* w_fp4, const void* w_sf,
+                                           const float* w_global_scale, int64_t n, const void* bias, void* workspace,
+                                           uint32_t* scratch, int out_dtype, float* d_global_scale_out,
+                                           uint32_t* d_scale_scratch, const float* next_weight_global_scale,
+                                           float* next_alpha_out, void* stream_) {
+  clear_error();
+  NVFP_REQUIRE(m >= 0 && n >= 0 && k >= 0, "negative shape");
+  NVFP_REQUIRE(k % 32 == 0, "Expected k to be divisible by 32, but got k: %lld.", (long long)k);
+  if (m == 0 || n == 0) return NVFP_OK;
+  NVFP_REQUIRE(x != nullptr && workspace != nullptr && w_global_scale != nullptr, "null pointer");
+  NVFP_REQUIRE(x_global_scale != nullptr || scratch != nullptr, "scratch is needed when the activation's scale is not given");
+  NVFP_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  NVFP_REQUIRE(x_dtype == NVFP_DTYPE_F16 || x_dtype == NVFP_DTYPE_BF16,
+               "Unsupported input data type for quantize_to_fp4 (dtype code %d).", x_dtype);
+  NVFP_REQUIRE(x_row_stride >= k && x_row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0,
+               "activation must be 16-byte aligned with a row stride that is >= k and a multiple of 8 elements");
+  NVFP_REQUIRE(d_global_scale_out == nullptr || d_scale_scratch != nullptr, "scratch of the output's global scale is null");
+  NVFP_REQUIRE(next_weight_global_scale == nullptr || (next_alpha_out != nullptr && d_global_scale_out != nullptr),
+               "the next layer's alpha needs the output's global scale and a place to go");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* a_fp4 = ws;
+  uint8_t* a_sf = a_fp4 + round_up(m * (k / 2), 256);
+  float* gs = reinterpret_cast<float*>(a_sf + round_up(nvfp_sf_rows_padded(m) * nvfp_sf_cols_padded(k, 16), 256));
+  float* alpha = gs + 1;
+  ChainOpts chain;
+  const float* alpha_ptr = alpha;
+  if (x_global_scale != nullptr) {
+    // the scale is known (the layer before formed it in its epilogue): no pass over x for its maximum; alpha is formed
+    // by the GEMM's epilogue from the two global scales
+    if (int rc = scaled_fp4_quant_launch(a_fp4, a_sf, x, x_global_scale, m, k, x_row_stride, x_dtype, /*release_next=*/true,
+                                         stream))
+      return rc;
+    alpha_ptr = x_global_scale;
+    chain.alpha_gs_b = w_global_scale;
+  } else {
+    if (int rc = dynamic_fp4_quant_launch(a_fp4, a_sf, gs, alpha, scratch, x, m, k, x_row_stride, x_dtype, w_global_scale,
+                                          /*release_next=*/true, nullptr, stream))
+      return rc;
+  }
+  if (d_global_scale_out != nullptr) {
+    chain.amax_scratch = d_scale_scratch;
+    chain.amax_gs_out = d_global_scale_out;
+    chain.amax_gs_other = next_weight_global_scale;
+    chain.amax_alpha_out = next_alpha_out;
+  }
+  return scaled_mm<false>(&d, 1, n, a_fp4, w_fp4, a_sf, w_sf, alpha_ptr, m, n, k, out_dtype, stream, bias,
+                          /*after_producer=*/true, nullptr, nullptr, 0, false, nullptr, &chain);
 }
 
 extern "C" int64_t nvfp_gated_mlp_workspace_bytes(int64_t m, int64_t hidden, int64_t inter) {
@@ -1061,3 +1300,17 @@ extern "C" int nvfp_linear_forward_gather(const nvfp_peer_group_t* group, int64_
   return scaled_mm<false>(rotated, group->world, dst_ld, a_fp4, w_fp4, a_sf, w_sf, alpha, m, n, k, out_dtype, stream, nullptr,
                           /*after_producer=*/true, nullptr, nullptr, 0, false, sync.world > 1 ? &sync : nullptr);
 }
+
+#ifdef NVFP_PAIR_TRACE
+// Instrumented build only: copies the per-cluster clock counters of the last fp4_gemm_pair_kernel launches to the host
+// (out: clusters x 8 uint64; see g_pair_trace) and clears them.
+extern "C" int nvfp_debug_pair_trace(unsigned long long* out, int clusters) {
+  clear_error();
+  NVFP_REQUIRE(out != nullptr && clusters > 0 && clusters <= kTraceClusters, "bad trace request");
+  NVFP_CUDA(cudaDeviceSynchronize());
+  NVFP_CUDA(cudaMemcpyFromSymbol(out, g_pair_trace, sizeof(unsigned long long) * 8 * clusters));
+  static unsigned long long zeros[kTraceClusters][8];
+  NVFP_CUDA(cudaMemcpyToSymbol(g_pair_trace, zeros, sizeof(zeros)));
+  return NVFP_OK;
+}
+#endif

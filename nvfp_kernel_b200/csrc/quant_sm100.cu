@@ -638,6 +638,19 @@ int dynamic_fp4_quant_launch(void* out_fp4, void* out_sf, float* gs_out, float* 
                                                    gs_weight, stream, release_next, one_pass);
 }
 
+int activation_scales_launch(float* gs_out, float* alpha_out, uint32_t* scratch, const void* in, int64_t m, int64_t n,
+                             int64_t stride, int in_dtype, const float* gs_other, cudaStream_t stream) {
+  return in_dtype == NVFP_DTYPE_F16
+             ? launch_amax<__half>(gs_out, scratch, in, m, n, stride, stream, true, gs_other, gs_other ? alpha_out : nullptr)
+             : launch_amax<__nv_bfloat16>(gs_out, scratch, in, m, n, stride, stream, true, gs_other,
+                                          gs_other ? alpha_out : nullptr);
+}
+
+int scaled_fp4_quant_launch(void* out_fp4, void* out_sf, const void* in, const float* gs, int64_t m, int64_t n,
+                            int64_t stride, int in_dtype, bool release_next, cudaStream_t stream) {
+  return launch_quant<16>(out_fp4, out_sf, in, gs, m, n, stride, in_dtype, 0, stream, /*wait_prev=*/false, release_next);
+}
+
 bool dynamic_fp4_quant_is_one_pass(int64_t m, int64_t n, int in_dtype) {
   return in_dtype == NVFP_DTYPE_F16 ? dynamic_quant_fits<__half>(m, n) : dynamic_quant_fits<__nv_bfloat16>(m, n);
 }

@@ -151,10 +151,34 @@ class QuantLinear(nn.Module):
         return static_out
 
     # ------------------------------------------------------------------ forward ---
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, x_global_scale: torch.Tensor | None = None, return_output_scale: bool = False,
+                next_layer: "QuantLinear | None" = None):
+        """x_global_scale / return_output_scale chain quantized layers without a pass over the activation between them
+        (single-GPU NVFP4 layers): with return_output_scale the GEMM's epilogue also forms the global scale of its
+        output, and the call returns (y, y_global_scale); handing that to the next layer's forward as x_global_scale
+        lets it quantize at once.  The bytes are those of the unchained layers."""
+        if x_global_scale is not None or return_output_scale:
+            return self._forward_chained(x, x_global_scale, return_output_scale, next_layer)
         if getattr(self, "_use_graph", False):
             return self._graphed_forward(x)
         return self._forward_impl(x)
+
+    def _forward_chained(self, x, x_global_scale, return_output_scale, next_layer):
+        if self.format != "nvfp4" or (self.parallel is not None and self.world > 1):
+            raise ValueError("chained global scales are offered for single-GPU NVFP4 layers")
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if return_output_scale and not hasattr(self, "_out_scale_scratch"):
+            self.register_buffer("_out_scale_scratch", torch.zeros(8, dtype=torch.int32, device=x2.device), persistent=False)
+        res = ops.linear_forward_chained(
+            x2, self.weight_fp4, self.weight_sf, self.weight_global_scale, self._scale_scratch, self.out_dtype,
+            bias=self.bias.detach() if self.bias is not None else None, input_global_scale=x_global_scale,
+            output_scale_scratch=self._out_scale_scratch if return_output_scale else None,
+            next_weight_global_scale=next_layer.weight_global_scale if (return_output_scale and next_layer is not None) else None)
+        if not return_output_scale:
+            return res.reshape(*lead, res.shape[-1])
+        y, y_gs, _ = res
+        return y.reshape(*lead, y.shape[-1]), y_gs
 
     def _forward_impl(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]

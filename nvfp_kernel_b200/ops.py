@@ -43,6 +43,7 @@ alpha_from_scales = _impl.alpha_from_scales
 activation_scales = _impl.activation_scales
 dynamic_scaled_fp4_quant = _impl.dynamic_scaled_fp4_quant
 linear_forward = _impl.linear_forward
+linear_forward_chained = _impl.linear_forward_chained
 gated_mlp_forward = _impl.gated_mlp_forward
 scaled_fp4_mm_fp4out = _impl.scaled_fp4_mm_fp4out
 scaled_fp4_mm_silu_mul = _impl.scaled_fp4_mm_silu_mul

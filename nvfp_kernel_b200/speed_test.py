@@ -5,6 +5,7 @@
     python -m nvfp_kernel_b200.speed_test --table quant   # quantizer alone, GB/s
     python -m nvfp_kernel_b200.speed_test --table fp4out  # GEMM + quantizer of its output, separate and fused
     python -m nvfp_kernel_b200.speed_test --table mxfp4   # MXFP4 at M = 4096, K = N = 8192, beside NVFP4
+    python -m nvfp_kernel_b200.speed_test --table host    # host microseconds per call (enqueue only)
     python -m nvfp_kernel_b200.speed_test --table mlp     # gated MLP: separate kernels vs activation + quantizer in the epilogue
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m nvfp_kernel_b200.speed_test --table tp
                                                           # Llama-3-70B prefill layers, tensor-parallel
@@ -127,6 +128,44 @@ def decode(repeats: int):
             t_graph = time_us(lambda: layer(a_static), repeats)
             nbytes = n * k * 0.5625 + m * k * 0.5625 + 2.0 * m * n
             print(f"{m:<5} {k:<7} {n:<7} {t_bf16:<13.1f} {t_mm:<11.1f} {nbytes / t_mm / 1e3:<9.0f} {t_fwd:<13.1f} {t_graph:<13.1f}")
+
+
+def host(repeats: int):
+    """Host time per call (enqueue only, microseconds): how long the calling thread is busy before the call returns,
+    with the GPU kept behind (bursts of calls, then a synchronize).  What a decode loop pays per layer on the CPU."""
+    import time
+    print(f"{'M':<5} {'K':<7} {'N':<7} {'GEMM call (us)':<16} {'forward call (us)':<18} {'C ABI GEMM (us)':<16}")
+    print("-" * 72)
+    from . import _capi
+    lib = _capi.load()
+    for m, k, n in ((16, 4096, 4096), (16, 4096, 28672), (128, 4096, 6144), (2048, 4096, 4096)):
+        a = torch.randn(m, k, dtype=torch.bfloat16, device="cuda")
+        w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+        layer = QuantLinear(k, n, device="cuda").load_weight(w)
+        gs = ops.global_scale(a)
+        a_fp4, a_sf = ops.scaled_fp4_quant(a, gs)
+        alpha = ops.alpha_from_scales(gs, layer.weight_global_scale)
+        w_sf = layer.weight_sf.view(torch.float8_e4m3fn)
+        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        args = (out.data_ptr(), a_fp4.data_ptr(), layer.weight_fp4.data_ptr(), a_sf.data_ptr(), layer.weight_sf.data_ptr(),
+                alpha.data_ptr(), m, n, k, _capi.NVFP_DTYPE_BF16, stream)
+
+        def burst(fn, calls=64):
+            best = float("inf")
+            for _ in range(max(3, repeats // 8)):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(calls):
+                    fn()
+                best = min(best, (time.perf_counter() - t0) / calls * 1e6)
+            torch.cuda.synchronize()
+            return best
+
+        t_mm = burst(lambda: ops.cutlass_scaled_fp4_mm(a_fp4, layer.weight_fp4, a_sf, w_sf, alpha, torch.bfloat16))
+        t_fwd = burst(lambda: layer(a))
+        t_c = burst(lambda: lib.nvfp_scaled_fp4_mm(*args))
+        print(f"{m:<5} {k:<7} {n:<7} {t_mm:<16.1f} {t_fwd:<18.1f} {t_c:<16.1f}")
 
 
 def quant(repeats: int):
@@ -335,11 +374,11 @@ def main():
     ap = argparse.ArgumentParser(description="BF16 GEMM vs FP4 GEMM with online activation quantization")
     ap.add_argument("--batch_size", type=int, default=4096, help="M dimension of the sweep")
     ap.add_argument("--repeats", type=int, default=50)
-    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp", "fp4out", "mlp", "mxfp4"])
+    ap.add_argument("--table", default="sweep", choices=["sweep", "decode", "quant", "tp", "fp4out", "mlp", "mxfp4", "host"])
     args = ap.parse_args()
     torch.cuda.empty_cache()
     {"sweep": lambda: sweep(args.batch_size, args.repeats), "decode": lambda: decode(args.repeats),
-     "quant": lambda: quant(args.repeats), "fp4out": lambda: fp4out(min(args.repeats, 20)), "mlp": lambda: mlp(min(args.repeats, 10)), "mxfp4": lambda: mxfp4(min(args.repeats, 20)), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
+     "quant": lambda: quant(args.repeats), "host": lambda: host(args.repeats), "fp4out": lambda: fp4out(min(args.repeats, 20)), "mlp": lambda: mlp(min(args.repeats, 10)), "mxfp4": lambda: mxfp4(min(args.repeats, 20)), "tp": lambda: tensor_parallel(min(args.repeats, 20))}[args.table]()
 
 
 if __name__ == "__main__":

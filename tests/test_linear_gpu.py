@@ -400,3 +400,33 @@ def test_speed_test_tables_run(capsys):
     speed_test.quant(1)
     out = capsys.readouterr().out
     assert out.count("\n") >= 12 + 5 + 4 and "14336" in out and "28672" in out
+
+
+# shapes that take the CTA-pair kernel, the one-CTA tile kernel and the few-rows kernel
+@pytest.mark.parametrize("m,k,n1,n2", [(2048, 1024, 2048, 1024), (300, 512, 1024, 512), (100, 512, 384, 256), (16, 1024, 4096, 1024),
+                                       (1, 4096, 4096, 4096), (4096, 2048, 4096, 2048)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_global_scale_from_the_producers_epilogue_chains_two_layers(m, k, n1, n2, dt):
+    """Layer 1's GEMM forms the global scale of its output in its epilogue; layer 2 quantizes with it at once.  The
+    scale equals nvfp_global_scale of layer 1's output bit for bit, and layer 2's result equals the unchained layer's
+    (GEMM -> global scale -> quantizer -> GEMM), also with a bias in layer 1 and on repeated calls."""
+    import nvfp_kernel_b200 as nv
+    from helpers import capi_global_scale
+    torch.manual_seed(m + n1)
+    x = torch.randn(m, k).to(dt).cuda()
+    l1 = nv.QuantLinear(k, n1, bias=True, out_dtype=dt, device="cuda").load_weight((torch.randn(n1, k) * 0.05).to(dt).cuda())
+    l1.bias.data.copy_((torch.randn(n1) * 0.5).to(dt))
+    l2 = nv.QuantLinear(n1, n2, out_dtype=dt, device="cuda").load_weight((torch.randn(n2, n1) * 0.05).to(dt).cuda())
+    for scale in (1.0, 0.125, 3.0):                 # the scratch cleans itself between calls
+        xs = (x * scale).to(dt)
+        y_plain = l1(xs)
+        z_plain = l2(y_plain)
+        y, y_gs = l1(xs, return_output_scale=True, next_layer=l2)
+        assert torch.equal(y, y_plain)
+        assert torch.equal(y_gs, capi_global_scale(y_plain)), (y_gs.item(), capi_global_scale(y_plain).item())
+        z = l2(y, x_global_scale=y_gs)
+        assert torch.equal(z, z_plain)
+    # both ends open at once: a middle layer takes a known scale and hands on its own
+    z2, z2_gs = l2(y, x_global_scale=y_gs, return_output_scale=True)
+    assert torch.equal(z2, z_plain) and torch.equal(z2_gs, capi_global_scale(z_plain))
+    assert nv.device_status() == 0
