@@ -111,3 +111,36 @@ def test_root_ops_shim_and_build_profile():
     assert run("emulation").returncode == 0                     # accepted, builds the real kernels
     bad = run("bogus")
     assert bad.returncode != 0 and "Invalid NVFP_BUILD_PROFILE" in bad.stderr
+
+
+def test_peer_group_struct_and_its_validation():
+    """nvfp_peer_group_t as ctypes sees it matches the header (two ints, eight destinations, eight flag blocks, the wait
+    limit), and a malformed group is rejected on the host before anything is launched."""
+    assert ctypes.sizeof(_capi.PeerGroup) == 2 * 4 + 8 * 8 + 8 * 8 + 8
+    lib = _capi.load()
+    buf = ctypes.create_string_buffer(8192)
+    p = ctypes.addressof(buf) // 256 * 256 + 256
+    g = _capi.PeerGroup()
+    g.world, g.rank = 0, 0
+    args = (4096, p, p, p, p, p, 256, 4096, 256, _capi.NVFP_DTYPE_BF16, 0, None)
+    assert lib.nvfp_scaled_fp4_mm_gather(ctypes.byref(g), *args) == _capi.NVFP_ERR_INVALID_ARGUMENT
+    assert b"world" in lib.nvfp_last_error()
+    g.world, g.rank = 2, 2
+    assert lib.nvfp_scaled_fp4_mm_gather(ctypes.byref(g), *args) == _capi.NVFP_ERR_INVALID_ARGUMENT
+    g.rank = 1
+    g.dst[0], g.dst[1] = p, None
+    assert lib.nvfp_scaled_fp4_mm_gather(ctypes.byref(g), *args) == _capi.NVFP_ERR_INVALID_ARGUMENT
+    assert b"destination of rank 1" in lib.nvfp_last_error()
+    g.dst[1] = p + 1024
+    g.flags[0] = p + 2048                       # flag blocks for every rank or for none
+    assert lib.nvfp_scaled_fp4_mm_gather(ctypes.byref(g), *args) == _capi.NVFP_ERR_INVALID_ARGUMENT
+    assert b"flag blocks" in lib.nvfp_last_error()
+    # NVFP4 gather: slabs are whole 64-column scale chunks
+    g.flags[0] = None
+    sf = (ctypes.c_void_p * _capi.NVFP_MAX_RANKS)(p, p)
+    rc = lib.nvfp_scaled_fp4_mm_gather_fp4(ctypes.byref(g), sf, 4096, 96, p, p, p, p, p, None, p, 256, 2048, 256,
+                                           _capi.NVFP_DTYPE_BF16, 0, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT and b"multiples of 64" in lib.nvfp_last_error()
+    # chained layers: the output's scale needs its scratch
+    rc = lib.nvfp_scaled_fp4_mm_amax(p, p, p, p, p, p, None, 256, 256, 256, _capi.NVFP_DTYPE_BF16, 0, p, None, None, None, None)
+    assert rc == _capi.NVFP_ERR_INVALID_ARGUMENT
