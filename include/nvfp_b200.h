@@ -86,7 +86,10 @@ int nvfp_mxfp4_quant(void* out_fp4, void* out_sf, const void* in, int64_t m, int
  *
  *   a    [m, k/2] packed e2m1, b [n, k/2] packed e2m1 (weights are [N, K], K-major)
  *   sfa  round_up(m,128) x round_up(k/16,4) ue4m3, swizzled; sfb likewise for n.
- *        Scale bytes of K-blocks beyond k must be finite (the quantizers here write 0).
+ *        When k is not a multiple of 64 the last MMA covers scale columns past k/16: their operand bytes read as
+ *        zero, so those scale bytes must be zero or at least finite (0x7F / 0xFF would turn 0 * scale into NaN).
+ *        The quantizers here write every padding byte as 0; for scale tensors produced elsewhere use
+ *        nvfp_kernel_b200.sharding.zero_scale_padding once, at load time.
  *   alpha device pointer to one fp32, read by the kernel's epilogue
  *   d    [m, n] out_dtype (fp16 / bf16 as in the reference, or fp32), row-major,
  *        16-byte aligned
@@ -386,8 +389,10 @@ int nvfp_dynamic_fp4_quant(void* out_fp4, void* out_sf, float* gs_out, float* al
  * reference.  The amax word lives in a 256-byte array inside the library (held by every GPU
  * that loads it, until exit); the call allocates nothing and calls no allocating routine.
  *   - tensors of more than 2^32 elements are rejected (NVFP_ERR_INVALID_ARGUMENT);
- *   - the first call on each device looks the array's address up (cudaGetSymbolAddress):
- *     make that call before any stream capture;
+ *   - the first call on each device looks the array's address up (cudaGetSymbolAddress) and, under lazy module
+ *     loading, that look-up or the first launch may load the module and allocate its globals: make the first
+ *     call during warm-up, before the allocator is closed and before any stream capture.  Later calls
+ *     allocate nothing;
  *   - all calls on a device share the array: the call clears the word it uses on its stream,
  *     but two calls that overlap on the GPU (different streams) race.  Serialise them.
  */

@@ -508,7 +508,7 @@ template <bool MX, typename OutT, int BOXES>
 int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
                         bool after_producer) {
   using C = SkinnyCfg<MX, BOXES>;
-  constexpr int kMaxTokens = BOXES == 4 ? 64 : 128;   // (one-box stages: experiment only)
+  constexpr int kMaxTokens = BOXES == 4 ? 64 : 128;
   SkinnyParams sp{};
   sp.g = base;
   sp.after_producer = after_producer ? 1 : 0;
@@ -612,13 +612,11 @@ int launch_skinny_boxes(const GemmParams& base, const void* a, const void* b, in
 }
 
 // Up to 64 tokens: stages of 1024 elements of K; above, the activation box is as large as the weight box and
-// stages of 512 keep three of them in shared memory.
+// stages of 512 keep three of them in shared memory.  Smaller stages for the decode shapes (256 or 512 elements, so
+// that the first MMAs start before a whole 88 KB stage has landed) measured slower or equal on every one of them.
 template <bool MX, typename OutT>
 int launch_skinny(const GemmParams& base, const void* a, const void* b, int sm_count, cudaStream_t stream,
                   bool after_producer = false) {
-  static const char* forced = getenv("NVFP_SKINNY_BOXES");      // experiment switch: stage size in 256-element boxes
-  if (forced && forced[0] == '1') return launch_skinny_boxes<MX, OutT, 1>(base, a, b, sm_count, stream, after_producer);
-  if (forced && forced[0] == '2') return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer);
   if (base.m <= 64) return launch_skinny_boxes<MX, OutT, 4>(base, a, b, sm_count, stream, after_producer);
   return launch_skinny_boxes<MX, OutT, 2>(base, a, b, sm_count, stream, after_producer);
 }
