@@ -13,7 +13,9 @@
  *   dequantize ................. nvfp/pseudo_quant.py:166-180
  * It agrees bit for bit with oracle/nvfp_oracle.py (checked by the CPU tests), which in
  * turn is pinned against outputs of the reference itself (tests/golden/).
- * MXFP4: the reference has no reachable MXFP4 path -- parity unpinned.
+ * MXFP4: the reference has no reachable MXFP4 path; its disabled e8m0 branch (kernel/nvfp4_utils.cuh:196-202) pins the
+ * `floor` scale rounding of the numpy oracle's quantizer (tests/golden/ref_kernel_ue8m0_sm100.npz); this file holds
+ * the MXFP4 GEMM only.
  *
  * The hardware reciprocal rcp.approx.ftz.f32 is modelled either by the correctly rounded
  * 1/x or by a caller-supplied table of (input, output) bit patterns captured on a GPU.

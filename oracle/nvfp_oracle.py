@@ -294,12 +294,14 @@ def global_scale_from_amax(amax) -> np.float32:
 # MXFP4 quantizer (32-element blocks, e8m0 scales, no global scale)
 # --------------------------------------------------------------------------- #
 def mxfp4_quantize(x, rounding: str = "rceil", pad_value: int = 0):
-    """32-element MXFP4 quantizer.  parity unpinned: the reference holds no MXFP4 path.
-
-    ``rounding="floor"`` widens the reference's disabled e8m0 branch
-    (kernel/nvfp4_utils.cuh:196-202: exponent bits of amax*rcp(6)) to 32-element
-    blocks; ``rounding="rceil"`` rounds the exponent up (the behaviour of
-    ``cvt.rp.satfinite.ue8m0x2.f32``) so no element saturates.  The element scale is
+    """32-element MXFP4 quantizer.  The reference holds no reachable MXFP4 path; what it holds is a
+    disabled e8m0 branch of its quantizer (kernel/nvfp4_utils.cuh:196-202: exponent bits of
+    amax*rcp(6), 16-element blocks).  ``rounding="floor"`` is that branch widened to 32-element
+    blocks, and is PINNED to it: tests/golden/ref_kernel_ue8m0_sm100.npz holds the branch's own
+    output (compiled from the reference's sources, run on a B200) on inputs whose 32-blocks are two
+    equal halves, and this function reproduces it byte for byte (tests/test_oracle_cpu.py).
+    ``rounding="rceil"`` rounds the exponent up (the behaviour of ``cvt.rp.satfinite.ue8m0x2.f32``) so
+    no element saturates: a build decision without a counterpart in the reference.  The element scale is
     the exact reciprocal power of two, applied with a flush-to-zero multiply.
     Returns (packed [m, n/2], swizzled e8m0 bytes, linear e8m0 bytes [m, n/32]).
     """

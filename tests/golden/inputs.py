@@ -65,3 +65,11 @@ def gemm_inputs(m: int, n: int, k: int, seed: int = 0, w_std: float = 1.0, dtype
     g1 = torch.Generator().manual_seed(seed + 1)
     w = torch.randn((n, k), generator=g1, dtype=torch.float32) * w_std
     return a.to(dtype), w.to(dtype)
+
+
+def mx_duplicated_halves(dist: str, shape, dtype=torch.bfloat16, seed: int = 17) -> torch.Tensor:
+    """[m, n] input whose every 32-element block is two copies of one 16-element half: a 16-block quantizer (the
+    reference's e8m0 branch) and a 32-block quantizer (MXFP4 here) must then choose the same scale for it."""
+    m, n = shape
+    half = make_input(dist, (m, n // 2), dtype, seed).reshape(m, n // 32, 1, 16)
+    return half.expand(m, n // 32, 2, 16).reshape(m, n).contiguous()

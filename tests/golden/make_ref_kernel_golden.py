@@ -1,4 +1,4 @@
-"""Generates ref_kernel_sm100.npz by RUNNING the reference's own CUDA quantizer
+"""Generates ref_kernel_sm100.npz and ref_kernel_ue8m0_sm100.npz by RUNNING the reference's own CUDA quantizer
 (kernel/nvfp4_quant_kernels.cu of the reference, built for sm_100a by
 oracle/build_oracle.py into oracle/_ref/) on a B200.
 
@@ -20,7 +20,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path[:0] = [HERE, ROOT]
-from inputs import DISTRIBUTIONS, make_input  # noqa: E402
+from inputs import DISTRIBUTIONS, make_input, mx_duplicated_halves  # noqa: E402
 from oracle import nvfp_oracle as O  # noqa: E402
 
 CASE_DISTS = DISTRIBUTIONS + ("zeros_mixed",)
@@ -78,6 +78,27 @@ def main():
     path = os.path.join(out_dir, "ref_kernel_sm100.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")
+
+    # The reference's e8m0 branch (cvt_warp_fp16_to_fp4<Type, true>, kernel/nvfp4_utils.cuh:196-202; 16-element blocks,
+    # no global scale), run through its own launcher template: pins MXFP4's `floor` scale rounding.  Inputs: every
+    # 32-block two copies of one 16-element half (inputs.mx_duplicated_halves, seed 17).
+    if hasattr(ref, "scaled_fp4_quant_ue8m0"):
+        mx = {}
+        for dist in CASE_DISTS + ("student_t3",):
+            for shape in ((128, 128), (129, 96)):
+                for dt_name, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+                    x = mx_duplicated_halves(dist, shape, dt, seed=17).cuda()
+                    m, n = shape
+                    fp4 = torch.empty((m, n // 2), dtype=torch.uint8, device="cuda")
+                    rm, rn = (m + 127) // 128 * 128, (n // 16 + 3) // 4 * 4
+                    sf = torch.zeros((rm, rn // 4), dtype=torch.int32, device="cuda")
+                    ref.scaled_fp4_quant_ue8m0(fp4, x, sf)
+                    key = f"{dist}_{m}x{n}_{dt_name}"
+                    mx[key + "_fp4"] = fp4.cpu().numpy()
+                    mx[key + "_sf16"] = O.unswizzle_128x4(sf.view(torch.uint8).reshape(rm, rn).cpu().numpy(), m, n // 16)
+        path = os.path.join(out_dir, "ref_kernel_ue8m0_sm100.npz")
+        np.savez_compressed(path, **mx)
+        print("wrote", path, os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":

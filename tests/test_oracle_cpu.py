@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from inputs import DISTRIBUTIONS, c1_inputs, make_input
+from inputs import DISTRIBUTIONS, c1_inputs, make_input, mx_duplicated_halves
 from oracle import c_oracle, nvfp_oracle as O, pseudo_path
 
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_torch_path.npz"))
@@ -141,6 +141,24 @@ def test_mxfp4_properties():
     for rounding in ("rceil", "floor"):
         fp4, swz, lin = O.mxfp4_quantize(y, rounding)
         assert lin[0, 0] == 127 - 3 and (fp4 == 0x77).all()
+
+
+@pytest.mark.parametrize("dist", DISTRIBUTIONS + ("zeros_mixed", "student_t3"))
+def test_mxfp4_floor_restatement_matches_the_reference_ue8m0_branch(dist):
+    """tests/golden/ref_kernel_ue8m0_sm100.npz holds what the reference's own e8m0 branch (16-element blocks,
+    kernel/nvfp4_utils.cuh:196-202, compiled from its sources and run on a B200 by make_ref_kernel_golden.py)
+    produced for inputs whose 32-blocks are two copies of one 16-element half.  The oracle's 32-block `floor`
+    quantizer must give the same packed bytes, and its scale byte must equal both of the reference's."""
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_kernel_ue8m0_sm100.npz"))
+    for shape in ((128, 128), (129, 96)):
+        for dt in ("bf16", "fp16"):
+            key = f"{dist}_{shape[0]}x{shape[1]}_{dt}"
+            x = mx_duplicated_halves(dist, shape, TORCH_DT[dt], seed=17)
+            fp4, _, lin = O.mxfp4_quantize(x, "floor")
+            sf16 = gold[key + "_sf16"]
+            assert np.array_equal(sf16[:, 0::2], sf16[:, 1::2]), key
+            assert np.array_equal(lin, sf16[:, 0::2]), key
+            assert np.array_equal(fp4, gold[key + "_fp4"]), (key, int((fp4 != gold[key + "_fp4"]).sum()))
 
 
 def test_pseudo_path_port_matches_oracle_and_reference_c1():

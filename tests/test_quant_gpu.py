@@ -237,8 +237,8 @@ def test_one_pass_dynamic_quant_equals_global_scale_then_quantize(dt):
 @pytest.mark.parametrize("rounding", ["rceil", "floor"])
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
 def test_mxfp4_bit_exact_vs_cpu_restatement(rounding, dt):
-    """MXFP4 parity is unpinned by the reference (it has no MXFP4 path): this is
-    CUDA-vs-own-CPU-restatement self-consistency."""
+    """CUDA against the CPU restatement, both roundings.  The restatement's `floor` mode is pinned to the reference's
+    e8m0 branch (test_oracle_cpu.py, test_reference_pins_gpu.py); `rceil` is this package's own rule."""
     for dist in ALL_DISTS + ("student_t3",):
         for shape in ((128, 128), (129, 96), (1, 4096), (300, 2048)):
             x = make_input(dist, shape, TORCH_DT[dt], seed=13)
