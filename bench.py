@@ -367,6 +367,24 @@ def main_ours(args, rank: int, world: int, local_rank: int):
             layer.forward_gather_fp4(a, out_gs)
         ms_fp4_gather = timed(lambda: layer.forward_gather_fp4(a, out_gs), args.steps, own_kernels_per_step)
 
+    # ---- what NVLink gives a kernel's stores into a peer's memory on this box (N > 1): the roofline of the gather ---
+    nvlink = None
+    if world > 1:
+        import torch.distributed._symmetric_memory as symm_mem
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        probe = symm_mem.empty((M * N_PER_GPU,), dtype=torch.bfloat16, device=dev)
+        handle = symm_mem.rendezvous(probe, dist.group.WORLD)
+        peer_view = handle.get_buffer((rank + 1) % world, (M * N_PER_GPU,), torch.bfloat16)
+        src = torch.zeros_like(probe)
+        for _ in range(2):
+            peer_view.copy_(src)
+        ms_copy = timed(lambda: peer_view.copy_(src), 10, 0)
+        nvlink = {"peer_store_gbs": M * N_PER_GPU * 2 / (ms_copy * 1e-3) / 1e9,
+                  "what": "134 MB copied by a torch elementwise kernel (SM stores) from this rank's memory into the next "
+                          "rank's peer-mapped buffer, all ranks at once (a ring), max over ranks; per direction per GPU"}
+        del probe, handle, peer_view, src
+        torch.cuda.empty_cache()
+
     # ---- region 1: whole hot path, activation resident in HBM, exactly --steps steps (burst) -------------------
     with sampler:
         ms_step = timed(lambda: step(a), args.steps, own_kernels_per_step)
@@ -644,6 +662,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     }
     if parity is not None:
         line["parity"] = parity
+        line["nvlink"] = nvlink
     if world == 1 and not args.no_cpu_baseline:
         tflops, cores, sample, _, _ = run_cpu_baseline(20.0, 3, 1)
         line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
