@@ -322,7 +322,7 @@ def test_accumulator_sums_products_exactly_and_truncates_toward_zero():
 
 
 @pytest.mark.parametrize("m,n_local,k,world", [(300, 256, 512, 2), (128, 128, 256, 4), (2048, 1024, 1024, 2), (40, 64, 128, 3),
-                                               (512, 320, 256, 2)])
+                                               (512, 320, 256, 2), (256, 128, 512, 8)])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 def test_nvfp4_gather_epilogue_fills_a_gathered_operand(m, n_local, k, world, dt):
     """The column-parallel gather of the NVFP4 form of the output, with the `world` ranks' slabs computed one after the
@@ -359,3 +359,106 @@ def test_nvfp4_gather_epilogue_fills_a_gathered_operand(m, n_local, k, world, dt
     assert torch.equal(sc, want_sf), f"{(sc != want_sf).sum().item()} scale bytes differ"
     assert (packed[:256] == 0xAA).all() and (packed[256 + pk.numel():] == 0xAA).all(), "packed: out-of-bounds write"
     assert (scales[:256] == 0xAA).all() and (scales[256 + sc.numel():] == 0xAA).all(), "scales: out-of-bounds write"
+
+
+def _peer_group(world, rank, dst, flags, limit_ns=0):
+    import ctypes
+    from nvfp_kernel_b200 import _capi
+    g = _capi.PeerGroup()
+    g.world, g.rank, g.wait_limit_ns = world, rank, limit_ns
+    for r in range(world):
+        g.dst[r] = dst[r]
+        if flags is not None:
+            g.flags[r] = flags[r].data_ptr()
+    return g
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2), (8, 3)])
+def test_rank_synchronisation_protocol_with_the_peers_played_by_the_host(world, rank):
+    """The in-kernel synchronisation of a tensor-parallel layer (ready / done flags, call counter) on ONE GPU: this
+    process is one rank of a group of `world`, the other ranks' destinations and flag blocks are ordinary local
+    buffers, and the HOST plays those ranks by writing their announcements before the launch (no kernel waits for
+    another kernel).  Checked: the slab lands at this rank's columns of every destination, the rank announces ready and
+    done with the call's number on every peer's block, its own counter advances, nothing times out; a second call
+    needs the next number; and with peers that never announce, the kernel gives up after the limit, reports it,
+    keeps its own destination intact and skips the peers'."""
+    import ctypes
+    from nvfp_kernel_b200 import _capi
+    lib = _capi.load()
+    m, n, k = 512, 256, 512
+    a, w = gemm_inputs(m, n, k, seed=3 + rank, w_std=0.05)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    want = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    ld = world * n
+    gathered = [torch.zeros((m, ld), dtype=torch.bfloat16, device="cuda") for _ in range(world)]   # every rank's matrix
+    flags = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]
+    dst = [g.data_ptr() + rank * n * 2 for g in gathered]       # where this rank's slab starts in each of them
+    peers = [r for r in range(world) if r != rank]
+    lo, hi = rank * n, (rank + 1) * n
+
+    def call(limit_ns=0):
+        g = _peer_group(world, rank, dst, flags, limit_ns)
+        _capi.check(lib.nvfp_scaled_fp4_mm_gather(ctypes.byref(g), ld, a_fp4.data_ptr(), w_fp4.data_ptr(), a_sf.data_ptr(),
+                                                  w_sf.data_ptr(), alpha.data_ptr(), m, n, k, _capi.NVFP_DTYPE_BF16, 0,
+                                                  torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+
+    def peers_announce(seq):
+        for r in peers:
+            flags[rank][r] = seq          # ready[r] on this rank's block: peer r has reached call `seq`
+            flags[rank][8 + r] = seq      # done[r]: peer r's stores of call `seq` have arrived
+
+    for seq in (1, 2):
+        peers_announce(seq)
+        for g in gathered:
+            g.zero_()
+        call()
+        assert _capi.device_status() == 0
+        for g in gathered:
+            assert torch.equal(g[:, lo:hi], want)
+            assert not g[:, :lo].any() and not g[:, hi:].any()
+        for r in peers:
+            f = flags[r].cpu().tolist()
+            assert f[rank] == seq and f[8 + rank] == seq, (r, f)      # ready and done announced on peer r's block
+        mine = flags[rank].cpu().tolist()
+        assert mine[17] == seq and mine[16] == 0, mine               # call counter advanced, arrival counter cleaned
+    # the peers never reach call 3: bounded waits of 2 ms, reported, nothing written to them
+    for g in gathered:
+        g.zero_()
+    call(limit_ns=2_000_000)
+    assert _capi.device_status() == 0x20
+    assert torch.equal(gathered[rank][:, lo:hi], want) and not any(bool(gathered[r].any()) for r in peers)
+    assert flags[rank].cpu().tolist()[17] == 3
+    # and the next call works again once the peers are back
+    peers_announce(4)
+    call()
+    assert _capi.device_status() == 0 and all(torch.equal(g[:, lo:hi], want) for g in gathered)
+
+
+def test_reduce_scatter_epilogue_with_one_rank_and_with_the_peer_played_by_the_host():
+    """nvfp_scaled_fp4_mm_reduce_scatter on one GPU: a group of one (the whole fp32 product added into a zeroed buffer)
+    and a group of two whose other rank is played by the host: rank 0's rows of the sum land in its own buffer, the
+    other half in the "peer's"."""
+    import ctypes
+    from nvfp_kernel_b200 import _capi
+    lib = _capi.load()
+    m, n, k = 512, 256, 1024
+    a, w = gemm_inputs(m, n, k, seed=9, w_std=0.05)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    want = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.float32)
+    args = (a_fp4.data_ptr(), w_fp4.data_ptr(), a_sf.data_ptr(), w_sf.data_ptr(), alpha.data_ptr(), m, n, k, 0,
+            torch.cuda.current_stream().cuda_stream)
+    whole = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    g = _peer_group(1, 0, [whole.data_ptr()], None)
+    _capi.check(lib.nvfp_scaled_fp4_mm_reduce_scatter(ctypes.byref(g), *args))
+    torch.cuda.synchronize()
+    assert torch.equal(whole, want)
+    halves = [torch.zeros((m // 2, n), dtype=torch.float32, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(2)]
+    flags[0][1] = 1
+    flags[0][9] = 1
+    g = _peer_group(2, 0, [h.data_ptr() for h in halves], flags)
+    _capi.check(lib.nvfp_scaled_fp4_mm_reduce_scatter(ctypes.byref(g), *args))
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+    assert torch.equal(halves[0], want[:m // 2]) and torch.equal(halves[1], want[m // 2:])
