@@ -305,6 +305,10 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     else:
         layer = QuantLinear(K, N_PER_GPU, device=dev)
     install_weight(layer, randn_bf16((N_PER_GPU, K), 1000 + rank))
+    # in-kernel waits on peer ranks: the library's bound is two seconds; the processes of a benchmark start their
+    # first calls with whatever skew the host gives them, so allow the maximum (ten seconds) here
+    PEER_WAIT_NS = 10_000_000_000
+    layer.peer_wait_limit_ns = PEER_WAIT_NS
     gathered = torch.empty((world * M, N_PER_GPU), dtype=torch.bfloat16, device=dev) if world > 1 else None
     layer.gather_output = fused
 
@@ -342,6 +346,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
         other = QuantLinear(K, n_total, parallel="column", fused_gather=not fused, device=dev)
         other.weight_fp4, other.weight_sf = layer.weight_fp4, layer.weight_sf
         other.weight_global_scale.copy_(layer.weight_global_scale)
+        other.peer_wait_limit_ns = PEER_WAIT_NS
         y_other = other(a)
         column_ok = all_ranks(bool(torch.equal(y_gathered, y_other)))
         parity["column_fused_vs_nccl"] = "bitwise" if column_ok else "MISMATCH"
@@ -548,6 +553,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     else:
         gu = QuantLinear(K, C4_GATE_UP_N, device=dev)
     install_weight(gu, randn_bf16((n_gu_local, K), 2000 + rank, 0.02))
+    gu.peer_wait_limit_ns = PEER_WAIT_NS
     gu.gather_output = True
     for _ in range(3):
         gu(x_gu)
@@ -570,6 +576,7 @@ def main_ours(args, rank: int, world: int, local_rank: int):
     else:
         dn = QuantLinear(C4_DOWN_K, N_PER_GPU, device=dev)
     install_weight(dn, randn_bf16((N_PER_GPU, k_dn_local), 4000 + rank, 0.02))
+    dn.peer_wait_limit_ns = PEER_WAIT_NS
     for _ in range(3):
         y_dn = dn(x_dn)
     if world > 1:
