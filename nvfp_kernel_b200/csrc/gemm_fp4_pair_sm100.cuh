@@ -19,6 +19,9 @@
 
 constexpr int kPairBM = 256;
 constexpr int kPairBN = 256;
+// Tile numbering (pair_tile_coords): the rows of A that one band of tile rows covers should stay in L2 while all of B
+// streams past them once per band; this many bytes of A (values and scales) per band at most.
+constexpr int64_t kPairBandBytes = 40ll << 20;
 
 template <bool MX>
 struct PairCfg {
@@ -104,13 +107,33 @@ struct PeerSync {
 // barriers)  [2] issuer waiting for an accumulator (epilogue not done)  [3] K stages issued  [4] leader's producer
 // waiting for a free stage  [5] first epilogue warp of the leader waiting for a finished accumulator  [6] the same
 // warp waiting for its staging buffers (output stores not yet read out of shared memory)  [7] tiles.
+// Hand-over of the tensor pipe from one tile to the next, as sums of clock64 values over the tiles that have a
+// successor (differences of the sums, divided by that number of tiles, are mean intervals): [9] the leader's first
+// epilogue warp sees the tile finished  [10] it has the shared columns in registers and releases the accumulator
+// [8] the issuer sees the release (the next tile's first MMA is issued right after); [13] / [12] / [11]: the epilogue
+// warp past its tcgen05 fence / the loads of the first 64 columns issued / their data in registers.
+// g_trace_no_loads != 0: after the first fill of the ring the producers only signal the stages instead of loading
+// them (results are garbage): the stage time without any operand traffic into shared memory.
 constexpr int kTraceClusters = 128;
-__device__ unsigned long long g_pair_trace[kTraceClusters][8];
+constexpr int kTraceSlots = 16;
+__device__ unsigned long long g_pair_trace[kTraceClusters][kTraceSlots];
+__device__ int g_trace_no_loads;
 __device__ __forceinline__ long long trace_clock() { return clock64(); }
 #define NVFP_TRACE(...) __VA_ARGS__
 #else
 #define NVFP_TRACE(...)
 #endif
+
+// Tile number -> tile row and column.  Tiles are numbered down the rows of a BAND of p.band tile rows, column after
+// column, band after band, so the CTA pairs that run at the same time (consecutive numbers) cover a roughly square
+// patch of the output: fewer distinct operand panels are being pulled out of L2 at any moment than with whole columns.
+__device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+  const int per_band = p.band * p.tiles_n;
+  const int b = tile / per_band, within = tile - b * per_band;
+  const int rows = min(p.band, p.tiles_m - b * p.band);
+  tn = within / rows;
+  tm = b * p.band + (within - tn * rows);
+}
 
 template <bool MX, typename OutT, int OUT_MODE = kOutStoreAll>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -188,7 +211,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       if (p.after_producer && first_tile < num_tiles) {
         // Launched under the kernel that writes A, its scales and alpha: the ring's first fill fetches the B side
         // (which that kernel does not touch) at once and the A side after griddepcontrol.wait.
-        const int tm = first_tile % p.tiles_m, tn = first_tile / p.tiles_m;
+        int tm, tn;
+        pair_tile_coords(p, first_tile, tm, tn);
         const int early = min(k_stages, C::kStages);
         for (int ks = 0; ks < early; ++ks) {
           const uint32_t st = smem_base + (uint32_t)ks * C::kStageBytes;
@@ -210,7 +234,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         ks0 = early;
       }
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ks0 = 0) {
-        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        int tm, tn;
+        pair_tile_coords(p, tile, tm, tn);
         for (int ks = ks0; ks < k_stages; ++ks, ++kc) {
           const uint32_t s = kc % C::kStages, ph = (kc / C::kStages) & 1u;
           NVFP_TRACE(const long long tw0 = trace_clock();)
@@ -226,6 +251,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           // Only the leader arms the barrier (CTA-local, no cluster-scope release on the hot path).  The
           // peer's bytes may arrive first: the transaction count goes negative for a moment, the phase
           // cannot complete before the leader's arrival.
+          NVFP_TRACE(if (g_trace_no_loads && kc >= (uint32_t)C::kStages) {
+            if (rank == 0) mbar_arrive(bar(kFull + s));
+            continue;
+          })
           if (rank == 0) mbar_arrive_expect_tx(bar(kFull + s), 2 * C::kStageBytes);
           tma_load_2d_pair(st, &tmap_a, full, ks * kStageKBytes, tm * kPairBM + (int)rank * 128);
           tma_load_2d_pair(st + C::kABytes, &tmap_b, full, ks * kStageKBytes, tn * kPairBN + (int)rank * 128);
@@ -263,7 +292,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const uint64_t sfb_desc0 = make_smem_desc(smem_base + C::kABytes + C::kBBytes + C::kSfaBytes, 0, 128, 0);
       const uint32_t sfa_tmem = tmem_base + C::kSfColBase, sfb_tmem = sfa_tmem + C::kSfaCols;
       const int tail_mmas = (p.k - (k_stages - 1) * kStageK + kMmaK - 1) / kMmaK;   // MMAs in the last stage
-      NVFP_TRACE(long long trace_full = 0, trace_acc = 0, trace_stages = 0; const long long trace_t0 = trace_clock();)
+      NVFP_TRACE(long long trace_full = 0, trace_acc = 0, trace_stages = 0; const long long trace_t0 = trace_clock();
+                 unsigned long long trace_handover = 0;)
       for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++it) {
         NVFP_TRACE(const long long ta0 = trace_clock();)
         if (!mbar_wait_bounded(bar(kAccEmpty), ((uint32_t)it & 1u) ^ 1u, abort_flag)) {
@@ -271,7 +301,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           atomicOr(p.status, kErrIssuer);
           break;
         }
-        NVFP_TRACE(trace_acc += trace_clock() - ta0;)
+        NVFP_TRACE(trace_acc += trace_clock() - ta0; if (it > 0) trace_handover += (unsigned long long)trace_clock();)
         const uint32_t d_tmem = tmem_base + ((it & 1) ? C::kOddAccCol : 0u);
         const bool more_tiles = tile + tile_step < num_tiles;
         for (int ks = 0; ks < k_stages; ++ks) {
@@ -333,6 +363,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         unsigned long long* t = g_pair_trace[cluster_id_x()];
         t[0] = (unsigned long long)(trace_clock() - trace_t0); t[1] = (unsigned long long)trace_full;
         t[2] = (unsigned long long)trace_acc; t[3] = (unsigned long long)trace_stages; t[7] = (unsigned long long)it;
+        t[8] = trace_handover;
       })
       if (*abort_flag) {
         tc_commit_pair(map_to_cta(bar(kDrain), 0));
@@ -362,17 +393,19 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // destinations in other GPUs' memory are written only once their owners have announced ready (lane 0 decides:
     // it issues the stores)
     bool peers_asked = sync.world <= 1, remote_ok = true;
-    NVFP_TRACE(long long trace_accfull = 0, trace_store = 0;)
+    NVFP_TRACE(long long trace_accfull = 0, trace_store = 0; unsigned long long trace_seen = 0, trace_released = 0, trace_ld_issued = 0, trace_loaded = 0, trace_fenced = 0;)
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
-      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      int tm, tn;
+      pair_tile_coords(p, tile, tm, tn);
       NVFP_TRACE(const long long te0 = trace_clock();)
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(kAccFull), (uint32_t)it & 1u, abort_flag))) {
         *abort_flag = 1;
         if (lane == 0) atomicOr(p.status, kErrEpilogue);
         break;
       }
-      NVFP_TRACE(trace_accfull += trace_clock() - te0;)
+      NVFP_TRACE(trace_accfull += trace_clock() - te0; if (tile + tile_step < num_tiles) trace_seen += (unsigned long long)trace_clock();)
       tc_fence_after_sync();
+      NVFP_TRACE(if (tile + tile_step < num_tiles) trace_fenced += (unsigned long long)trace_clock();)
       const int row0 = tm * kPairBM + (int)rank * 128 + q * 32;
       const bool odd = (it & 1) != 0;
       const uint32_t t_row = tmem_base + (odd ? C::kOddAccCol : 0u) + ((uint32_t)(q * 32) << 16);
@@ -387,11 +420,14 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
         for (int h = 0; h < kCols / 32; ++h)
           tmem_ld_32x32b_x32(t_row + c * kCols + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[h * 32]));
+        NVFP_TRACE(if (i == 0 && tile + tile_step < num_tiles) trace_ld_issued += (unsigned long long)trace_clock();)
         tmem_ld_wait();
+        NVFP_TRACE(if (i == 0 && tile + tile_step < num_tiles) trace_loaded += (unsigned long long)trace_clock();)
         if (i == kEarlySteps - 1) {
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+          if (lane == 0) mbar_arrive_remote(acc_empty_leader);
+          NVFP_TRACE(if (tile + tile_step < num_tiles) trace_released += (unsigned long long)trace_clock();)
         }
         if constexpr (OUT_MODE == kOutFused) {
           if (p.act) finish_row_chunk<OutT, 64, true>(p, r, alpha, bias, row0 + lane, tn * kPairBN + c * kCols, out_gs, rcp_out_gs, rcp6);
@@ -509,6 +545,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     NVFP_TRACE(if (rank == 0 && warp == 2 && lane == 0 && cluster_id_x() < kTraceClusters) {
       g_pair_trace[cluster_id_x()][5] = (unsigned long long)trace_accfull;
       g_pair_trace[cluster_id_x()][6] = (unsigned long long)trace_store;
+      g_pair_trace[cluster_id_x()][9] = trace_seen;
+      g_pair_trace[cluster_id_x()][10] = trace_released;
+      g_pair_trace[cluster_id_x()][11] = trace_loaded;
+      g_pair_trace[cluster_id_x()][12] = trace_ld_issued;
+      g_pair_trace[cluster_id_x()][13] = trace_fenced;
     })
     if (track_amax) absmax_finish<OutT>(p, mx2_bits, gridDim.x * 4u);
     if (lane == 0) bulk_wait_group<0>();    // all stores performed before the CTA may exit
@@ -588,6 +629,15 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   GemmParams p = base;
   p.tiles_m = (int)ceil_div(p.m, kPairBM);
   p.tiles_n = (int)ceil_div(p.n, kPairBN);
+  {
+    // With one band (A small enough to stay in L2) B is read from DRAM once; with A much larger than L2 and whole
+    // columns of tiles, A would be read again for every two or three tile columns.
+    const int64_t row_bytes = (int64_t)kPairBM * (p.k / 2 + p.k / 16);
+    p.band = (int)std::max<int64_t>(1, std::min<int64_t>(p.tiles_m, kPairBandBytes / std::max<int64_t>(row_bytes, 1)));
+  }
+#ifdef NVFP_PAIR_TRACE
+  if (const char* band = getenv("NVFP_TRACE_BAND")) p.band = std::max(1, std::min(p.tiles_m, atoi(band)));
+#endif
   CUtensorMap map_a, map_b, map_sfa, map_sfb;
   if (int rc = make_operand_map(&map_a, a, p.m, p.k, 128)) return rc;
   if (int rc = make_operand_map(&map_b, b, p.n, p.k, 128)) return rc;
@@ -607,7 +657,16 @@ int launch_pair(const GemmParams& base, const void* a, const void* b, void* cons
   auto kernel = fp4_gemm_pair_kernel<MX, OutT, OUT_MODE>;
   if (int rc = ensure_dynamic_smem(kernel, (int)C::kSmemBytes)) return rc;
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-  const unsigned pairs = (unsigned)std::min<int64_t>(tiles, sm_count / 2);
+  unsigned pairs = (unsigned)std::min<int64_t>(tiles, sm_count / 2);
+#ifdef NVFP_PAIR_TRACE
+  // instrumented build only: fewer CTA pairs, to see how a pair's stage time depends on how many pairs pull operands
+  if (const char* cap = getenv("NVFP_TRACE_MAX_PAIRS")) pairs = std::max(1u, std::min(pairs, (unsigned)atoi(cap)));
+  {
+    const char* no_loads = getenv("NVFP_TRACE_NO_LOADS");
+    const int flag = no_loads && atoi(no_loads) != 0;
+    NVFP_CUDA(cudaMemcpyToSymbolAsync(g_trace_no_loads, &flag, sizeof(flag), 0, cudaMemcpyHostToDevice, stream));
+  }
+#endif
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kThreads);

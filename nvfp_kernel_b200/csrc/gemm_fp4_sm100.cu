@@ -87,6 +87,7 @@ struct GemmParams {
   void* d;
   int m, n, k;
   int tiles_m, tiles_n;
+  int band;             // CTA-pair kernel: tiles are numbered in bands of this many tile rows (see pair_tile_coords)
   int sf_k_chunks;      // 512-byte chunks per 128-row scale tile along K
   int sfb_row_tiles;    // 128-row scale tiles of B
   uint32_t* status;
@@ -1303,13 +1304,13 @@ extern "C" int nvfp_linear_forward_gather(const nvfp_peer_group_t* group, int64_
 
 #ifdef NVFP_PAIR_TRACE
 // Instrumented build only: copies the per-cluster clock counters of the last fp4_gemm_pair_kernel launches to the host
-// (out: clusters x 8 uint64; see g_pair_trace) and clears them.
+// (out: clusters x kTraceSlots uint64; see g_pair_trace) and clears them.
 extern "C" int nvfp_debug_pair_trace(unsigned long long* out, int clusters) {
   clear_error();
   NVFP_REQUIRE(out != nullptr && clusters > 0 && clusters <= kTraceClusters, "bad trace request");
   NVFP_CUDA(cudaDeviceSynchronize());
-  NVFP_CUDA(cudaMemcpyFromSymbol(out, g_pair_trace, sizeof(unsigned long long) * 8 * clusters));
-  static unsigned long long zeros[kTraceClusters][8];
+  NVFP_CUDA(cudaMemcpyFromSymbol(out, g_pair_trace, sizeof(unsigned long long) * kTraceSlots * clusters));
+  static unsigned long long zeros[kTraceClusters][kTraceSlots];
   NVFP_CUDA(cudaMemcpyToSymbol(g_pair_trace, zeros, sizeof(zeros)));
   return NVFP_OK;
 }

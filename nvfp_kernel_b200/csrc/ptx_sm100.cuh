@@ -328,13 +328,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-// Arrivals on an mbarrier given by a shared::cluster address (own or peer CTA).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;"
-               ::"r"(cluster_bar), "r"(bytes) : "memory");
+// Arrive on a barrier of another CTA of the cluster with the default semantics (release at CTA scope).  Enough where the
+// barrier orders accesses to tensor memory (tcgen05 fences on both sides) and no data in shared or global memory
+// changes hands; an arrive with a cluster-scope release (mbarrier.arrive.release.cluster) was measured at about a thousand clocks in an
+// epilogue warp that has output stores in flight.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 // Tiled loads into THIS CTA's shared memory whose completion is reported to an mbarrier
 // that may live in the peer CTA (cluster address).  Each CTA fetches its own tile.
