@@ -393,7 +393,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // destinations in other GPUs' memory are written only once their owners have announced ready (lane 0 decides:
     // it issues the stores)
     bool peers_asked = sync.world <= 1, remote_ok = true;
-    NVFP_TRACE(long long trace_accfull = 0, trace_store = 0; unsigned long long trace_seen = 0, trace_released = 0, trace_ld_issued = 0, trace_loaded = 0, trace_fenced = 0;)
+    NVFP_TRACE(long long trace_accfull = 0, trace_store = 0; unsigned long long trace_seen = 0, trace_released = 0, trace_ld_issued = 0, trace_loaded = 0, trace_fenced = 0, trace_first_ld = 0;)
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++it) {
       int tm, tn;
       pair_tile_coords(p, tile, tm, tn);
@@ -418,8 +418,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int c = odd ? i : kSteps - 1 - i;
         uint32_t r[kCols];
 #pragma unroll
-        for (int h = 0; h < kCols / 32; ++h)
+        for (int h = 0; h < kCols / 32; ++h) {
           tmem_ld_32x32b_x32(t_row + c * kCols + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[h * 32]));
+          NVFP_TRACE(if (h == 0 && i == 0 && tile + tile_step < num_tiles) trace_first_ld += (unsigned long long)trace_clock();)
+        }
         NVFP_TRACE(if (i == 0 && tile + tile_step < num_tiles) trace_ld_issued += (unsigned long long)trace_clock();)
         tmem_ld_wait();
         NVFP_TRACE(if (i == 0 && tile + tile_step < num_tiles) trace_loaded += (unsigned long long)trace_clock();)
@@ -550,6 +552,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       g_pair_trace[cluster_id_x()][11] = trace_loaded;
       g_pair_trace[cluster_id_x()][12] = trace_ld_issued;
       g_pair_trace[cluster_id_x()][13] = trace_fenced;
+      g_pair_trace[cluster_id_x()][14] = trace_first_ld;
     })
     if (track_amax) absmax_finish<OutT>(p, mx2_bits, gridDim.x * 4u);
     if (lane == 0) bulk_wait_group<0>();    // all stores performed before the CTA may exit

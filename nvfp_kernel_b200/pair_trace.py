@@ -74,10 +74,11 @@ def main():
     loaded = sum(raw[c * SLOTS + 11] for c in range(clusters))
     ld_issued = sum(raw[c * SLOTS + 12] for c in range(clusters))
     fenced = sum(raw[c * SLOTS + 13] for c in range(clusters))
+    first_ld = sum(raw[c * SLOTS + 14] for c in range(clusters))
     handovers = sum(raw[c * SLOTS + 7] - 1 for c in range(clusters))
     if handovers > 0:
         print(f"tile hand-over, mean clocks over {handovers} hand-overs: finished tile seen by the epilogue -> shared columns "
-              f"in registers, accumulator released: {(released - seen) / handovers:.0f} (tcgen05 fence passed after {(fenced - seen) / handovers:.0f}, loads issued after {(ld_issued - seen) / handovers:.0f}, "
+              f"in registers, accumulator released: {(released - seen) / handovers:.0f} (tcgen05 fence passed after {(fenced - seen) / handovers:.0f}, first load issued after {(first_ld - seen) / handovers:.0f}, loads issued after {(ld_issued - seen) / handovers:.0f}, "
               f"data there after {(loaded - seen) / handovers:.0f}); released -> seen by the issuer: "
               f"{(taken - released) / handovers:.0f}")
     if no_loads:
