@@ -239,6 +239,17 @@ def test_llama70b_prefill_shard_shapes_with_outlier_channels():
         _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, seed=k)
 
 
+def test_tiles_numbered_in_bands_when_the_activation_outgrows_l2():
+    """K = 28672 (the Llama-3-70B down projection): a tile row of A is 4 MB, so the CTA-pair kernel numbers its tiles in
+    bands of 10 tile rows; 13 tile rows (the last one ragged) make a full band and a short one."""
+    m, n, k = 3172, 1536, 28672
+    a, w = gemm_inputs(m, n, k, seed=11, w_std=0.02)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha))
+    _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, seed=k)
+
+
 @pytest.mark.parametrize("rounding", ["rceil", "floor"])
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (17, 64, 192), (129, 256, 448), (256, 384, 1024), (4096, 8192, 8192)])
 def test_mxfp4_gemm(rounding, m, n, k):
