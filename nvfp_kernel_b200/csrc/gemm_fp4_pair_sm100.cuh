@@ -125,8 +125,9 @@ __device__ __forceinline__ long long trace_clock() { return clock64(); }
 #endif
 
 // Tile number -> tile row and column.  Tiles are numbered down the rows of a BAND of p.band tile rows, column after
-// column, band after band, so the CTA pairs that run at the same time (consecutive numbers) cover a roughly square
-// patch of the output: fewer distinct operand panels are being pulled out of L2 at any moment than with whole columns.
+// column, band after band.  The host sizes a band so that its rows of A stay in L2 while all of B streams past them
+// once (launch_pair): with whole columns of tiles and an A larger than L2, A would come from DRAM again for every
+// two or three tile columns (M = N = 8192, K = 28672: 648 us in bands of 10 tile rows, 709-756 us in whole columns).
 __device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   const int per_band = p.band * p.tiles_n;
   const int b = tile / per_band, within = tile - b * per_band;

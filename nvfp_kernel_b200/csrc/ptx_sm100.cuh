@@ -330,8 +330,8 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 }
 // Arrive on a barrier of another CTA of the cluster with the default semantics (release at CTA scope).  Enough where the
 // barrier orders accesses to tensor memory (tcgen05 fences on both sides) and no data in shared or global memory
-// changes hands; an arrive with a cluster-scope release (mbarrier.arrive.release.cluster) was measured at about a thousand clocks in an
-// epilogue warp that has output stores in flight.
+// changes hands; an arrive with a cluster-scope release (mbarrier.arrive.release.cluster) was measured at about a
+// thousand clocks in an epilogue warp that has output stores in flight.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
