@@ -239,6 +239,29 @@ def test_llama70b_prefill_shard_shapes_with_outlier_channels():
         _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, seed=k)
 
 
+def _ragged_pair_kernel_shapes(count=12, seed=2024):
+    """Seeded shapes that land on the CTA-pair kernel (at least 74 tiles of 256 x 256) with ragged edges in M, N and K
+    (K not a multiple of the 256-element stage, N not a multiple of 64, M not a multiple of 32)."""
+    g = torch.Generator().manual_seed(seed)
+    shapes = []
+    while len(shapes) < count:
+        m = int(torch.randint(2100, 4200, (1,), generator=g))
+        n = int(torch.randint(2100 // 32, 4200 // 32, (1,), generator=g)) * 32
+        k = int(torch.randint(2, 96, (1,), generator=g)) * 32
+        if ((m + 255) // 256) * ((n + 255) // 256) >= 74:
+            shapes.append((m, n, k))
+    return shapes
+
+
+@pytest.mark.parametrize("m,n,k", _ragged_pair_kernel_shapes())
+def test_ragged_shapes_on_the_pair_kernel(m, n, k):
+    a, w = gemm_inputs(m, n, k, seed=m + n + k, w_std=0.02)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha))
+    _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, seed=k, count=1024)
+
+
 def test_tiles_numbered_in_bands_when_the_activation_outgrows_l2():
     """K = 28672 (the Llama-3-70B down projection): a tile row of A is 4 MB, so the CTA-pair kernel numbers its tiles in
     bands of 10 tile rows; 13 tile rows (the last one ragged) make a full band and a short one."""
