@@ -257,9 +257,22 @@ def _ragged_pair_kernel_shapes(count=12, seed=2024):
 def test_ragged_shapes_on_the_pair_kernel(m, n, k):
     a, w = gemm_inputs(m, n, k, seed=m + n + k, w_std=0.02)
     a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
-    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
-    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha))
+    ref = _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, alpha)
+    # the output type changes the epilogue's step width (64 columns of 16-bit values, 32 of fp32)
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
+        out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, dt)
+        check_gemm(out, ref)
     _spot_check_fp64(out, a_fp4, a_sf, w_fp4, w_sf, alpha, seed=k, count=1024)
+
+
+@pytest.mark.parametrize("m,n,k", [(m, n, (k + 63) // 64 * 64) for (m, n, k) in _ragged_pair_kernel_shapes(6, seed=7)])
+def test_ragged_shapes_on_the_pair_kernel_mxfp4(m, n, k):
+    a = make_input("student_t3", (m, k), torch.bfloat16, m + k).cuda()
+    w = (make_input("normal", (n, k), torch.float32, n + k) * 0.02).to(torch.bfloat16).cuda()
+    a_fp4, a_sf = capi_mx_quant(a, "rceil")
+    w_fp4, w_sf = capi_mx_quant(w, "rceil")
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, None, torch.bfloat16, mx=True)
+    check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, None, block=32, ue8m0=True))
 
 
 def test_tiles_numbered_in_bands_when_the_activation_outgrows_l2():
