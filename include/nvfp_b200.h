@@ -35,7 +35,11 @@ typedef enum {
 #define NVFP_DTYPE_F32 2 /* GEMM output only: unrounded partial sums for K-split layers */
 
 /* MXFP4 scale rounding: exponent of amax/6 rounded up (no element saturates), or
- * truncated (the reference's disabled e8m0 branch, kernel/nvfp4_utils.cuh:196-202). */
+ * truncated (the reference's disabled e8m0 branch, kernel/nvfp4_utils.cuh:196-202).
+ * A block whose maximum is infinite gets the largest finite scale byte (254) when rounding
+ * up and, like that branch, the raw exponent bits (255, the e8m0 NaN code) when truncating;
+ * its elements become zeros (finite ones) and the largest e2m1 code (infinite ones) either way.
+ * NaN elements do not take part in a block's maximum; a block of nothing but NaNs gets 255. */
 #define NVFP_MX_ROUND_CEIL 0
 #define NVFP_MX_ROUND_FLOOR 1
 

@@ -245,7 +245,10 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
       const uint32_t bits = __float_as_uint(sf_value);
       uint32_t e = (bits >> 23) & 0xffu;
       if (mx_rounding == NVFP_MX_ROUND_CEIL && (bits & 0x7fffffu) != 0 && e < 254) e += 1;
-      e = min(e, 254u);
+      // An infinite block maximum has exponent bits 255.  The reference's e8m0 branch stores them as they are
+      // (kernel/nvfp4_utils.cuh:196-202 there; 255 is the e8m0 NaN code) and `floor` follows it; `ceil` keeps the
+      // largest finite scale.  Either way the elements are multiplied by 0.
+      if (mx_rounding == NVFP_MX_ROUND_CEIL) e = min(e, 254u);
       if (sf_value != sf_value) e = 255u;
       sf_byte = (uint8_t)e;
       const float out_scale = (e > 0 && e < 254) ? __uint_as_float((254u - e) << 23) : 0.0f;

@@ -110,12 +110,12 @@ void nvfp_oracle_quantize_nvfp4(const uint16_t* x, int is_bf16, int64_t m, int64
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < m; ++r) {
     for (int64_t kb = 0; kb < kb_count; ++kb) {
-      float v[16], amax = 0.f;
+      float v[16], amax = NAN;   /* fmaxf skips a NaN operand, as __hmax2 does: NaN only if every element is */
       for (int i = 0; i < 16; ++i) {
         uint16_t h = x[r * stride + kb * 16 + i];
         v[i] = is_bf16 ? bf16_to_f(h) : f16_to_f(h);
         float a = fabsf(v[i]);
-        if (a > amax) amax = a;                 /* NaN inputs are ignored, like __hmax2 */
+        amax = fmaxf(amax, a);                 /* NaN inputs are ignored, like __hmax2 */
       }
       float sfv = mul_ftz(gs, mul_ftz(amax, r6));
       uint8_t sb = e4m3_encode(sfv);
@@ -139,17 +139,17 @@ void nvfp_oracle_quantize_mxfp4(const uint16_t* x, int is_bf16, int64_t m, int64
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < m; ++r) {
     for (int64_t kb = 0; kb < kb_count; ++kb) {
-      float v[32], amax = 0.f;
+      float v[32], amax = NAN;   /* fmaxf skips a NaN operand, as __hmax2 does: NaN only if every element is */
       for (int i = 0; i < 32; ++i) {
         uint16_t h = x[r * stride + kb * 32 + i];
         v[i] = is_bf16 ? bf16_to_f(h) : f16_to_f(h);
         float a = fabsf(v[i]);
-        if (a > amax) amax = a;
+        amax = fmaxf(amax, a);
       }
       float sfv = mul_ftz(amax, r6);
       uint32_t bits = f_bits(sfv), e = (bits >> 23) & 0xff;
       if (rounding == 0 && (bits & 0x7fffffu) != 0 && e < 254) e += 1;
-      if (e > 254) e = 254;
+      if (e > 254 && rounding == 0) e = 254;   /* infinite block: rceil keeps 254, floor the raw exponent 255 (the reference's branch) */
       if (sfv != sfv) e = 255;
       float o = (e > 0 && e < 254) ? bits_f((254u - e) << 23) : 0.f;
       out_sf[sf_offset(r, kb, k_tiles)] = (uint8_t)e;
@@ -199,12 +199,12 @@ int nvfp_oracle_scaled_mm(const uint8_t* a, const uint8_t* b, const uint8_t* sfa
 
 /* max |x| as fp32 (exact in the input type) */
 float nvfp_oracle_amax(const uint16_t* x, int is_bf16, int64_t m, int64_t n, int64_t stride) {
-  float amax = 0.f;
+  float amax = 0.f;   /* the sweep starts from zero and fmaxf skips NaN operands, as __hmax2 does */
   for (int64_t r = 0; r < m; ++r)
     for (int64_t c = 0; c < n; ++c) {
       uint16_t h = x[r * stride + c];
       float a = fabsf(is_bf16 ? bf16_to_f(h) : f16_to_f(h));
-      if (a > amax) amax = a;
+      amax = fmaxf(amax, a);
     }
   return amax;
 }

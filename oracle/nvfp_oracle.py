@@ -76,10 +76,18 @@ class RcpTable:
         x = np.asarray(x, dtype=np.float32)
         bits = np.ascontiguousarray(x).view(np.uint32)
         uniq, inv = np.unique(bits, return_inverse=True)
-        try:
-            out = np.array([self._map[int(u)] for u in uniq], dtype=np.uint32)
-        except KeyError as exc:  # pragma: no cover - fixture bug
-            raise KeyError(f"reciprocal of bit pattern {exc} was not captured") from None
+
+        def one(u: int) -> int:
+            if u in self._map:
+                return self._map[u]
+            # not captured because no finite scale leads there: the instruction's results for NaN and infinity
+            if (u & 0x7FFFFFFF) > 0x7F800000:
+                return 0x7FFFFFFF                       # NaN in, NaN out
+            if (u & 0x7FFFFFFF) == 0x7F800000:
+                return u & 0x80000000                   # 1 / +-inf = +-0
+            raise KeyError(f"reciprocal of bit pattern {u} was not captured")
+
+        out = np.array([one(int(u)) for u in uniq], dtype=np.uint32)
         return out[inv].reshape(x.shape).view(np.float32)
 
 
@@ -157,6 +165,12 @@ def e2m1_encode(y) -> np.ndarray:
     sign = (np.signbit(y).astype(np.uint8) << 3)
     out = code | sign
     return np.where(np.isnan(y), np.uint8(0x7), out).astype(np.uint8)
+
+
+def _block_absmax(xb) -> np.ndarray:
+    """max |x| over the last axis the way __hmax2 / __hmax form it (kernel/nvfp4_utils.cuh:170-187): a NaN operand is
+    skipped, the result is NaN only if every element is."""
+    return np.fmax.reduce(np.abs(xb), axis=-1).astype(np.float32)
 
 
 def e2m1_decode(nib) -> np.ndarray:
@@ -241,7 +255,7 @@ def nvfp4_quantize_kernel(x, global_scale, rcp=rcp_true, pad_value: int = 0):
     assert n % 16 == 0
     gs = np.float32(global_scale)
     xb = x.reshape(m, n // 16, 16)
-    amax = np.max(np.abs(xb), axis=-1).astype(np.float32)      # :170-187 (exact in input type)
+    amax = _block_absmax(xb)                                   # :170-187 (exact in input type)
     r6 = rcp(np.array([6.0], dtype=np.float32))[0]
     sf_value = mul_ftz(gs, mul_ftz(amax, r6))                   # :192
     sf_byte = e4m3_encode_satfinite(sf_value)                    # :205
@@ -269,7 +283,7 @@ def nvfp4_quantize_torch_path(x, global_scale, rcp=rcp_true):
     assert n % 16 == 0
     gs = np.float32(global_scale)
     xb = x.reshape(m, n // 16, 16)
-    amax = np.max(np.abs(xb), axis=-1).astype(np.float32)
+    amax = _block_absmax(xb)
     block_scale = (amax / np.float32(6.0)).astype(np.float32)
     scaled = (block_scale * gs).astype(np.float32)
     clamped = np.clip(scaled, np.float32(2.0 ** -6), np.float32(E4M3_MAX))
@@ -309,7 +323,7 @@ def mxfp4_quantize(x, rounding: str = "rceil", pad_value: int = 0):
     m, n = x.shape
     assert n % 32 == 0
     xb = x.reshape(m, n // 32, 32)
-    amax = np.max(np.abs(xb), axis=-1).astype(np.float32)
+    amax = _block_absmax(xb)
     r6 = rcp_true(np.array([6.0], dtype=np.float32))[0]
     sf_value = mul_ftz(amax, r6)
     bits = sf_value.view(np.uint32)
@@ -319,7 +333,9 @@ def mxfp4_quantize(x, rounding: str = "rceil", pad_value: int = 0):
     elif rounding != "floor":
         raise ValueError(rounding)
     nanblk = np.isnan(sf_value)
-    exp = np.where(nanblk, 255, np.minimum(exp, 254))
+    # an infinite block maximum: the reference's branch stores the raw exponent bits, 255 (the e8m0 NaN code), and
+    # `floor` follows it; `rceil` keeps the largest finite scale, 254
+    exp = np.where(nanblk, 255, exp if rounding == "floor" else np.minimum(exp, 254))
     sf_byte = exp.astype(np.uint8)
     # 1 / 2^(exp-127) as an fp32 bit pattern; exp 0 (zero / flushed block) -> scale 0
     inv_bits = np.where((exp > 0) & (exp < 254), (254 - exp) << 23, 0).astype(np.uint32)

@@ -34,6 +34,18 @@ def make_input(dist: str, shape, dtype=torch.bfloat16, seed: int = 0) -> torch.T
         t = randn(shape)
         t[:, : shape[1] // 4] = 0.0
         t[:, shape[1] // 4: shape[1] // 2] *= 1e-38
+    elif dist == "specials":             # not in the reference: infinities, NaNs, -0, denormals, the largest finite value
+        t = randn(shape).to(dtype)
+        fi = torch.finfo(dtype)
+        values = [float("inf"), -float("inf"), float("nan"), -0.0, fi.smallest_normal / 4, -fi.smallest_normal / 8,
+                  fi.max, -fi.max, 0.0]
+        rows, cols = shape
+        for i, v in enumerate(values):
+            t[(3 + 7 * i) % rows, (5 + 16 * i) % cols] = v                       # one special value in an ordinary block
+            c0 = (16 * (i % max(1, cols // 16))) % cols
+            t[(40 + i) % rows, c0: c0 + 16] = v                                  # a block of nothing else
+            t[(60 + i) % rows, c0: c0 + 16: 2] = v                               # every other element of a block
+        return t
     elif dist == "student_t3":           # BASELINE config 5 activations
         z = randn(shape)
         chi2 = (randn(shape) ** 2 + randn(shape) ** 2 + randn(shape) ** 2) / 3.0

@@ -8,7 +8,8 @@ For every case it stores the kernel's packed nibbles, its scale bytes (valid reg
 the reference leaves padding uninitialised), the global scale, and the results of the
 reference's reciprocal_approximate_ftz_tensor for every value the quantizer can feed to
 rcp.approx.ftz with that global scale, so that the CPU oracle can replay the hardware
-reciprocal exactly.  Inputs are the seeded tensors of tests/golden/inputs.py (seed 11).
+reciprocal exactly.  Inputs are the seeded tensors of tests/golden/inputs.py (seed 11): the reference's seven
+distributions, `zeros_mixed` and `specials` (infinities, NaNs, -0, denormals; global scale 672 for that one).
 """
 import importlib.util
 import os
@@ -23,7 +24,7 @@ sys.path[:0] = [HERE, ROOT]
 from inputs import DISTRIBUTIONS, make_input, mx_duplicated_halves  # noqa: E402
 from oracle import nvfp_oracle as O  # noqa: E402
 
-CASE_DISTS = DISTRIBUTIONS + ("zeros_mixed",)
+CASE_DISTS = DISTRIBUTIONS + ("zeros_mixed", "specials")
 CASE_SHAPES = ((128, 128), (129, 80))
 
 
@@ -59,7 +60,8 @@ def main():
         for shape in CASE_SHAPES:
             for dt_name, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
                 x = make_input(dist, shape, dt, seed=11)
-                amax = x.float().abs().max()
+                finite = x.float()[torch.isfinite(x.float())]
+                amax = finite.abs().max() if dist != "specials" else torch.tensor(4.0)
                 gs = (torch.tensor(448.0 * 6.0) / (amax if amax > 0 else torch.tensor(1.0))).to(torch.float32)
                 xg, gsg = x.cuda(), gs.reshape(1).cuda()
                 fp4, sf = ref_quant(ref, xg, gsg)
@@ -73,7 +75,7 @@ def main():
                 out[key + "_sf"] = O.unswizzle_128x4(sf.cpu().numpy(), shape[0], shape[1] // 16)
                 out[key + "_rcp_in"] = torch.cat([first, second]).cpu().numpy()
                 out[key + "_rcp_out"] = torch.cat([r1, r2]).cpu().numpy()
-                if dist == "zeros_mixed":
+                if dist in ("zeros_mixed", "specials"):
                     out[key + "_x"] = x.view(torch.int16).numpy()
     path = os.path.join(out_dir, "ref_kernel_sm100.npz")
     np.savez_compressed(path, **out)

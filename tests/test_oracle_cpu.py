@@ -143,7 +143,7 @@ def test_mxfp4_properties():
         assert lin[0, 0] == 127 - 3 and (fp4 == 0x77).all()
 
 
-@pytest.mark.parametrize("dist", DISTRIBUTIONS + ("zeros_mixed", "student_t3"))
+@pytest.mark.parametrize("dist", DISTRIBUTIONS + ("zeros_mixed", "specials", "student_t3"))
 def test_mxfp4_floor_restatement_matches_the_reference_ue8m0_branch(dist):
     """tests/golden/ref_kernel_ue8m0_sm100.npz holds what the reference's own e8m0 branch (16-element blocks,
     kernel/nvfp4_utils.cuh:196-202, compiled from its sources and run on a B200 by make_ref_kernel_golden.py)
@@ -200,7 +200,7 @@ KERNEL_GOLD_PATH = os.path.join(os.path.dirname(__file__), "golden", "ref_kernel
 
 
 @pytest.mark.skipif(not os.path.exists(KERNEL_GOLD_PATH), reason="reference-kernel fixture not generated")
-@pytest.mark.parametrize("dist", DISTRIBUTIONS + ("zeros_mixed",))
+@pytest.mark.parametrize("dist", DISTRIBUTIONS + ("zeros_mixed", "specials"))
 def test_kernel_restatement_matches_reference_cuda_kernel_outputs(dist):
     """tests/golden/ref_kernel_sm100.npz holds outputs of the reference's own CUDA quantizer
     run on a B200, with the hardware reciprocals it used; the numpy and C restatements must

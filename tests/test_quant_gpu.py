@@ -18,6 +18,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TORCH_DT = {"bf16": torch.bfloat16, "fp16": torch.float16}
 ALL_DISTS = DISTRIBUTIONS + ("zeros_mixed",)
+# with a given global scale the quantizers are also compared on infinities, NaNs, -0 and denormals
+QUANT_DISTS = ALL_DISTS + ("specials",)
 
 
 REF = load_ref_quantizer()
@@ -54,7 +56,7 @@ def _padding_is_zero(sf, m, n, block=16):
 @pytest.mark.parametrize("shape", [(128, 128), (129, 80), (1, 4096), (17, 14336), (16, 16), (300, 2048), (1024, 1024)])
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
 def test_bit_exact_vs_reference_kernel(shape, dt):
-    for dist in ALL_DISTS:
+    for dist in QUANT_DISTS:
         x = make_input(dist, shape, TORCH_DT[dt], seed=11).cuda()
         gs = _gs_for(x).cuda()
         r_fp4, r_sf = _ref_quant(x, gs)
@@ -62,6 +64,29 @@ def test_bit_exact_vs_reference_kernel(shape, dt):
         assert torch.equal(fp4, r_fp4), f"{dist}: packed nibbles differ in {(fp4 != r_fp4).sum().item()} bytes"
         assert np.array_equal(_valid_sf(sf, *shape), _valid_sf(r_sf, *shape)), f"{dist}: scale bytes differ"
         assert _padding_is_zero(sf, *shape), f"{dist}: scale padding not zero"
+
+
+@needs_ref
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_special_values_vs_reference_kernel(dt):
+    """Infinities, NaNs, negative zero, denormals and the largest finite value inside otherwise ordinary blocks, and
+    blocks made of nothing else: the bytes must be the reference kernel's, whatever it does with them."""
+    tdt = TORCH_DT[dt]
+    x = make_input("normal", (256, 512), tdt, seed=23)
+    big = torch.finfo(tdt).max
+    tiny = torch.finfo(tdt).smallest_normal
+    specials = [float("inf"), -float("inf"), float("nan"), -0.0, tiny / 4, -tiny / 8, big, -big, 0.0]
+    for i, v in enumerate(specials):
+        x[3 + 7 * i, 5 + 16 * i] = v              # one special value in an ordinary block
+        x[200 + i, 64:80] = v                     # a block of nothing else
+        x[100 + i, 16 * i: 16 * i + 16:2] = v     # every other element of a block
+    x = x.cuda()
+    for gs_value in (1.0, 2688.0 / 4.0, 37.5):
+        gs = torch.tensor([gs_value], dtype=torch.float32, device="cuda")
+        r_fp4, r_sf = _ref_quant(x, gs)
+        fp4, sf = capi_quant(x, gs)
+        assert torch.equal(fp4, r_fp4), f"gs {gs_value}: packed nibbles differ in {(fp4 != r_fp4).sum().item()} bytes"
+        assert np.array_equal(_valid_sf(sf, 256, 512), _valid_sf(r_sf, 256, 512)), f"gs {gs_value}: scale bytes differ"
 
 
 @needs_ref
@@ -84,7 +109,7 @@ def test_matches_committed_reference_kernel_outputs():
     if not os.path.exists(path):
         pytest.skip("tests/golden/ref_kernel_sm100.npz not generated yet")
     gold = np.load(path)
-    for dist in ALL_DISTS:
+    for dist in QUANT_DISTS:
         for shape in ((128, 128), (129, 80)):
             for dt in ("bf16", "fp16"):
                 key = f"{dist}_{shape[0]}x{shape[1]}_{dt}"
@@ -95,7 +120,7 @@ def test_matches_committed_reference_kernel_outputs():
                 assert np.array_equal(_valid_sf(sf, *shape), gold[key + "_sf"]), key
 
 
-@pytest.mark.parametrize("dist", ALL_DISTS)
+@pytest.mark.parametrize("dist", QUANT_DISTS)
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
 def test_bit_exact_vs_cpu_oracle_with_hardware_reciprocal(dist, dt):
     for shape in ((129, 80), (256, 192)):
@@ -239,7 +264,7 @@ def test_one_pass_dynamic_quant_equals_global_scale_then_quantize(dt):
 def test_mxfp4_bit_exact_vs_cpu_restatement(rounding, dt):
     """CUDA against the CPU restatement, both roundings.  The restatement's `floor` mode is pinned to the reference's
     e8m0 branch (test_oracle_cpu.py, test_reference_pins_gpu.py); `rceil` is this package's own rule."""
-    for dist in ALL_DISTS + ("student_t3",):
+    for dist in QUANT_DISTS + ("student_t3",):
         for shape in ((128, 128), (129, 96), (1, 4096), (300, 2048)):
             x = make_input(dist, shape, TORCH_DT[dt], seed=13)
             fp4, sf = capi_mx_quant(x.cuda(), rounding)

@@ -36,7 +36,7 @@ def test_mxfp4_floor_mode_equals_the_reference_ue8m0_branch(dt):
     32-block is two copies of one 16-element half, both must pick the same scale (the block maximum is the same) and
     therefore the same nibbles: `floor` mode's packed bytes equal the reference's, and each 32-block scale byte
     equals both of the reference's 16-block bytes."""
-    for dist in DISTRIBUTIONS + ("zeros_mixed", "student_t3"):
+    for dist in DISTRIBUTIONS + ("zeros_mixed", "specials", "student_t3"):
         for m, n in ((128, 128), (129, 96), (1, 4096), (300, 2048)):
             half = make_input(dist, (m, n // 2), TORCH_DT[dt], seed=17).reshape(m, n // 32, 1, 16)
             x = half.expand(m, n // 32, 2, 16).reshape(m, n).contiguous().cuda()
