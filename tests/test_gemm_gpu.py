@@ -176,6 +176,31 @@ def test_result_written_as_nvfp4_equals_gemm_then_quantizer(m, n, k, dt):
             assert torch.equal(got_sf, want_sf), (m, n, k, b is not None)
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 256, 512), (300, 4128, 1024), (2048, 4096, 512), (48, 4096, 4096)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_result_written_as_nvfp4_with_overflowing_and_nan_values(m, n, k, dt):
+    """The same equality when the GEMM's values leave the finite range: an alpha that pushes part of the output to
+    +-inf in the output type, and a NaN bias entry.  Whatever the quantizer makes of such blocks, the epilogue must make
+    the same (few-rows, 128-row-tile and CTA-pair kernels)."""
+    from helpers import capi_mm_fp4out
+    a, w = gemm_inputs(m, n, k, seed=m + n, w_std=0.05)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    plain = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, dt)
+    big_alpha = (alpha * (torch.finfo(dt).max / plain.float().abs().max() * 4.0)).to(torch.float32)
+    bias = torch.zeros(n, dtype=dt, device="cuda")
+    bias[n // 3] = float("nan")
+    bias[n // 2] = float("inf")
+    for b in (None, bias):
+        plain = capi_mm(a_fp4, w_fp4, a_sf, w_sf, big_alpha, dt, bias=b)
+        assert torch.isinf(plain.float()).any()
+        for out_gs_value in (1.0, 2688.0 / 1000.0):
+            out_gs = torch.tensor([out_gs_value], dtype=torch.float32, device="cuda")
+            want_fp4, want_sf = capi_quant(plain.contiguous(), out_gs)
+            got_fp4, got_sf = capi_mm_fp4out(a_fp4, w_fp4, a_sf, w_sf, big_alpha, out_gs, dt, bias=b)
+            assert torch.equal(got_fp4, want_fp4), (m, n, k, b is not None, (got_fp4 != want_fp4).sum().item())
+            assert torch.equal(got_sf, want_sf), (m, n, k, b is not None)
+
+
 def test_config1_vs_reference_pseudo_quant_path():
     """BASELINE config 1 (1024^3, seed 0): real path vs the port of the reference's torch
     pseudo-quant path on CPU (oracle/pseudo_path.py, itself pinned to the reference's output)."""

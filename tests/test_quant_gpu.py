@@ -81,7 +81,8 @@ def test_special_values_vs_reference_kernel(dt):
         x[200 + i, 64:80] = v                     # a block of nothing else
         x[100 + i, 16 * i: 16 * i + 16:2] = v     # every other element of a block
     x = x.cuda()
-    for gs_value in (1.0, 2688.0 / 4.0, 37.5):
+    # ordinary global scales, then degenerate ones (zero, denormal, huge, infinite, NaN, negative)
+    for gs_value in (1.0, 2688.0 / 4.0, 37.5, 0.0, 1e-39, 3e38, float("inf"), float("nan"), -2.0):
         gs = torch.tensor([gs_value], dtype=torch.float32, device="cuda")
         r_fp4, r_sf = _ref_quant(x, gs)
         fp4, sf = capi_quant(x, gs)
