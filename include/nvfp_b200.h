@@ -351,7 +351,9 @@ int nvfp_reciprocal_approximate_ftz(float* out, const float* in, int64_t count, 
  *   amax_bits  device scratch, TWO uint32 (8 bytes, 8-byte aligned); the call resets them on the stream
  *              first; afterwards word 0 holds the bit pattern of max|x| as fp32.
  *   gs_out     device, one fp32; amax == 0 gives gs = 2688 (amax treated as 1,
- *              as in test_refactor.py:21-25).
+ *              as in test_refactor.py:21-25).  Like torch.abs(x).max(), the maximum is NaN when any
+ *              element is NaN (gs = NaN) and infinite when one is infinite (gs = 0); so are the scales of
+ *              nvfp_activation_scales, nvfp_dynamic_fp4_quant and nvfp_scaled_fp4_mm_amax.
  */
 int nvfp_global_scale(float* gs_out, uint32_t* amax_bits, const void* in, int64_t m, int64_t n,
                       int64_t in_row_stride, int in_dtype, void* stream);

@@ -163,10 +163,10 @@ __device__ __forceinline__ void absmax_fold(uint32_t& mx2_bits, const uint4& o) 
   if constexpr (sizeof(OutT) == 2) {
     using V2 = typename Vec2<OutT>::type;
     V2 mx2 = *reinterpret_cast<V2*>(&mx2_bits);
-    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.x)));
-    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.y)));
-    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.z)));
-    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const V2*>(&o.w)));
+    mx2 = __hmax2_nan(mx2, __habs2(*reinterpret_cast<const V2*>(&o.x)));
+    mx2 = __hmax2_nan(mx2, __habs2(*reinterpret_cast<const V2*>(&o.y)));
+    mx2 = __hmax2_nan(mx2, __habs2(*reinterpret_cast<const V2*>(&o.z)));
+    mx2 = __hmax2_nan(mx2, __habs2(*reinterpret_cast<const V2*>(&o.w)));
     mx2_bits = *reinterpret_cast<uint32_t*>(&mx2);
   }
 }
@@ -179,9 +179,9 @@ __device__ __forceinline__ void absmax_finish(const GemmParams& p, uint32_t mx2_
   if constexpr (sizeof(OutT) == 2) {
     using V2 = typename Vec2<OutT>::type;
     const V2 mx2 = *reinterpret_cast<V2*>(&mx2_bits);
-    float mx = to_float<OutT>(__hmax(mx2.x, mx2.y));
+    float mx = to_float<OutT>(__hmax_nan(mx2.x, mx2.y));
 #pragma unroll
-    for (int sh = 16; sh > 0; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+    for (int sh = 16; sh > 0; sh >>= 1) mx = max_nan_nonneg(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
     if ((threadIdx.x & 31) == 0) {
       uint32_t* toggle = p.amax_scratch + 4;
       const uint32_t t = *reinterpret_cast<volatile uint32_t*>(toggle) & 1u;   // read before this warp arrives

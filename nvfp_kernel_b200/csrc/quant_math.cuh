@@ -61,6 +61,14 @@ template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat
   return __bfloat162float(v);
 }
 
+// Maximum of two NON-NEGATIVE floats that propagates NaN, as torch.max does (the global scale of a tensor is
+// 2688 / torch.abs(x).max() in the reference, speed_test.py:46-47: a NaN anywhere makes it NaN).  Non-negative floats
+// order like their bit patterns, and a positive NaN's pattern is above infinity's.  The BLOCK maxima of the quantizers
+// are a different matter: they follow the reference kernel's __hmax2, which skips a NaN operand.
+__device__ __forceinline__ float max_nan_nonneg(float a, float b) {
+  return __uint_as_float(max(__float_as_uint(a), __float_as_uint(b)));
+}
+
 template <typename T> __device__ __forceinline__ typename Vec2<T>::type zero2();
 template <> __device__ __forceinline__ __half2 zero2<__half>() { return __float2half2_rn(0.0f); }
 template <> __device__ __forceinline__ __nv_bfloat162 zero2<__nv_bfloat16>() {

@@ -178,16 +178,16 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
 #pragma unroll
     for (int p = 0; p < kPasses; ++p)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx2 = __hmax2(mx2, __habs2(v[p].h2[i]));
-    float mx = to_float<T>(__hmax(mx2.x, mx2.y));
+      for (int i = 0; i < 8; ++i) mx2 = __hmax2_nan(mx2, __habs2(v[p].h2[i]));
+    float mx = to_float<T>(__hmax_nan(mx2.x, mx2.y));
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    for (int s = 16; s > 0; s >>= 1) mx = max_nan_nonneg(mx, __shfl_xor_sync(0xffffffffu, mx, s));
     if ((tid & 31) == 0) warp_max[tid >> 5] = mx;
     __syncthreads();
     if (tid == 0) {
       float r = warp_max[0];
 #pragma unroll
-      for (int w = 1; w < kThreads / 32; ++w) r = fmaxf(r, warp_max[w]);
+      for (int w = 1; w < kThreads / 32; ++w) r = max_nan_nonneg(r, warp_max[w]);
       uint32_t* toggle = dyn.scratch + 4;
       const uint32_t t = *reinterpret_cast<volatile uint32_t*>(toggle) & 1u;
       uint32_t* pair = dyn.scratch + 2u * t;
@@ -264,9 +264,11 @@ quant_fp4_kernel(const T* __restrict__ in, int64_t in_stride, const float* __res
     }
     if (col_ok && row < m)
       *reinterpret_cast<uint2*>(out + (int64_t)row * (n / 2) + col / 2) = packed;
+    // padding of the scale tensor (rows past m, columns past n) is zero whatever the global scale is: with a NaN
+    // or infinite scale a block of zeros would otherwise get the NaN byte
     if (seg % kThreadsPerBlock == 0)
       sf_stage[(sf_col_in_tile / 4) * 512 + (row_in_tile % 32) * 16 + (row_in_tile / 32) * 4 +
-               (sf_col_in_tile % 4)] = sf_byte;
+               (sf_col_in_tile % 4)] = (col_ok && row < m) ? sf_byte : (uint8_t)0;
   }
   __syncthreads();
   if (tid < 32 * kChunksPerTile) {
@@ -327,17 +329,17 @@ quant_fp4_small_kernel(const T* __restrict__ in, int64_t in_stride, uint8_t* __r
 #pragma unroll
   for (int i = 0; i < kSmallBlocksPerThread; ++i)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) mx2 = __hmax2(mx2, __habs2(v[i].h2[e]));
-  float mx = to_float<T>(__hmax(mx2.x, mx2.y));
+    for (int e = 0; e < 8; ++e) mx2 = __hmax2_nan(mx2, __habs2(v[i].h2[e]));
+  float mx = to_float<T>(__hmax_nan(mx2.x, mx2.y));
 #pragma unroll
-  for (int sh = 16; sh > 0; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+  for (int sh = 16; sh > 0; sh >>= 1) mx = max_nan_nonneg(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
   if ((tid & 31) == 0) warp_max[tid >> 5] = mx;
   __syncthreads();
   ptx::cluster_wait();
   if (tid < 32) {
     float r = tid < kSmallThreads / 32 ? warp_max[tid] : 0.0f;
 #pragma unroll
-    for (int sh = 16; sh > 0; sh >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, sh));
+    for (int sh = 16; sh > 0; sh >>= 1) r = max_nan_nonneg(r, __shfl_xor_sync(0xffffffffu, r, sh));
     // lane l tells CTA l
     if ((uint32_t)tid < csize)
       asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ptx::map_to_cta(ptx::smem_u32(&cta_max[rank]), (uint32_t)tid)), "f"(r)
@@ -347,7 +349,7 @@ quant_fp4_small_kernel(const T* __restrict__ in, int64_t in_stride, uint8_t* __r
   ptx::cluster_wait();
   if (tid == 0) {
     float r = cta_max[0];
-    for (uint32_t c = 1; c < csize; ++c) r = fmaxf(r, cta_max[c]);
+    for (uint32_t c = 1; c < csize; ++c) r = max_nan_nonneg(r, cta_max[c]);
     if (r == 0.0f) r = 1.0f;
     // same two roundings as amax_kernel: reciprocal(amax) * 2688
     const float g = __fmul_rn(__frcp_rn(r), 448.0f * 6.0f);
@@ -383,7 +385,8 @@ __global__ void rcp_kernel(float* __restrict__ out, const float* __restrict__ in
 }
 
 // max |x| over the tensor -> atomicMax on the fp32 bit pattern (non-negative floats
-// order like unsigned integers).  VEC = elements per load: 16 (one 32-byte load, needs 32-byte
+// order like unsigned integers; a NaN, whose pattern is above infinity's, wins every comparison on the way and makes the
+// global scale NaN, as torch.abs(x).max() would).  VEC = elements per load: 16 (one 32-byte load, needs 32-byte
 // aligned rows) or 8.  Every thread keeps four loads in flight; the grid sweeps the tensor front
 // to back.
 template <typename T, int VEC>
@@ -414,18 +417,18 @@ amax_kernel(const T* __restrict__ in, int64_t in_stride, int64_t m, int64_t n, u
 #pragma unroll
     for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int e = 0; e < VEC / 2; ++e) mx2 = __hmax2(mx2, __habs2(v[u].h2[e]));
+      for (int e = 0; e < VEC / 2; ++e) mx2 = __hmax2_nan(mx2, __habs2(v[u].h2[e]));
   }
-  float mx = to_float<T>(__hmax(mx2.x, mx2.y));
+  float mx = to_float<T>(__hmax_nan(mx2.x, mx2.y));
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+  for (int s = 16; s > 0; s >>= 1) mx = max_nan_nonneg(mx, __shfl_xor_sync(0xffffffffu, mx, s));
   __shared__ float warp_max[8];
   if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = mx;
   __syncthreads();
   if (threadIdx.x == 0) {
     float r = warp_max[0];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) r = fmaxf(r, warp_max[w]);
+    for (int w = 1; w < 8; ++w) r = max_nan_nonneg(r, warp_max[w]);
     // scratch[0] = running maximum (fp32 bits), scratch[1] = number of blocks that have contributed
     atomicMax(&scratch[0], __float_as_uint(r));
     __threadfence();

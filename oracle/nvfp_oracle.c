@@ -199,12 +199,14 @@ int nvfp_oracle_scaled_mm(const uint8_t* a, const uint8_t* b, const uint8_t* sfa
 
 /* max |x| as fp32 (exact in the input type) */
 float nvfp_oracle_amax(const uint16_t* x, int is_bf16, int64_t m, int64_t n, int64_t stride) {
-  float amax = 0.f;   /* the sweep starts from zero and fmaxf skips NaN operands, as __hmax2 does */
+  float amax = 0.f;   /* torch.abs(x).max(): a NaN anywhere makes the result NaN */
+  int nan_seen = 0;
   for (int64_t r = 0; r < m; ++r)
     for (int64_t c = 0; c < n; ++c) {
       uint16_t h = x[r * stride + c];
       float a = fabsf(is_bf16 ? bf16_to_f(h) : f16_to_f(h));
+      if (a != a) nan_seen = 1;
       amax = fmaxf(amax, a);
     }
-  return amax;
+  return nan_seen ? NAN : amax;
 }

@@ -429,4 +429,15 @@ def test_global_scale_from_the_producers_epilogue_chains_two_layers(m, k, n1, n2
     # both ends open at once: a middle layer takes a known scale and hands on its own
     z2, z2_gs = l2(y, x_global_scale=y_gs, return_output_scale=True)
     assert torch.equal(z2, z_plain) and torch.equal(z2_gs, capi_global_scale(z_plain))
+    # a NaN in layer 1's output (here through its bias) makes the scale NaN, as 2688 / torch.abs(y).max() would be; an
+    # infinity makes it 0; the scratch serves a clean call afterwards
+    good = l1.bias.data.clone()
+    for special in (float("nan"), float("inf")):
+        l1.bias.data[n1 // 2] = special
+        y_bad, gs_bad = l1(x, return_output_scale=True, next_layer=l2)
+        want = (448.0 * 6.0) / torch.abs(y_bad).max().to(torch.float32)
+        assert (torch.isnan(gs_bad).all() and torch.isnan(want)) if special != special else gs_bad.item() == want.item() == 0.0
+        l1.bias.data.copy_(good)
+    y, y_gs = l1(x, return_output_scale=True, next_layer=l2)
+    assert torch.equal(y_gs, capi_global_scale(l1(x)))
     assert nv.device_status() == 0

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import capi_global_scale, capi_mx_quant, capi_quant, capi_rcp, gpu_rcp_table, load_ref_quantizer
+from helpers import capi_dynamic_quant, capi_global_scale, capi_mx_quant, capi_quant, capi_rcp, gpu_rcp_table, load_ref_quantizer
 from inputs import DISTRIBUTIONS, make_input
 from oracle import c_oracle, nvfp_oracle as O
 
@@ -192,6 +192,34 @@ def test_reciprocal_op_close_to_true_reciprocal():
     rel = ((y.double() - 1.0 / x.double()).abs() * x.double()).max().item()
     assert rel < 2.0 ** -22
     assert capi_rcp(torch.zeros(1, device="cuda")).item() == float("inf")
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_global_scale_of_a_tensor_with_nan_or_infinity_follows_torch(dt):
+    """2688 / torch.abs(x).max() (speed_test.py:46-47 of the reference) is NaN as soon as one element is, and 0 when the
+    maximum is infinite.  Every way to the global scale says the same: the sweep, the sweep that also forms alpha, and
+    the dynamic quantizers (one cluster, one cooperative launch, two launches), whose bytes are those of the quantizer
+    called with that scale."""
+    tdt = TORCH_DT[dt]
+    gs_w = torch.tensor([3.0], dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for shape in ((16, 4096), (129, 80), (1024, 1024), (4096, 4096)):
+        for special, check in ((float("nan"), lambda g: bool(torch.isnan(g).all())),
+                               (-float("inf"), lambda g: g.item() == 0.0)):
+            x = make_input("normal", shape, tdt, seed=31).cuda()
+            x[shape[0] // 2, shape[1] // 3] = special
+            want = (448.0 * 6.0) / torch.abs(x).max().to(torch.float32)
+            assert check(want.reshape(1)), "the torch formula itself"
+            gs = capi_global_scale(x)
+            assert check(gs), (shape, special, gs.item())
+            fp4, sf, gs_d, alpha = capi_dynamic_quant(x, scratch, gs_w)
+            assert check(gs_d), (shape, special, gs_d.item())
+            assert torch.isnan(alpha).all() if special != special else torch.isinf(alpha).all()
+            q, qsf = capi_quant(x, gs_d)
+            assert torch.equal(fp4, q) and torch.equal(sf, qsf), (shape, special)
+    # and a clean tensor right after, with the same scratch words
+    x = make_input("normal", (1024, 1024), tdt, seed=32).cuda()
+    assert capi_dynamic_quant(x, scratch, gs_w)[2].item() == ((448.0 * 6.0) / torch.abs(x).max().to(torch.float32)).item()
 
 
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
