@@ -433,7 +433,7 @@ fp4_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
                   *reinterpret_cast<uint2*>(out_fp4 + (int64_t)token * (out_cols / 2) + ocol / 2) = qv;
                 if (ocol / 64 < k_tiles)      // token < 128: rows [m, nt) of the one 128-row scale tile get zero scales
                   p.out_sf[(int64_t)(ocol / 64) * 512 + (token % 32) * 16 + (token / 32) * 4 + (ocol % 64) / 16] =
-                      token < p.m ? sf : (uint8_t)0;
+                      (token < p.m && ocol < out_cols) ? sf : (uint8_t)0;      // padding stays zero under a NaN scale too
               }
             }
             continue;

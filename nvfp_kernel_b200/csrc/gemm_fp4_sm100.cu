@@ -257,7 +257,9 @@ __device__ __forceinline__ void quantize_row_chunk_to_regs(const GemmParams& p, 
     for (int i = 0; i < 8; ++i) h2[i] = *reinterpret_cast<const V2*>(&w[8 * b + i]);
     uint8_t sf;
     q[b] = nvfp4_quantize_block<OutT>(h2, gs, rcp_gs, rcp6, sf);
-    sf_word |= (uint32_t)sf << (8 * b);
+    // a block past the last column is padding of the scale tensor: zero whatever the global scale (a NaN or infinite
+    // one would turn a block of zeros into the NaN byte)
+    if (col0 + 16 * b < p.n) sf_word |= (uint32_t)sf << (8 * b);
   }
   if (row >= p.m) sf_word = 0;
 }
@@ -319,7 +321,7 @@ __device__ __forceinline__ void finish_row_chunk(const GemmParams& p, const uint
     for (int i = 0; i < 8; ++i) h2[i] = *reinterpret_cast<const V2*>(&out_pairs[8 * b + i]);
     uint8_t sf;
     q[b] = nvfp4_quantize_block<OutT>(h2, gs, rcp_gs, rcp6, sf);
-    sf_word |= (uint32_t)sf << (8 * b);
+    if (ocol0 + 16 * b < out_cols) sf_word |= (uint32_t)sf << (8 * b);      // padding blocks keep a zero scale byte
   }
   uint8_t* out = static_cast<uint8_t*>(p.d);
   if (row < p.m) {

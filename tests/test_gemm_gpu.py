@@ -193,7 +193,7 @@ def test_result_written_as_nvfp4_with_overflowing_and_nan_values(m, n, k, dt):
     for b in (None, bias):
         plain = capi_mm(a_fp4, w_fp4, a_sf, w_sf, big_alpha, dt, bias=b)
         assert torch.isinf(plain.float()).any()
-        for out_gs_value in (1.0, 2688.0 / 1000.0):
+        for out_gs_value in (1.0, 2688.0 / 1000.0, float("nan"), float("inf"), 0.0):
             out_gs = torch.tensor([out_gs_value], dtype=torch.float32, device="cuda")
             want_fp4, want_sf = capi_quant(plain.contiguous(), out_gs)
             got_fp4, got_sf = capi_mm_fp4out(a_fp4, w_fp4, a_sf, w_sf, big_alpha, out_gs, dt, bias=b)
