@@ -300,6 +300,21 @@ def test_ragged_shapes_on_the_pair_kernel_mxfp4(m, n, k):
     check_gemm(out, _gpu_reference(a_fp4, a_sf, w_fp4, w_sf, None, block=32, ue8m0=True))
 
 
+def test_more_than_two_to_the_31_output_elements():
+    """65536 x 49152 outputs (3.2e9 elements, 6.4 GB of bf16) over a short K: output offsets no longer fit 32 bits.
+    Checked band by band against the fp32 product of the dequantized operands."""
+    m, n, k = 65536, 49152, 64
+    a, w = gemm_inputs(m, n, k, seed=21, w_std=0.05)
+    a_fp4, a_sf, w_fp4, w_sf, alpha = _quantize_pair(a, w)
+    out = capi_mm(a_fp4, w_fp4, a_sf, w_sf, alpha, torch.bfloat16)
+    da = dequant_gpu(a_fp4, a_sf, 16, False)
+    dw = dequant_gpu(w_fp4, w_sf, 16, False)
+    for r0 in range(0, m, 4096):
+        ref = (da[r0:r0 + 4096] @ dw.T) * alpha
+        check_gemm(out[r0:r0 + 4096], ref)
+        del ref
+
+
 def test_tiles_numbered_in_bands_when_the_activation_outgrows_l2():
     """K = 28672 (the Llama-3-70B down projection): a tile row of A is 4 MB, so the CTA-pair kernel numbers its tiles in
     bands of 10 tile rows; 13 tile rows (the last one ragged) make a full band and a short one."""

@@ -149,6 +149,31 @@ def test_null_global_scale_means_one_and_strided_rows():
     assert torch.equal(c[0], d[0]) and torch.equal(c[1], d[1])
 
 
+def test_more_than_two_to_the_31_elements():
+    """A tensor of 2.4e9 elements (49152 x 49152, 4.8 GB of bf16): element offsets no longer fit 32 bits.  The global
+    scale equals torch's, and row bands from the start, the middle and the end quantize to the bytes the same rows give
+    as a small tensor of their own (dynamic one-launch call included)."""
+    m = n = 49152
+    x = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for r0 in range(0, m, 4096):                       # filled in bands to keep the temporaries small
+        x[r0:r0 + 4096] = torch.randn((4096, n), generator=g, device="cuda").to(torch.bfloat16)
+    x[m - 3, n - 5] = 40.0
+    gs = capi_global_scale(x)
+    assert gs.item() == ((448.0 * 6.0) / torch.tensor(40.0)).item()
+    fp4, sf = capi_quant(x, gs)
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    d_fp4, d_sf, d_gs, _ = capi_dynamic_quant(x, scratch, None)
+    assert torch.equal(d_gs, gs) and torch.equal(d_fp4, fp4) and torch.equal(d_sf, sf)
+    del d_fp4, d_sf
+    k_cols = n // 16
+    for r0 in (0, 24576 - 128, m - 256):
+        band = x[r0:r0 + 256].contiguous()
+        b_fp4, b_sf = capi_quant(band, gs)
+        assert torch.equal(fp4[r0:r0 + 256], b_fp4), r0
+        assert torch.equal(sf[r0:r0 + 256], b_sf), r0          # 128-row scale tiles: whole tiles of the swizzled tensor
+
+
 def test_rows_and_tiles_are_independent_full_size():
     """Size-independent properties at the BASELINE size: permuting rows permutes the
     output, and any aligned sub-block quantizes to the same bytes as the full tensor."""
