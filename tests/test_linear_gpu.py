@@ -441,3 +441,31 @@ def test_global_scale_from_the_producers_epilogue_chains_two_layers(m, k, n1, n2
     y, y_gs = l1(x, return_output_scale=True, next_layer=l2)
     assert torch.equal(y_gs, capi_global_scale(l1(x)))
     assert nv.device_status() == 0
+
+
+def test_empty_batches():
+    """Zero rows: every level returns empty results of the right shape and launches nothing that could fault; a batch
+    of ordinary size right after is unaffected."""
+    import nvfp_kernel_b200 as nv
+    from helpers import capi_dynamic_quant, capi_global_scale, capi_mm, capi_quant
+    k, n = 256, 384
+    w = (torch.randn(n, k) * 0.05).to(torch.bfloat16).cuda()
+    layer = nv.QuantLinear(k, n, bias=True, device="cuda").load_weight(w)
+    empty = torch.empty((0, k), dtype=torch.bfloat16, device="cuda")
+    y = layer(empty)
+    assert y.shape == (0, n) and y.dtype == torch.bfloat16
+    q, sf = nv.scaled_fp4_quant(empty, torch.ones(1, device="cuda"))
+    assert q.shape == (0, k // 2) and sf.shape[0] == 0
+    # the C ABI with m == 0: nothing written, status OK
+    one = torch.ones(1, device="cuda")
+    cq, csf = capi_quant(empty, one)
+    assert cq.numel() == 0 and csf.numel() == 0
+    w_gs = capi_global_scale(w)
+    w4, wsf = capi_quant(w, w_gs)
+    out = capi_mm(cq, w4, csf, wsf, one, torch.bfloat16)
+    assert out.shape == (0, n)
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    dq = capi_dynamic_quant(empty, scratch, w_gs)
+    assert dq[0].numel() == 0
+    x = torch.randn(64, k).to(torch.bfloat16).cuda()
+    assert torch.equal(layer(x), layer(x.clone())) and nv.device_status() == 0
